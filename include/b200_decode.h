@@ -1,0 +1,196 @@
+/*
+ * b200_decode.h - C ABI of the B200 (sm_100a) decode hot path.
+ *
+ * One shared library, libb200decode.so.  Plain pointers and sizes only; every
+ * pointer is a DEVICE pointer unless stated otherwise; `stream` is a
+ * cudaStream_t passed as void*.  Unless an entry point says otherwise it
+ *   - allocates nothing and frees nothing (the caller owns every buffer,
+ *     including workspaces),
+ *   - never synchronises the stream or the device,
+ *   - returns 0 on success or a negative code (see b200_strerror); argument
+ *     errors are detected on the host before anything is launched,
+ *   - reports problems found on the device (a block id outside the pool, a
+ *     bounded barrier wait that ran out, ...) by writing a positive code into
+ *     the 4-byte status word at the start of the workspace it was given; the
+ *     word is sticky (first error wins) and must be zero before first use.
+ *     Read it with b200_read_status().
+ *
+ * The reference (AdvayMonga/inference-server) has no native interface: its
+ * decode step is TorchBackend.decode_step_batched
+ * (src/inference_server/backends/torch_backend.py:305-322), which hands dense
+ * tensors to a HuggingFace model.  Each entry point below names the piece of
+ * that step it replaces.
+ */
+#ifndef B200_DECODE_H_
+#define B200_DECODE_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* dtype codes for the attention / KV entry points */
+#define B200_DTYPE_BF16 0
+#define B200_DTYPE_F32 1
+
+/* ---------------------------------------------------------------- status -- */
+
+int b200_abi_version(void);
+/* Text for a return code (negative) or a device status word (positive). */
+const char* b200_strerror(int code);
+/* Thread-local detail string of the last failing call on this thread. */
+const char* b200_last_error_detail(void);
+/* Copies the device status word to the host and returns it negated (0 = clean).
+ * The only entry point that synchronises `stream`. */
+int b200_read_status(const void* status_word, void* stream);
+
+/* ------------------------------------------------------- paged attention -- */
+
+/*
+ * Replaces: page gather kv_cache/hf_format.py:21-45 (blocks_to_dynamic_cache),
+ * left-padded batch build backends/torch_backend.py:237-258, and the attention
+ * arithmetic of the model forward called at torch_backend.py:314-320
+ * (softmax(q K^T * scale) V per row with GQA head sharing, softmax in fp32).
+ *
+ *   q            [batch, num_q_heads, head_dim]
+ *   k_pool/v_pool[num_blocks, num_kv_heads, page_size, head_dim] - the layout
+ *                of kv_cache/block_manager.py:33-49, read in place
+ *   block_table  [batch, max_pages_per_seq] int32 page ids (Block.block_id,
+ *                kv_cache/block.py:18); all pages full except the last
+ *   ctx_lens     [batch] int32 tokens to attend to (including this step's)
+ *   out          [batch, num_q_heads, head_dim], same dtype as q
+ *   workspace    b200_paged_attn_workspace_bytes(...) bytes; starts with the
+ *                status word
+ *   split_tokens tokens per split of the KV length, a multiple of 64
+ *
+ * bf16 pools with page_size 16, head_dim 64 or 128 and at most 16 q heads per
+ * kv head take the TMA split-K kernel; anything else (fp32, other pages or head
+ * sizes up to 256) takes a plain fp32-arithmetic kernel without a split.
+ */
+size_t b200_paged_attn_workspace_bytes(int batch, int num_q_heads, int head_dim,
+                                       int max_pages_per_seq, int page_size, int split_tokens);
+int b200_paged_attn_decode(const void* q, const void* k_pool, const void* v_pool,
+                           const int32_t* block_table, const int32_t* ctx_lens, void* out,
+                           void* workspace, size_t workspace_bytes, int batch, int num_q_heads,
+                           int num_kv_heads, int head_dim, int page_size, int num_blocks,
+                           int max_pages_per_seq, float scale, int split_tokens, int dtype,
+                           void* stream);
+
+/*
+ * Replaces: the per-step KV growth DynamicCache.update does with torch.cat
+ * inside the forward called at torch_backend.py:314-320, and gives decode the
+ * page write the reference only has for prompts
+ * (kv_cache/cache_manager.py:185-214, _store_kv_in_blocks).
+ *
+ *   k_new/v_new  [batch, num_kv_heads, head_dim]
+ *   positions    [batch] int32 token index the row is written at
+ *   status_word  4-byte device word (may be NULL)
+ */
+int b200_kv_append(const void* k_new, const void* v_new, void* k_pool, void* v_pool,
+                   const int32_t* block_table, const int32_t* positions, void* status_word,
+                   int batch, int num_kv_heads, int head_dim, int page_size, int num_blocks,
+                   int max_pages_per_seq, int dtype, void* stream);
+
+/* ------------------------------------------------------------------- MoE -- */
+
+/*
+ * Replaces: the router of the sparse MoE block run by the forward at
+ * torch_backend.py:314-320 (fp32 softmax over experts, top-k, optional
+ * renormalisation).  Ties between equal logits go to the lower expert id.
+ *
+ *   logits       [num_tokens, num_experts] fp32
+ *   topk_ids     [num_tokens, top_k] int32, value-descending
+ *   topk_weights [num_tokens, top_k] fp32
+ */
+int b200_moe_route(const float* logits, int num_tokens, int num_experts, int top_k,
+                   int renormalize, int32_t* topk_ids, float* topk_weights, void* stream);
+
+/*
+ * Replaces: the sort-by-expert / offsets step of the grouped expert forward
+ * under the same call.  Pairs (token, slot) are numbered token * top_k + slot
+ * and stably sorted by expert id.
+ *
+ *   sorted_pair_ids [num_tokens * top_k] pair id held by each sorted row
+ *   row_of_pair     [num_tokens * top_k] sorted row of each pair (inverse)
+ *   expert_offsets  [num_experts + 1] first sorted row of each expert
+ *   tiles           b200_moe_max_tiles(...) * 16 bytes, {expert,row0,rows,0}
+ *                   int32 records of <=128 rows, or NULL (then num_tiles NULL)
+ *   num_tiles       1 int32
+ *   workspace       b200_moe_permute_workspace_bytes(...); starts with the
+ *                   status word
+ */
+size_t b200_moe_permute_workspace_bytes(int num_tokens, int num_experts, int top_k);
+int b200_moe_max_tiles(int num_tokens, int num_experts, int top_k);
+int b200_moe_permute(const int32_t* topk_ids, int num_tokens, int num_experts, int top_k,
+                     int32_t* sorted_pair_ids, int32_t* row_of_pair, int32_t* expert_offsets,
+                     void* tiles, int32_t* num_tiles, void* workspace, size_t workspace_bytes,
+                     void* stream);
+
+/*
+ * Replaces: the dynamic per-token activation quantisation of the FP8 expert
+ * layers (one fp32 scale per row per 128 columns: s = amax / 448, 1 for an
+ * all-zero group; q = e4m3(x / s)).
+ *
+ *   x            [num_tokens, hidden] bf16
+ *   row_of_pair  NULL: row t is written to row t.  Otherwise [num_tokens*top_k]:
+ *                row t is written to each of its top_k sorted rows.
+ *   xq           [rows, hidden] e4m3 bytes;  x_scale [rows, hidden / 128] fp32
+ */
+int b200_act_quant_fp8(const void* x, const int32_t* row_of_pair, int num_tokens, int hidden,
+                       int top_k, void* xq, float* x_scale, void* stream);
+
+/*
+ * Replace: the expert matmuls of the forward at torch_backend.py:314-320 on
+ * e4m3 weights with fp32 128x128 block scales (tcgen05 grouped GEMM).
+ *
+ * gate_up: h = silu(W13[e][:inter] x) * (W13[e][inter:] x) per sorted row,
+ *          re-quantised per row per 128 columns.
+ *   xq [num_rows, hidden] e4m3, x_scale [num_rows, hidden/128]
+ *   w13 [num_experts, 2*inter, hidden] e4m3,
+ *   w13_scale_inv [num_experts, 2*inter/128, hidden/128] fp32
+ *   hq [num_rows, inter] e4m3, h_scale [num_rows, inter/128] fp32
+ * down:    y = W2[e] h per sorted row.
+ *   w2 [num_experts, hidden, inter] e4m3,
+ *   w2_scale_inv [num_experts, hidden/128, inter/128] fp32
+ *   y_sorted [num_rows, hidden] bf16
+ * tiles/num_tiles come from b200_moe_permute; status_word may be NULL.
+ */
+int b200_moe_fp8_gemm_gate_up(const void* xq, const float* x_scale, const void* w13,
+                              const float* w13_scale_inv, const void* tiles,
+                              const int32_t* num_tiles, void* hq, float* h_scale,
+                              void* status_word, int num_rows, int num_experts, int hidden,
+                              int inter, void* stream);
+int b200_moe_fp8_gemm_down(const void* hq, const float* h_scale, const void* w2,
+                           const float* w2_scale_inv, const void* tiles, const int32_t* num_tiles,
+                           void* y_sorted, void* status_word, int num_rows, int num_experts,
+                           int hidden, int inter, void* stream);
+
+/*
+ * Replaces: the routing-weight multiply and per-token sum over the top_k expert
+ * outputs.  out[t] = sum_k topk_weights[t,k] * y_sorted[row_of_pair[t,k]] in
+ * fp32, k ascending, rounded to bf16.
+ */
+int b200_moe_combine(const void* y_sorted, const int32_t* row_of_pair, const float* topk_weights,
+                     int num_tokens, int hidden, int top_k, void* out, void* stream);
+
+/*
+ * The whole FP8 MoE layer for one batch of tokens: route, permute, quantise,
+ * gate/up GEMM, down GEMM, combine, in that order on `stream`.
+ *
+ *   x [num_tokens, hidden] bf16, router_logits [num_tokens, num_experts] fp32,
+ *   out [num_tokens, hidden] bf16, workspace b200_moe_fp8_workspace_bytes(...).
+ */
+size_t b200_moe_fp8_workspace_bytes(int num_tokens, int num_experts, int top_k, int hidden,
+                                    int inter);
+int b200_moe_fp8_forward(const void* x, const float* router_logits, const void* w13,
+                         const float* w13_scale_inv, const void* w2, const float* w2_scale_inv,
+                         void* out, void* workspace, size_t workspace_bytes, int num_tokens,
+                         int num_experts, int top_k, int hidden, int inter, int renormalize,
+                         void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* B200_DECODE_H_ */

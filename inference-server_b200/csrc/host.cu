@@ -1,0 +1,171 @@
+// Host-side support for the C-ABI: device check, TMA tensor-map cache, error
+// text.  Nothing here launches a kernel or allocates device memory.
+
+#include <stdarg.h>
+#include <stdio.h>
+#include <string.h>
+
+#include <mutex>
+#include <vector>
+
+#include "common.cuh"
+#include "host.h"
+
+namespace b200 {
+
+static thread_local char g_detail[512] = "";
+
+void set_detail(const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_detail, sizeof(g_detail), fmt, ap);
+  va_end(ap);
+}
+const char* get_detail() { return g_detail; }
+
+int cuda_fail(cudaError_t e, const char* where) {
+  set_detail("%s: %s", where, cudaGetErrorString(e));
+  return -kErrCuda;
+}
+
+int check_device(int* device_out) {
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return cuda_fail(e, "cudaGetDevice");
+  static int major_of[64];
+  static bool known[64] = {false};
+  int major = 0;
+  if (dev < 64 && known[dev]) {
+    major = major_of[dev];
+  } else {
+    e = cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev);
+    if (e != cudaSuccess) return cuda_fail(e, "cudaDeviceGetAttribute");
+    if (dev < 64) {
+      major_of[dev] = major;
+      known[dev] = true;
+    }
+  }
+  if (major != 10) {
+    set_detail("device %d has compute capability %d.x; this library is built for sm_100a only", dev,
+               major);
+    return -kErrUnsupported;
+  }
+  if (device_out) *device_out = dev;
+  return 0;
+}
+
+// ------------------------------------------------------- tensor-map cache --
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+struct MapKey {
+  int device;
+  const void* base;
+  uint64_t rows, cols;
+  int elem_bytes;
+  uint32_t box_rows, box_cols;
+  bool operator==(const MapKey& o) const {
+    return device == o.device && base == o.base && rows == o.rows && cols == o.cols &&
+           elem_bytes == o.elem_bytes && box_rows == o.box_rows && box_cols == o.box_cols;
+  }
+};
+struct MapEntry {
+  MapKey key;
+  CUtensorMap map;
+};
+
+static std::mutex g_map_mu;
+static std::vector<MapEntry> g_maps;
+static EncodeTiledFn g_encode = nullptr;
+
+int get_tensor_map_2d(const void* base, uint64_t rows, uint64_t cols, int elem_bytes,
+                      uint32_t box_rows, uint32_t box_cols, CUtensorMap* out) {
+  int dev = 0;
+  cudaError_t ce = cudaGetDevice(&dev);
+  if (ce != cudaSuccess) return cuda_fail(ce, "cudaGetDevice");
+  MapKey key{dev, base, rows, cols, elem_bytes, box_rows, box_cols};
+  std::lock_guard<std::mutex> lock(g_map_mu);
+  for (const MapEntry& e : g_maps) {
+    if (e.key == key) {
+      *out = e.map;
+      return 0;
+    }
+  }
+  if (g_encode == nullptr) {
+    void* fn = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    ce = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres);
+    if (ce != cudaSuccess || fn == nullptr || qres != cudaDriverEntryPointSuccess) {
+      set_detail("cuTensorMapEncodeTiled is not available from the driver");
+      return -kErrTensorMap;
+    }
+    g_encode = reinterpret_cast<EncodeTiledFn>(fn);
+  }
+  if (box_cols * static_cast<uint32_t>(elem_bytes) != 128u || box_rows == 0 || box_rows > 256 ||
+      (reinterpret_cast<uintptr_t>(base) & 15) != 0 || (cols * elem_bytes) % 16 != 0) {
+    set_detail("tensor map: base %p rows %llu cols %llu elem %d box %ux%u is not encodable", base,
+               (unsigned long long)rows, (unsigned long long)cols, elem_bytes, box_rows, box_cols);
+    return -kErrTensorMap;
+  }
+  cuuint64_t gdim[2] = {cols, rows};
+  cuuint64_t gstride[1] = {cols * static_cast<uint64_t>(elem_bytes)};
+  cuuint32_t box[2] = {box_cols, box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  MapEntry entry;
+  entry.key = key;
+  CUresult r = g_encode(&entry.map,
+                        elem_bytes == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8,
+                        2, const_cast<void*>(base), gdim, gstride, box, estr,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                        CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    set_detail("cuTensorMapEncodeTiled failed with CUresult %d (base %p rows %llu cols %llu)", (int)r,
+               base, (unsigned long long)rows, (unsigned long long)cols);
+    return -kErrTensorMap;
+  }
+  if (g_maps.size() >= 4096) g_maps.erase(g_maps.begin(), g_maps.begin() + 2048);
+  g_maps.push_back(entry);
+  *out = entry.map;
+  return 0;
+}
+
+}  // namespace b200
+
+using namespace b200;
+
+extern "C" int b200_abi_version(void) { return 1; }
+
+extern "C" const char* b200_strerror(int code) {
+  switch (code < 0 ? -code : code) {
+    case kErrOk: return "ok";
+    case kErrBadArg: return "bad argument (null pointer, shape or alignment)";
+    case kErrUnsupported: return "unsupported device or configuration (sm_100a required)";
+    case kErrWorkspace: return "workspace too small";
+    case kErrCuda: return "CUDA runtime error";
+    case kErrTensorMap: return "TMA tensor map could not be encoded";
+    case kErrDevBadBlockId: return "device: block table entry outside the pool";
+    case kErrDevBadCtxLen: return "device: context length or position outside the block table";
+    case kErrDevWaitTimeout: return "device: a bounded barrier wait ran out";
+    case kErrDevBadExpert: return "device: expert id outside [0, num_experts)";
+    default: return "unknown error";
+  }
+}
+
+extern "C" const char* b200_last_error_detail(void) { return get_detail(); }
+
+// Copies the device status word back and returns it negated (0 = clean).
+// This is the one entry point that synchronises the stream.
+extern "C" int b200_read_status(const void* status_word, void* stream) {
+  if (status_word == nullptr) {
+    set_detail("read_status: null pointer");
+    return -kErrBadArg;
+  }
+  int v = 0;
+  cudaError_t e = cudaMemcpyAsync(&v, status_word, sizeof(int), cudaMemcpyDeviceToHost, as_stream(stream));
+  if (e != cudaSuccess) return cuda_fail(e, "cudaMemcpyAsync(status)");
+  e = cudaStreamSynchronize(as_stream(stream));
+  if (e != cudaSuccess) return cuda_fail(e, "cudaStreamSynchronize");
+  return -v;
+}

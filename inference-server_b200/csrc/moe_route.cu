@@ -1,0 +1,333 @@
+// MoE routing, token permutation, activation quantisation and weighted combine.
+//
+// Semantics follow the router and expert dispatch the reference reaches through
+// its model forward (src/inference_server/backends/torch_backend.py:305-322 ->
+// transformers Qwen3MoeTopKRouter / grouped experts forward):
+//   route    probabilities = softmax(logits) in fp32; the K largest are taken,
+//            value descending, equal values by lower expert id; weights are the
+//            selected probabilities, renormalised to sum to 1 when `renorm`.
+//            Selection compares the logits themselves (softmax is monotone), so
+//            expert ids do not depend on how exp() rounds.
+//   permute  the T*K (token, slot) pairs, numbered token-major, are stably
+//            sorted by expert id: rows of one expert are contiguous and keep
+//            ascending pair order.
+//   quant    one scale per token per 128 columns: s = amax / 448 (1 when the
+//            group is all zero), q = e4m3(x / s), stored with s.
+//   combine  out[t] = sum_k w[t,k] * y[row_of_pair[t,k]] in fp32, k ascending.
+// All of it is integer/byte work bound by launch latency and HBM traffic; none
+// of it touches the tensor cores.
+
+#include "common.cuh"
+#include "host.h"
+
+namespace b200 {
+
+constexpr int kRouteWarps = 4;
+constexpr int kRouteMaxPerLane = 8;  // num_experts <= 256
+
+__global__ void __launch_bounds__(kRouteWarps * 32)
+moe_route_kernel(const float* __restrict__ logits, int T, int E, int K, int renorm,
+                 int* __restrict__ topk_ids, float* __restrict__ topk_w) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int t = blockIdx.x * kRouteWarps + warp;
+  if (t >= T) return;
+  float v[kRouteMaxPerLane];
+  float mx = -INFINITY;
+#pragma unroll
+  for (int j = 0; j < kRouteMaxPerLane; ++j) {
+    const int e = lane + 32 * j;
+    v[j] = e < E ? logits[static_cast<size_t>(t) * E + e] : -INFINITY;
+    mx = fmaxf(mx, v[j]);
+  }
+  mx = warp_max(mx);
+  float den = 0.f;
+#pragma unroll
+  for (int j = 0; j < kRouteMaxPerLane; ++j)
+    if (lane + 32 * j < E) den += expf(v[j] - mx);
+  den = warp_sum(den);
+
+  unsigned taken = 0;  // bit j: this lane's candidate j has been selected
+  float sel_sum = 0.f, my_p = 0.f;
+  int my_id = 0;
+  for (int k = 0; k < K; ++k) {
+    float bv = -INFINITY;
+    int be = 0x7fffffff;
+#pragma unroll
+    for (int j = 0; j < kRouteMaxPerLane; ++j) {
+      const int e = lane + 32 * j;
+      if (e < E && !((taken >> j) & 1u) && (be == 0x7fffffff || v[j] > bv)) {
+        bv = v[j];
+        be = e;
+      }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+      const int oe = __shfl_xor_sync(0xffffffffu, be, o);
+      const bool better = oe != 0x7fffffff && (be == 0x7fffffff || ov > bv || (ov == bv && oe < be));
+      if (better) {
+        bv = ov;
+        be = oe;
+      }
+    }
+    if ((be & 31) == lane) taken |= 1u << (be >> 5);
+    const float p = expf(bv - mx);
+    sel_sum += p;
+    if (lane == k) {
+      my_p = p;
+      my_id = be;
+    }
+  }
+  if (lane < K) {
+    topk_ids[static_cast<size_t>(t) * K + lane] = my_id;
+    topk_w[static_cast<size_t>(t) * K + lane] = my_p / (renorm ? sel_sum : den);
+  }
+}
+
+// ---------------------------------------------------------------- permute ---
+constexpr int kRankThreads = 256;
+
+// One CTA per expert: stable rank of every pair routed to this expert.
+__global__ void __launch_bounds__(kRankThreads)
+moe_rank_kernel(const int* __restrict__ topk_ids, int n_pairs, int* __restrict__ rank,
+                int* __restrict__ counts) {
+  __shared__ int part[kRankThreads];
+  const int e = blockIdx.x, tid = threadIdx.x;
+  const int chunk = (n_pairs + kRankThreads - 1) / kRankThreads;
+  const int lo = min(n_pairs, tid * chunk), hi = min(n_pairs, lo + chunk);
+  int c = 0;
+  for (int i = lo; i < hi; ++i) c += topk_ids[i] == e;
+  part[tid] = c;
+  __syncthreads();
+  for (int o = 1; o < kRankThreads; o <<= 1) {
+    const int add = tid >= o ? part[tid - o] : 0;
+    __syncthreads();
+    part[tid] += add;
+    __syncthreads();
+  }
+  int run = part[tid] - c;  // exclusive prefix
+  for (int i = lo; i < hi; ++i)
+    if (topk_ids[i] == e) rank[i] = run++;
+  if (tid == kRankThreads - 1) counts[e] = part[tid];
+}
+
+constexpr int kScatterThreads = 256;
+
+__global__ void __launch_bounds__(kScatterThreads)
+moe_scatter_kernel(const int* __restrict__ topk_ids, const int* __restrict__ rank,
+                   const int* __restrict__ counts, int n_pairs, int E, int tile_rows,
+                   int* __restrict__ sorted_pair, int* __restrict__ row_of_pair,
+                   int* __restrict__ expert_offsets, MoeTile* __restrict__ tiles,
+                   int* __restrict__ num_tiles, int* __restrict__ err) {
+  extern __shared__ int sm[];  // counts[E], offsets[E + 1]
+  int* cnt = sm;
+  int* off = sm + E;
+  const int tid = threadIdx.x;
+  for (int e = tid; e < E; e += kScatterThreads) cnt[e] = counts[e];
+  __syncthreads();
+  for (int e = tid; e <= E; e += kScatterThreads) {
+    int s = 0;
+    for (int j = 0; j < e; ++j) s += cnt[j];
+    off[e] = s;
+  }
+  __syncthreads();
+  if (blockIdx.x == 0) {
+    for (int e = tid; e <= E; e += kScatterThreads) expert_offsets[e] = off[e];
+    if (tiles != nullptr) {
+      for (int e = tid; e < E; e += kScatterThreads) {
+        int tp = 0;
+        for (int j = 0; j < e; ++j) tp += (cnt[j] + tile_rows - 1) / tile_rows;
+        const int nt = (cnt[e] + tile_rows - 1) / tile_rows;
+        for (int j = 0; j < nt; ++j) {
+          MoeTile t;
+          t.expert = e;
+          t.row0 = off[e] + j * tile_rows;
+          t.rows = min(tile_rows, cnt[e] - j * tile_rows);
+          t.pad = 0;
+          tiles[tp + j] = t;
+        }
+        if (e == E - 1) *num_tiles = tp + nt;
+      }
+    }
+  }
+  const int i = blockIdx.x * kScatterThreads + tid;
+  if (i < n_pairs) {
+    const int e = topk_ids[i];
+    if (e < 0 || e >= E) {
+      set_error(err, kErrDevBadExpert);
+    } else {
+      const int dst = off[e] + rank[i];
+      sorted_pair[dst] = i;
+      row_of_pair[i] = dst;
+    }
+  }
+}
+
+// ------------------------------------------------------ activation quant ----
+// One CTA per token, 8 columns per thread.  When row_of_pair is given the
+// quantised row is written to each of the token's K sorted rows; otherwise to
+// row t.
+__global__ void act_quant_scatter_kernel(const __nv_bfloat16* __restrict__ x,
+                                         const int* __restrict__ row_of_pair, int H, int K,
+                                         uint8_t* __restrict__ xq, float* __restrict__ xs) {
+  const int t = blockIdx.x, tid = threadIdx.x;
+  const uint4 raw = *reinterpret_cast<const uint4*>(x + static_cast<size_t>(t) * H + tid * 8);
+  const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
+  float f[8];
+  float amax = 0.f;
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const float2 p = __bfloat1622float2(h2[j]);
+    f[2 * j] = p.x;
+    f[2 * j + 1] = p.y;
+    amax = fmaxf(amax, fmaxf(fabsf(p.x), fabsf(p.y)));
+  }
+#pragma unroll
+  for (int o = 8; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+  const float s = amax > 0.f ? amax / 448.f : 1.f;
+  uint32_t lo = 0, hi = 0;
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    lo |= static_cast<uint32_t>(to_e4m3(f[j] / s)) << (8 * j);
+    hi |= static_cast<uint32_t>(to_e4m3(f[4 + j] / s)) << (8 * j);
+  }
+  const int groups = H / 128;
+  const int reps = row_of_pair ? K : 1;
+  for (int k = 0; k < reps; ++k) {
+    const int row = row_of_pair ? row_of_pair[static_cast<size_t>(t) * K + k] : t;
+    *reinterpret_cast<uint2*>(xq + static_cast<size_t>(row) * H + tid * 8) = make_uint2(lo, hi);
+    if ((tid & 15) == 0) xs[static_cast<size_t>(row) * groups + (tid >> 4)] = s;
+  }
+}
+
+// ------------------------------------------------------------- combine ------
+__global__ void moe_combine_kernel(const __nv_bfloat16* __restrict__ y,
+                                   const int* __restrict__ row_of_pair,
+                                   const float* __restrict__ topk_w, int H, int K,
+                                   __nv_bfloat16* __restrict__ out) {
+  const int t = blockIdx.x, tid = threadIdx.x;
+  float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+  for (int k = 0; k < K; ++k) {
+    const int row = row_of_pair[static_cast<size_t>(t) * K + k];
+    const float w = topk_w[static_cast<size_t>(t) * K + k];
+    const uint4 raw = *reinterpret_cast<const uint4*>(y + static_cast<size_t>(row) * H + tid * 8);
+    const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float2 p = __bfloat1622float2(h2[j]);
+      acc[2 * j] += w * p.x;
+      acc[2 * j + 1] += w * p.y;
+    }
+  }
+  uint4 o;
+  __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+  for (int j = 0; j < 4; ++j) o2[j] = __floats2bfloat162_rn(acc[2 * j], acc[2 * j + 1]);
+  *reinterpret_cast<uint4*>(out + static_cast<size_t>(t) * H + tid * 8) = o;
+}
+
+}  // namespace b200
+
+using namespace b200;
+
+extern "C" int b200_moe_route(const float* logits, int num_tokens, int num_experts, int top_k,
+                              int renormalize, int32_t* topk_ids, float* topk_weights,
+                              void* stream) {
+  B200_REQUIRE(logits && topk_ids && topk_weights, "moe_route: null pointer");
+  B200_REQUIRE(num_tokens >= 0, "moe_route: negative token count");
+  B200_REQUIRE(num_experts > 0 && num_experts <= 32 * kRouteMaxPerLane,
+               "moe_route: num_experts %d outside [1, %d]", num_experts, 32 * kRouteMaxPerLane);
+  B200_REQUIRE(top_k > 0 && top_k <= 32 && top_k <= num_experts,
+               "moe_route: top_k %d outside [1, min(32, num_experts)]", top_k);
+  int rc = check_device(nullptr);
+  if (rc) return rc;
+  if (num_tokens == 0) return 0;
+  const int blocks = (num_tokens + kRouteWarps - 1) / kRouteWarps;
+  moe_route_kernel<<<blocks, kRouteWarps * 32, 0, as_stream(stream)>>>(
+      logits, num_tokens, num_experts, top_k, renormalize, topk_ids, topk_weights);
+  B200_CUDA(cudaGetLastError());
+  return 0;
+}
+
+// Workspace layout: [status word, 256 B][counts: E ints][rank: T*K ints]
+extern "C" size_t b200_moe_permute_workspace_bytes(int num_tokens, int num_experts, int top_k) {
+  if (num_tokens < 0 || num_experts <= 0 || top_k <= 0) return 256;
+  size_t off = 256;
+  off += (static_cast<size_t>(num_experts) * 4 + 255) & ~size_t(255);
+  off += (static_cast<size_t>(num_tokens) * top_k * 4 + 255) & ~size_t(255);
+  return off;
+}
+
+extern "C" int b200_moe_max_tiles(int num_tokens, int num_experts, int top_k) {
+  if (num_tokens < 0 || num_experts <= 0 || top_k <= 0) return 0;
+  return (num_tokens * top_k + 127) / 128 + num_experts;
+}
+
+extern "C" int b200_moe_permute(const int32_t* topk_ids, int num_tokens, int num_experts, int top_k,
+                                int32_t* sorted_pair_ids, int32_t* row_of_pair,
+                                int32_t* expert_offsets, void* tiles, int32_t* num_tiles,
+                                void* workspace, size_t workspace_bytes, void* stream) {
+  B200_REQUIRE(topk_ids && sorted_pair_ids && row_of_pair && expert_offsets && workspace,
+               "moe_permute: null pointer");
+  B200_REQUIRE((tiles == nullptr) == (num_tiles == nullptr),
+               "moe_permute: tiles and num_tiles must be given together");
+  B200_REQUIRE(num_tokens >= 0 && num_experts > 0 && num_experts <= 1024 && top_k > 0,
+               "moe_permute: bad dimensions T=%d E=%d K=%d", num_tokens, num_experts, top_k);
+  const size_t need = b200_moe_permute_workspace_bytes(num_tokens, num_experts, top_k);
+  if (workspace_bytes < need) {
+    set_detail("moe_permute: workspace %zu < required %zu", workspace_bytes, need);
+    return -kErrWorkspace;
+  }
+  int rc = check_device(nullptr);
+  if (rc) return rc;
+  cudaStream_t st = as_stream(stream);
+  uint8_t* p = static_cast<uint8_t*>(workspace);
+  int* err = reinterpret_cast<int*>(p);
+  int* counts = reinterpret_cast<int*>(p + 256);
+  int* rank = reinterpret_cast<int*>(p + 256 + ((static_cast<size_t>(num_experts) * 4 + 255) & ~size_t(255)));
+  const int n_pairs = num_tokens * top_k;
+  moe_rank_kernel<<<num_experts, kRankThreads, 0, st>>>(topk_ids, n_pairs, rank, counts);
+  B200_CUDA(cudaGetLastError());
+  const int blocks = n_pairs > 0 ? (n_pairs + kScatterThreads - 1) / kScatterThreads : 1;
+  moe_scatter_kernel<<<blocks, kScatterThreads, (2 * num_experts + 1) * sizeof(int), st>>>(
+      topk_ids, rank, counts, n_pairs, num_experts, 128, sorted_pair_ids, row_of_pair,
+      expert_offsets, static_cast<MoeTile*>(tiles), num_tiles, err);
+  B200_CUDA(cudaGetLastError());
+  return 0;
+}
+
+extern "C" int b200_act_quant_fp8(const void* x, const int32_t* row_of_pair, int num_tokens,
+                                  int hidden, int top_k, void* xq, float* x_scale, void* stream) {
+  B200_REQUIRE(x && xq && x_scale, "act_quant_fp8: null pointer");
+  B200_REQUIRE(num_tokens >= 0 && hidden > 0 && hidden % 256 == 0 && hidden <= 8192,
+               "act_quant_fp8: hidden %d must be a multiple of 256 and <= 8192", hidden);
+  B200_REQUIRE(row_of_pair == nullptr || top_k > 0, "act_quant_fp8: top_k must be positive");
+  B200_REQUIRE((reinterpret_cast<uintptr_t>(x) & 15) == 0 && (reinterpret_cast<uintptr_t>(xq) & 7) == 0,
+               "act_quant_fp8: x must be 16-byte and xq 8-byte aligned");
+  int rc = check_device(nullptr);
+  if (rc) return rc;
+  if (num_tokens == 0) return 0;
+  act_quant_scatter_kernel<<<num_tokens, hidden / 8, 0, as_stream(stream)>>>(
+      static_cast<const __nv_bfloat16*>(x), row_of_pair, hidden, top_k, static_cast<uint8_t*>(xq),
+      x_scale);
+  B200_CUDA(cudaGetLastError());
+  return 0;
+}
+
+extern "C" int b200_moe_combine(const void* y_sorted, const int32_t* row_of_pair,
+                                const float* topk_weights, int num_tokens, int hidden, int top_k,
+                                void* out, void* stream) {
+  B200_REQUIRE(y_sorted && row_of_pair && topk_weights && out, "moe_combine: null pointer");
+  B200_REQUIRE(num_tokens >= 0 && hidden > 0 && hidden % 8 == 0 && hidden <= 8192 && top_k > 0,
+               "moe_combine: bad dimensions T=%d H=%d K=%d", num_tokens, hidden, top_k);
+  B200_REQUIRE((reinterpret_cast<uintptr_t>(y_sorted) & 15) == 0 && (reinterpret_cast<uintptr_t>(out) & 15) == 0,
+               "moe_combine: buffers must be 16-byte aligned");
+  int rc = check_device(nullptr);
+  if (rc) return rc;
+  if (num_tokens == 0) return 0;
+  moe_combine_kernel<<<num_tokens, hidden / 8, 0, as_stream(stream)>>>(
+      static_cast<const __nv_bfloat16*>(y_sorted), row_of_pair, topk_weights, hidden, top_k,
+      static_cast<__nv_bfloat16*>(out));
+  B200_CUDA(cudaGetLastError());
+  return 0;
+}

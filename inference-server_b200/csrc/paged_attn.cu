@@ -1,0 +1,606 @@
+// Paged GQA decode attention for sm_100a.
+//
+// Replaces, for one decode step, what the reference does with dense tensors:
+// gather of the KV pages into a [B,H,S,D] cache
+// (src/inference_server/kv_cache/hf_format.py:21-45), left padding
+// (src/inference_server/backends/torch_backend.py:237-258) and the masked
+// softmax(q K^T * scale) V with GQA head sharing inside the model forward
+// (torch_backend.py:305-322).  Here the pools are read in place, in the
+// reference layout [num_blocks, n_kv_heads, block_size, head_dim]
+// (src/inference_server/kv_cache/block_manager.py:33-49).
+//
+// Main kernel (bf16 pools, page 16, head_dim 64 or 128):
+//   grid  = (batch, max_splits, n_kv_heads), block = 4 consumer warps + 1
+//           producer warp.  One CTA owns `split_tokens` consecutive tokens of one
+//           (sequence, kv head).
+//   load  = the producer warp looks page ids up in the block table and issues
+//           one TMA box (16 rows x 128 bytes, 128-byte swizzle) per page half
+//           for K and for V into a 3-stage ring of 64-token stages; stage
+//           hand-over is by mbarrier (full: transaction bytes, empty: 4 warps).
+//   math  = consumer warp w owns page w of every stage: S = Q K^T with
+//           mma.sync m16n8k16 (rows = the <=16 query heads of the kv group),
+//           online softmax in fp32 with quad shuffles, O += P V.
+//   out   = the 4 warps merge through shared memory and write one fp32 partial
+//           (o, m, l) per (sequence, q head, split); a second kernel folds the
+//           splits in fixed order and writes bf16.
+// The kernel is HBM-bound: per token and kv head it reads 2*D*2 bytes once.
+//
+// Generic kernel: any head_dim <= 256, any page size, fp32 or bf16 pools, no
+// split, fp32 arithmetic throughout.  It serves shapes the main kernel does not
+// (the tiny fp32 parity model) and is not tuned.
+
+#include "common.cuh"
+#include "host.h"
+
+namespace b200 {
+
+constexpr int kPage = 16;         // tokens per page in the main kernel
+constexpr int kStagePages = 4;    // pages per pipeline stage
+constexpr int kStages = 3;        // pipeline depth
+constexpr int kConsumerWarps = 4;
+constexpr int kAttnThreads = (kConsumerWarps + 1) * 32;
+constexpr int kBoxBytes = kPage * 128;  // one TMA box: 16 rows x 128 bytes
+
+template <int D>
+struct AttnCfg {
+  static constexpr int kHalves = D / 64;                       // 128-byte column halves per row
+  static constexpr int kPageBytes = 2 * kHalves * kBoxBytes;   // K then V
+  static constexpr int kStageBytes = kStagePages * kPageBytes;
+  static constexpr int kRingBytes = kStages * kStageBytes;
+  static constexpr int kORow = D + 8;                          // padded fp32 row of the merge buffer
+  static constexpr int kSmemBytes = kRingBytes + 1024 /* alignment slack */ + 64 /* barriers */ + 512 /* m, l */;
+  static_assert(kConsumerWarps * 16 * kORow * 4 <= kRingBytes, "merge buffer must fit in the ring");
+};
+
+template <int D>
+__global__ void __launch_bounds__(kAttnThreads, 2)
+paged_attn_decode_kernel(const __grid_constant__ CUtensorMap k_map,
+                         const __grid_constant__ CUtensorMap v_map,
+                         const __nv_bfloat16* __restrict__ q,
+                         const int* __restrict__ block_table,
+                         const int* __restrict__ ctx_lens,
+                         float* __restrict__ part_o, float2* __restrict__ part_ml,
+                         int* __restrict__ err, int num_q_heads, int num_kv_heads,
+                         int num_blocks, int max_pages, int split_tokens, int max_splits,
+                         float scale_log2) {
+#ifdef B200_DEVICE_OK
+  using Cfg = AttnCfg<D>;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t ring = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* ring_ptr = smem_raw + (ring - smem_u32(smem_raw));
+  const uint32_t bars = ring + Cfg::kRingBytes;  // full[kStages], empty[kStages]
+  float* ml_sm = reinterpret_cast<float*>(ring_ptr + Cfg::kRingBytes + 64);  // [4 warps][16 rows][2]
+
+  const int b = blockIdx.x, split = blockIdx.y, kvh = blockIdx.z;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int group = num_q_heads / num_kv_heads;
+
+  int L = ctx_lens[b];
+  if (L < 0 || L > max_pages * kPage) {
+    if (threadIdx.x == 0) set_error(err, kErrDevBadCtxLen);
+    L = L < 0 ? 0 : max_pages * kPage;
+  }
+  const int start = split * split_tokens;
+  if (start >= L) return;  // uniform for the whole CTA
+  const int end = min(L, start + split_tokens);
+  const int npages = (end - start + kPage - 1) / kPage;
+  const int nstages = (npages + kStagePages - 1) / kStagePages;
+  const int first_page = start / kPage;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(bars + 8 * s, 1);
+      mbar_init(bars + 8 * (kStages + s), kConsumerWarps);
+    }
+    fence_mbar_init();
+    fence_proxy_async();
+  }
+  __syncthreads();
+
+  if (warp == kConsumerWarps) {
+    // ------------------------------------------------------------ producer --
+    if (lane == 0) {
+      tma_prefetch_desc(&k_map);
+      tma_prefetch_desc(&v_map);
+    }
+    const int* table_row = block_table + static_cast<size_t>(b) * max_pages + first_page;
+    // lane -> (page, K or V, column half)
+    const int lp = lane / (2 * Cfg::kHalves);
+    const int lkv = (lane / Cfg::kHalves) & 1;
+    const int lh = lane % Cfg::kHalves;
+    for (int i = 0; i < nstages; ++i) {
+      const int slot = i % kStages;
+      const uint32_t phase = (i / kStages) & 1;
+      const int pages = min(kStagePages, npages - i * kStagePages);
+      int id = 0;
+      if (lp < pages && lane < kStagePages * 2 * Cfg::kHalves) {
+        id = table_row[i * kStagePages + lp];
+        if (id < 0 || id >= num_blocks) {
+          set_error(err, kErrDevBadBlockId);
+          id = 0;
+        }
+      }
+      if (!mbar_wait(bars + 8 * (kStages + slot), phase ^ 1, err)) break;
+      if (lane == 0) mbar_arrive_expect_tx(bars + 8 * slot, pages * Cfg::kPageBytes);
+      __syncwarp();
+      if (lp < pages && lane < kStagePages * 2 * Cfg::kHalves) {
+        const uint32_t dst = ring + slot * Cfg::kStageBytes + lp * Cfg::kPageBytes +
+                             (lkv * Cfg::kHalves + lh) * kBoxBytes;
+        const int y = (id * num_kv_heads + kvh) * kPage;
+        tma_load_2d(dst, lkv ? &v_map : &k_map, bars + 8 * slot, lh * 64, y);
+      }
+    }
+    return;
+  }
+
+  // --------------------------------------------------------------- consumers --
+  const int gq = lane >> 2;  // fragment row (query head inside the kv group)
+  const int tq = lane & 3;
+  const bool hi_rows = group > 8;
+
+  // Q fragments for every 16-wide slice of head_dim (A operand, rows = heads).
+  uint32_t qa[D / 16][4];
+  {
+    const __nv_bfloat16* qb = q + (static_cast<size_t>(b) * num_q_heads + kvh * group) * D;
+#pragma unroll
+    for (int ks = 0; ks < D / 16; ++ks) {
+      const int d0 = ks * 16 + 2 * tq;
+      const uint32_t* r0 = reinterpret_cast<const uint32_t*>(qb + static_cast<size_t>(gq) * D + d0);
+      const uint32_t* r1 =
+          reinterpret_cast<const uint32_t*>(qb + static_cast<size_t>(gq + 8) * D + d0);
+      qa[ks][0] = gq < group ? __ldg(r0) : 0u;
+      qa[ks][1] = gq + 8 < group ? __ldg(r1) : 0u;
+      qa[ks][2] = gq < group ? __ldg(r0 + 4) : 0u;
+      qa[ks][3] = gq + 8 < group ? __ldg(r1 + 4) : 0u;
+    }
+  }
+
+  float o[D / 8][4];
+#pragma unroll
+  for (int n = 0; n < D / 8; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
+  float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
+
+  // ldmatrix lane roles
+  const int lj = lane >> 3, lr = lane & 7;
+  const int k_tok = (lj >> 1) * 8 + lr;  // K: matrices 0,1 -> tokens 0-7; 2,3 -> tokens 8-15
+  const int k_sub = lj & 1;              //    matrices 0,2 -> low 8 of the k-slice; 1,3 -> high 8
+  const int v_tok = (lj & 1) * 8 + lr;   // V: matrices 0,2 -> tokens 0-7; 1,3 -> tokens 8-15
+  const int v_sub = lj >> 1;             //    matrices 0,1 -> first n-tile; 2,3 -> second n-tile
+
+  bool alive = true;
+  for (int i = 0; i < nstages && alive; ++i) {
+    const int slot = i % kStages;
+    const uint32_t phase = (i / kStages) & 1;
+    alive = mbar_wait(bars + 8 * slot, phase, err);
+    const int page = i * kStagePages + warp;
+    if (alive && page < npages) {
+      const uint32_t kbase = ring + slot * Cfg::kStageBytes + warp * Cfg::kPageBytes;
+      const uint32_t vbase = kbase + Cfg::kHalves * kBoxBytes;
+
+      float s0[4] = {0.f, 0.f, 0.f, 0.f}, s1[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+      for (int ks = 0; ks < D / 16; ++ks) {
+        const int cidx = ks * 2 + k_sub;
+        uint32_t b00, b01, b10, b11;
+        ldmatrix_x4(kbase + (cidx >> 3) * kBoxBytes + swz128(k_tok, cidx & 7), b00, b01, b10, b11);
+        mma_bf16_16816(s0, qa[ks], b00, b01);
+        mma_bf16_16816(s1, qa[ks], b10, b11);
+      }
+
+      const int tok0 = start + page * kPage + 2 * tq;  // token of s0[0]; s0[1] is +1, s1[*] is +8
+      if (start + page * kPage + kPage > L) {
+        if (tok0 >= L) s0[0] = s0[2] = -INFINITY;
+        if (tok0 + 1 >= L) s0[1] = s0[3] = -INFINITY;
+        if (tok0 + 8 >= L) s1[0] = s1[2] = -INFINITY;
+        if (tok0 + 9 >= L) s1[1] = s1[3] = -INFINITY;
+      }
+
+      // online softmax, log2 domain; rows gq (index 0,1) and gq + 8 (index 2,3)
+      float mx0 = fmaxf(fmaxf(s0[0], s0[1]), fmaxf(s1[0], s1[1]));
+      mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
+      mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+      const float mn0 = fmaxf(m0, mx0 * scale_log2);
+      const float a0 = exp2f(m0 - mn0);
+      m0 = mn0;
+      const float p00 = exp2f(s0[0] * scale_log2 - mn0), p01 = exp2f(s0[1] * scale_log2 - mn0);
+      const float p10 = exp2f(s1[0] * scale_log2 - mn0), p11 = exp2f(s1[1] * scale_log2 - mn0);
+      l0 = l0 * a0 + (p00 + p01) + (p10 + p11);
+      float a1 = 1.f, p02 = 0.f, p03 = 0.f, p12 = 0.f, p13 = 0.f;
+      if (hi_rows) {
+        float mx1 = fmaxf(fmaxf(s0[2], s0[3]), fmaxf(s1[2], s1[3]));
+        mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
+        mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+        const float mn1 = fmaxf(m1, mx1 * scale_log2);
+        a1 = exp2f(m1 - mn1);
+        m1 = mn1;
+        p02 = exp2f(s0[2] * scale_log2 - mn1);
+        p03 = exp2f(s0[3] * scale_log2 - mn1);
+        p12 = exp2f(s1[2] * scale_log2 - mn1);
+        p13 = exp2f(s1[3] * scale_log2 - mn1);
+        l1 = l1 * a1 + (p02 + p03) + (p12 + p13);
+      }
+      uint32_t pa[4];
+      pa[0] = pack_bf16x2(p00, p01);
+      pa[1] = pack_bf16x2(p02, p03);
+      pa[2] = pack_bf16x2(p10, p11);
+      pa[3] = pack_bf16x2(p12, p13);
+
+#pragma unroll
+      for (int np = 0; np < D / 16; ++np) {
+        o[2 * np][0] *= a0;
+        o[2 * np][1] *= a0;
+        o[2 * np + 1][0] *= a0;
+        o[2 * np + 1][1] *= a0;
+        if (hi_rows) {
+          o[2 * np][2] *= a1;
+          o[2 * np][3] *= a1;
+          o[2 * np + 1][2] *= a1;
+          o[2 * np + 1][3] *= a1;
+        }
+        const int cidx = np * 2 + v_sub;
+        uint32_t v0, v1, v2, v3;
+        ldmatrix_x4_trans(vbase + (cidx >> 3) * kBoxBytes + swz128(v_tok, cidx & 7), v0, v1, v2, v3);
+        mma_bf16_16816(o[2 * np], pa, v0, v1);
+        mma_bf16_16816(o[2 * np + 1], pa, v2, v3);
+      }
+    }
+    __syncwarp();
+    if (lane == 0) mbar_arrive(bars + 8 * (kStages + slot));
+  }
+
+  l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
+  l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
+  l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
+  l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+
+  // Every consumer warp has waited on every stage, so the ring is idle and can
+  // be reused as the merge buffer once all four warps are here.
+  asm volatile("bar.sync 1, %0;" ::"r"(kConsumerWarps * 32) : "memory");
+  float* o_sm = reinterpret_cast<float*>(ring_ptr);  // [warp][16][kORow]
+  {
+    float* ow = o_sm + (warp * 16) * Cfg::kORow;
+#pragma unroll
+    for (int n = 0; n < D / 8; ++n) {
+      const int d = n * 8 + 2 * tq;
+      if (gq < group) *reinterpret_cast<float2*>(ow + gq * Cfg::kORow + d) = make_float2(o[n][0], o[n][1]);
+      if (gq + 8 < group)
+        *reinterpret_cast<float2*>(ow + (gq + 8) * Cfg::kORow + d) = make_float2(o[n][2], o[n][3]);
+    }
+    if (tq == 0) {
+      ml_sm[(warp * 16 + gq) * 2 + 0] = m0;
+      ml_sm[(warp * 16 + gq) * 2 + 1] = l0;
+      ml_sm[(warp * 16 + gq + 8) * 2 + 0] = hi_rows ? m1 : -INFINITY;
+      ml_sm[(warp * 16 + gq + 8) * 2 + 1] = hi_rows ? l1 : 0.f;
+    }
+  }
+  asm volatile("bar.sync 1, %0;" ::"r"(kConsumerWarps * 32) : "memory");
+
+  for (int idx = threadIdx.x; idx < group * D; idx += kConsumerWarps * 32) {
+    const int g = idx / D, d = idx % D;
+    float mw[kConsumerWarps], mmax = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < kConsumerWarps; ++w) {
+      mw[w] = ml_sm[(w * 16 + g) * 2];
+      mmax = fmaxf(mmax, mw[w]);
+    }
+    float acc = 0.f, lsum = 0.f;
+#pragma unroll
+    for (int w = 0; w < kConsumerWarps; ++w) {
+      const float wgt = mw[w] == -INFINITY ? 0.f : exp2f(mw[w] - mmax);
+      acc += wgt * o_sm[(w * 16 + g) * Cfg::kORow + d];
+      lsum += wgt * ml_sm[(w * 16 + g) * 2 + 1];
+    }
+    const size_t row = (static_cast<size_t>(b) * num_q_heads + kvh * group + g) * max_splits + split;
+    part_o[row * D + d] = acc;
+    if (d == 0) part_ml[row] = make_float2(mmax, lsum);
+  }
+#endif
+}
+
+// Folds the per-split partials of one (sequence, q head) in split order.
+__global__ void paged_attn_reduce_kernel(const float* __restrict__ part_o,
+                                         const float2* __restrict__ part_ml,
+                                         const int* __restrict__ ctx_lens,
+                                         __nv_bfloat16* __restrict__ out, int num_q_heads, int D,
+                                         int max_splits, int split_tokens, int max_ctx) {
+  const int h = blockIdx.x, b = blockIdx.y, d = threadIdx.x;
+  int L = ctx_lens[b];
+  L = L < 0 ? 0 : (L > max_ctx ? max_ctx : L);
+  const int n = (L + split_tokens - 1) / split_tokens;
+  const size_t row = (static_cast<size_t>(b) * num_q_heads + h) * max_splits;
+  float mmax = -INFINITY;
+  for (int s = 0; s < n; ++s) mmax = fmaxf(mmax, part_ml[row + s].x);
+  float acc = 0.f, den = 0.f;
+  for (int s = 0; s < n; ++s) {
+    const float2 ml = part_ml[row + s];
+    const float w = exp2f(ml.x - mmax);
+    den += w * ml.y;
+    acc += w * part_o[(row + s) * D + d];
+  }
+  out[(static_cast<size_t>(b) * num_q_heads + h) * D + d] = __float2bfloat16(n > 0 ? acc / den : 0.f);
+}
+
+// ------------------------------------------------------------ generic path --
+template <typename T>
+__device__ __forceinline__ float to_f32(T v);
+template <>
+__device__ __forceinline__ float to_f32<float>(float v) { return v; }
+template <>
+__device__ __forceinline__ float to_f32<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+template <typename T>
+__device__ __forceinline__ T from_f32(float v);
+template <>
+__device__ __forceinline__ float from_f32<float>(float v) { return v; }
+template <>
+__device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float v) { return __float2bfloat16(v); }
+
+constexpr int kGenWarps = 4;
+constexpr int kGenMaxPerLane = 8;  // head_dim <= 256
+
+template <typename T>
+__global__ void __launch_bounds__(kGenWarps * 32)
+paged_attn_generic_kernel(const T* __restrict__ q, const T* __restrict__ k_pool,
+                          const T* __restrict__ v_pool, const int* __restrict__ block_table,
+                          const int* __restrict__ ctx_lens, T* __restrict__ out,
+                          int* __restrict__ err, int num_q_heads, int num_kv_heads, int D, int page,
+                          int num_blocks, int max_pages, float scale) {
+  __shared__ float o_sm[kGenWarps][256];
+  __shared__ float m_sm[kGenWarps], l_sm[kGenWarps];
+  const int h = blockIdx.x, b = blockIdx.y;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int kvh = h / (num_q_heads / num_kv_heads);
+  int L = ctx_lens[b];
+  if (L < 0 || L > max_pages * page) {
+    if (threadIdx.x == 0) set_error(err, kErrDevBadCtxLen);
+    L = L < 0 ? 0 : max_pages * page;
+  }
+  float qr[kGenMaxPerLane], acc[kGenMaxPerLane];
+#pragma unroll
+  for (int j = 0; j < kGenMaxPerLane; ++j) {
+    const int d = lane + 32 * j;
+    qr[j] = d < D ? to_f32<T>(q[(static_cast<size_t>(b) * num_q_heads + h) * D + d]) : 0.f;
+    acc[j] = 0.f;
+  }
+  float m = -INFINITY, l = 0.f;
+  for (int tok = warp; tok < L; tok += kGenWarps) {
+    int id = block_table[static_cast<size_t>(b) * max_pages + tok / page];
+    if (id < 0 || id >= num_blocks) {
+      set_error(err, kErrDevBadBlockId);
+      id = 0;
+    }
+    const size_t base = ((static_cast<size_t>(id) * num_kv_heads + kvh) * page + tok % page) * D;
+    float dot = 0.f;
+#pragma unroll
+    for (int j = 0; j < kGenMaxPerLane; ++j) {
+      const int d = lane + 32 * j;
+      if (d < D) dot += qr[j] * to_f32<T>(k_pool[base + d]);
+    }
+    dot = warp_sum(dot) * scale;
+    const float mn = fmaxf(m, dot);
+    const float a = expf(m - mn), p = expf(dot - mn);
+    m = mn;
+    l = l * a + p;
+#pragma unroll
+    for (int j = 0; j < kGenMaxPerLane; ++j) {
+      const int d = lane + 32 * j;
+      if (d < D) acc[j] = acc[j] * a + p * to_f32<T>(v_pool[base + d]);
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < kGenMaxPerLane; ++j) {
+    const int d = lane + 32 * j;
+    if (d < D) o_sm[warp][d] = acc[j];
+  }
+  if (lane == 0) {
+    m_sm[warp] = m;
+    l_sm[warp] = l;
+  }
+  __syncthreads();
+  for (int d = threadIdx.x; d < D; d += blockDim.x) {
+    float mmax = -INFINITY;
+    for (int w = 0; w < kGenWarps; ++w) mmax = fmaxf(mmax, m_sm[w]);
+    float num = 0.f, den = 0.f;
+    for (int w = 0; w < kGenWarps; ++w) {
+      const float wgt = m_sm[w] == -INFINITY ? 0.f : expf(m_sm[w] - mmax);
+      num += wgt * o_sm[w][d];
+      den += wgt * l_sm[w];
+    }
+    out[(static_cast<size_t>(b) * num_q_heads + h) * D + d] = from_f32<T>(den > 0.f ? num / den : 0.f);
+  }
+}
+
+// Writes this step's K and V rows ([B, n_kv_heads, D]) into their page slots:
+// the decode-time counterpart of the reference's prompt-only page write
+// (src/inference_server/kv_cache/cache_manager.py:185-214).
+template <typename T>
+__global__ void kv_append_kernel(const T* __restrict__ k_new, const T* __restrict__ v_new,
+                                 T* __restrict__ k_pool, T* __restrict__ v_pool,
+                                 const int* __restrict__ block_table,
+                                 const int* __restrict__ positions, int* __restrict__ err,
+                                 int num_kv_heads, int D, int page, int num_blocks,
+                                 int max_pages) {
+  const int b = blockIdx.x;
+  const int pos = positions[b];
+  if (pos < 0 || pos >= max_pages * page) {
+    if (threadIdx.x == 0) set_error(err, kErrDevBadCtxLen);
+    return;
+  }
+  const int id = block_table[static_cast<size_t>(b) * max_pages + pos / page];
+  if (id < 0 || id >= num_blocks) {
+    if (threadIdx.x == 0) set_error(err, kErrDevBadBlockId);
+    return;
+  }
+  const int slot = pos % page;
+  for (int i = threadIdx.x; i < num_kv_heads * D; i += blockDim.x) {
+    const int h = i / D, d = i % D;
+    const size_t dst = ((static_cast<size_t>(id) * num_kv_heads + h) * page + slot) * D + d;
+    const size_t src = static_cast<size_t>(b) * num_kv_heads * D + i;
+    k_pool[dst] = k_new[src];
+    v_pool[dst] = v_new[src];
+  }
+}
+
+// ------------------------------------------------------------------ launch --
+struct AttnWorkspace {
+  int* err;
+  float2* ml;
+  float* o;
+  size_t bytes;
+};
+
+static int max_splits_of(int max_pages, int page, int split_tokens) {
+  return (max_pages * page + split_tokens - 1) / split_tokens;
+}
+
+static AttnWorkspace carve(void* ws, int batch, int hq, int D, int max_splits) {
+  AttnWorkspace w;
+  uint8_t* p = static_cast<uint8_t*>(ws);
+  w.err = reinterpret_cast<int*>(p);
+  size_t off = 256;
+  w.ml = reinterpret_cast<float2*>(p + off);
+  off += (static_cast<size_t>(batch) * hq * max_splits * sizeof(float2) + 255) & ~size_t(255);
+  w.o = reinterpret_cast<float*>(p + off);
+  off += static_cast<size_t>(batch) * hq * max_splits * D * sizeof(float);
+  w.bytes = off;
+  return w;
+}
+
+template <int D>
+static int launch_main(const void* q, const void* k_pool, const void* v_pool,
+                       const int* block_table, const int* ctx_lens, void* out,
+                       const AttnWorkspace& w, int batch, int hq, int hkv, int num_blocks,
+                       int max_pages, float scale, int split_tokens, int max_splits,
+                       cudaStream_t stream) {
+  using Cfg = AttnCfg<D>;
+  CUtensorMap kmap, vmap;
+  const uint64_t rows = static_cast<uint64_t>(num_blocks) * hkv * kPage;
+  int rc = get_tensor_map_2d(k_pool, rows, D, 2, kPage, 64, &kmap);
+  if (rc) return rc;
+  rc = get_tensor_map_2d(v_pool, rows, D, 2, kPage, 64, &vmap);
+  if (rc) return rc;
+  static bool attr_done[64] = {false};
+  int dev = 0;
+  B200_CUDA(cudaGetDevice(&dev));
+  if (dev < 64 && !attr_done[dev]) {
+    B200_CUDA(cudaFuncSetAttribute(paged_attn_decode_kernel<D>,
+                                   cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
+    attr_done[dev] = true;
+  }
+  dim3 grid(batch, max_splits, hkv);
+  const float scale_log2 = scale * 1.4426950408889634f;
+  paged_attn_decode_kernel<D><<<grid, kAttnThreads, Cfg::kSmemBytes, stream>>>(
+      kmap, vmap, static_cast<const __nv_bfloat16*>(q), block_table, ctx_lens, w.o, w.ml, w.err, hq,
+      hkv, num_blocks, max_pages, split_tokens, max_splits, scale_log2);
+  B200_CUDA(cudaGetLastError());
+  paged_attn_reduce_kernel<<<dim3(hq, batch), D, 0, stream>>>(
+      w.o, w.ml, ctx_lens, static_cast<__nv_bfloat16*>(out), hq, D, max_splits, split_tokens,
+      max_pages * kPage);
+  B200_CUDA(cudaGetLastError());
+  return 0;
+}
+
+}  // namespace b200
+
+using namespace b200;
+
+extern "C" size_t b200_paged_attn_workspace_bytes(int batch, int num_q_heads, int head_dim,
+                                                  int max_pages_per_seq, int page_size,
+                                                  int split_tokens) {
+  if (batch <= 0 || num_q_heads <= 0 || head_dim <= 0 || max_pages_per_seq <= 0 || page_size <= 0 ||
+      split_tokens <= 0)
+    return 256;
+  const int ms = max_splits_of(max_pages_per_seq, page_size, split_tokens);
+  return carve(nullptr, batch, num_q_heads, head_dim, ms).bytes;
+}
+
+extern "C" int b200_paged_attn_decode(const void* q, const void* k_pool, const void* v_pool,
+                                      const int32_t* block_table, const int32_t* ctx_lens,
+                                      void* out, void* workspace, size_t workspace_bytes, int batch,
+                                      int num_q_heads, int num_kv_heads, int head_dim,
+                                      int page_size, int num_blocks, int max_pages_per_seq,
+                                      float scale, int split_tokens, int dtype, void* stream) {
+  B200_REQUIRE(q && k_pool && v_pool && block_table && ctx_lens && out && workspace,
+               "paged_attn_decode: null pointer");
+  B200_REQUIRE(batch > 0 && num_q_heads > 0 && num_kv_heads > 0 && num_blocks > 0 &&
+                   max_pages_per_seq > 0 && page_size > 0,
+               "paged_attn_decode: non-positive dimension");
+  B200_REQUIRE(num_q_heads % num_kv_heads == 0, "paged_attn_decode: q heads %d not a multiple of kv heads %d",
+               num_q_heads, num_kv_heads);
+  B200_REQUIRE(head_dim > 0 && head_dim <= 256, "paged_attn_decode: head_dim %d outside (0, 256]", head_dim);
+  B200_REQUIRE(dtype == 0 || dtype == 1, "paged_attn_decode: dtype %d is neither 0 (bf16) nor 1 (f32)", dtype);
+  B200_REQUIRE(workspace_bytes >= 256, "paged_attn_decode: workspace smaller than the status word block");
+  int dev = 0;
+  int rc = check_device(&dev);
+  if (rc) return rc;
+  cudaStream_t st = as_stream(stream);
+  const int group = num_q_heads / num_kv_heads;
+  const bool fast = dtype == 0 && page_size == kPage && (head_dim == 64 || head_dim == 128) &&
+                    group <= 16 && split_tokens > 0;
+  if (fast) {
+    B200_REQUIRE(split_tokens % (kPage * kStagePages) == 0,
+                 "paged_attn_decode: split_tokens %d not a multiple of %d", split_tokens,
+                 kPage * kStagePages);
+    B200_REQUIRE((reinterpret_cast<uintptr_t>(k_pool) & 15) == 0 &&
+                     (reinterpret_cast<uintptr_t>(v_pool) & 15) == 0 &&
+                     (reinterpret_cast<uintptr_t>(q) & 3) == 0,
+                 "paged_attn_decode: pools must be 16-byte aligned");
+    const int ms = max_splits_of(max_pages_per_seq, page_size, split_tokens);
+    B200_REQUIRE(ms <= 65535 && num_kv_heads <= 65535, "paged_attn_decode: grid too large");
+    AttnWorkspace w = carve(workspace, batch, num_q_heads, head_dim, ms);
+    if (workspace_bytes < w.bytes) {
+      set_detail("paged_attn_decode: workspace %zu < required %zu", workspace_bytes, w.bytes);
+      return -kErrWorkspace;
+    }
+    if (head_dim == 128)
+      return launch_main<128>(q, k_pool, v_pool, block_table, ctx_lens, out, w, batch, num_q_heads,
+                              num_kv_heads, num_blocks, max_pages_per_seq, scale, split_tokens, ms, st);
+    return launch_main<64>(q, k_pool, v_pool, block_table, ctx_lens, out, w, batch, num_q_heads,
+                           num_kv_heads, num_blocks, max_pages_per_seq, scale, split_tokens, ms, st);
+  }
+  int* err = static_cast<int*>(workspace);
+  dim3 grid(num_q_heads, batch);
+  if (dtype == 0)
+    paged_attn_generic_kernel<__nv_bfloat16><<<grid, kGenWarps * 32, 0, st>>>(
+        static_cast<const __nv_bfloat16*>(q), static_cast<const __nv_bfloat16*>(k_pool),
+        static_cast<const __nv_bfloat16*>(v_pool), block_table, ctx_lens,
+        static_cast<__nv_bfloat16*>(out), err, num_q_heads, num_kv_heads, head_dim, page_size,
+        num_blocks, max_pages_per_seq, scale);
+  else
+    paged_attn_generic_kernel<float><<<grid, kGenWarps * 32, 0, st>>>(
+        static_cast<const float*>(q), static_cast<const float*>(k_pool),
+        static_cast<const float*>(v_pool), block_table, ctx_lens, static_cast<float*>(out), err,
+        num_q_heads, num_kv_heads, head_dim, page_size, num_blocks, max_pages_per_seq, scale);
+  B200_CUDA(cudaGetLastError());
+  return 0;
+}
+
+extern "C" int b200_kv_append(const void* k_new, const void* v_new, void* k_pool, void* v_pool,
+                              const int32_t* block_table, const int32_t* positions,
+                              void* status_word, int batch, int num_kv_heads, int head_dim,
+                              int page_size, int num_blocks, int max_pages_per_seq, int dtype,
+                              void* stream) {
+  B200_REQUIRE(k_new && v_new && k_pool && v_pool && block_table && positions,
+               "kv_append: null pointer");
+  B200_REQUIRE(batch > 0 && num_kv_heads > 0 && head_dim > 0 && page_size > 0 && num_blocks > 0 &&
+                   max_pages_per_seq > 0,
+               "kv_append: non-positive dimension");
+  B200_REQUIRE(dtype == 0 || dtype == 1, "kv_append: dtype %d is neither 0 (bf16) nor 1 (f32)", dtype);
+  int rc = check_device(nullptr);
+  if (rc) return rc;
+  cudaStream_t st = as_stream(stream);
+  const int threads = num_kv_heads * head_dim < 256 ? ((num_kv_heads * head_dim + 31) / 32) * 32 : 256;
+  if (dtype == 0)
+    kv_append_kernel<__nv_bfloat16><<<batch, threads, 0, st>>>(
+        static_cast<const __nv_bfloat16*>(k_new), static_cast<const __nv_bfloat16*>(v_new),
+        static_cast<__nv_bfloat16*>(k_pool), static_cast<__nv_bfloat16*>(v_pool), block_table,
+        positions, static_cast<int*>(status_word), num_kv_heads, head_dim, page_size, num_blocks,
+        max_pages_per_seq);
+  else
+    kv_append_kernel<float><<<batch, threads, 0, st>>>(
+        static_cast<const float*>(k_new), static_cast<const float*>(v_new),
+        static_cast<float*>(k_pool), static_cast<float*>(v_pool), block_table, positions,
+        static_cast<int*>(status_word), num_kv_heads, head_dim, page_size, num_blocks,
+        max_pages_per_seq);
+  B200_CUDA(cudaGetLastError());
+  return 0;
+}

@@ -1,0 +1,263 @@
+"""Operator wrappers: torch CUDA tensors in, C-ABI calls out.
+
+Each function checks shapes/dtypes/contiguity, passes raw device pointers and
+the current torch CUDA stream to ``libb200decode.so`` and returns torch tensors.
+Nothing here computes on the host and nothing falls back to torch ops: without
+the library, or off a CUDA device, the calls raise.
+"""
+from __future__ import annotations
+
+import torch
+
+from . import _lib
+from ._lib import check
+
+DTYPE_CODE = {torch.bfloat16: 0, torch.float32: 1}
+
+
+def _ptr(t: torch.Tensor | None):
+    return None if t is None else t.data_ptr()
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _need(t: torch.Tensor, name: str, dtype=None):
+    if not t.is_cuda:
+        raise ValueError(f"{name} must be a CUDA tensor (this path has no CPU implementation)")
+    if not t.is_contiguous():
+        raise ValueError(f"{name} must be contiguous")
+    if dtype is not None and t.dtype != dtype:
+        raise ValueError(f"{name} must be {dtype}, got {t.dtype}")
+
+
+def read_status(status: torch.Tensor, where: str = "device status") -> None:
+    """Synchronise and raise if the device status word at the start of `status` is set."""
+    rc = _lib.load().b200_read_status(status.data_ptr(), _stream())
+    check(rc, where)
+
+
+# ------------------------------------------------------------ paged attention
+
+
+def default_split_tokens(batch: int, num_kv_heads: int, max_ctx: int, num_sms: int = 148) -> int:
+    """Tokens per KV split: large enough to amortise the pipeline fill, small
+    enough that batch * kv_heads * splits covers a few waves of CTAs."""
+    target_ctas = 4 * num_sms
+    per_seq = max(1, target_ctas // max(1, batch * num_kv_heads))
+    split = (max_ctx + per_seq - 1) // per_seq
+    split = ((split + 63) // 64) * 64
+    return int(min(max(split, 256), 2048))
+
+
+def paged_attn_workspace(batch, num_q_heads, head_dim, max_pages, page_size, split_tokens, device):
+    n = _lib.load().b200_paged_attn_workspace_bytes(batch, num_q_heads, head_dim, max_pages, page_size, split_tokens)
+    return torch.zeros(n, dtype=torch.uint8, device=device)
+
+
+def paged_attn_decode(
+    q: torch.Tensor,
+    k_pool: torch.Tensor,
+    v_pool: torch.Tensor,
+    block_table: torch.Tensor,
+    ctx_lens: torch.Tensor,
+    scale: float,
+    split_tokens: int | None = None,
+    workspace: torch.Tensor | None = None,
+    out: torch.Tensor | None = None,
+) -> torch.Tensor:
+    """softmax(q K^T * scale) V over the pages listed in `block_table`.
+
+    q [B, Hq, D]; pools [num_blocks, Hkv, page, D] (the reference BlockManager
+    layout); block_table [B, max_pages] int32; ctx_lens [B] int32.
+    """
+    _need(q, "q")
+    _need(k_pool, "k_pool", q.dtype)
+    _need(v_pool, "v_pool", q.dtype)
+    _need(block_table, "block_table", torch.int32)
+    _need(ctx_lens, "ctx_lens", torch.int32)
+    if q.dtype not in DTYPE_CODE:
+        raise ValueError(f"unsupported dtype {q.dtype}")
+    B, Hq, D = q.shape
+    nb, Hkv, page, D2 = k_pool.shape
+    if D2 != D or v_pool.shape != k_pool.shape:
+        raise ValueError("pool shape does not match q / each other")
+    if block_table.shape[0] != B or ctx_lens.shape[0] != B:
+        raise ValueError("block_table / ctx_lens batch mismatch")
+    max_pages = block_table.shape[1]
+    if split_tokens is None:
+        split_tokens = default_split_tokens(B, Hkv, max_pages * page)
+    if workspace is None:
+        workspace = paged_attn_workspace(B, Hq, D, max_pages, page, split_tokens, q.device)
+    if out is None:
+        out = torch.empty_like(q)
+    rc = _lib.load().b200_paged_attn_decode(
+        _ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(block_table), _ptr(ctx_lens), _ptr(out),
+        _ptr(workspace), workspace.numel(), B, Hq, Hkv, D, page, nb, max_pages, float(scale),
+        int(split_tokens), DTYPE_CODE[q.dtype], _stream(),
+    )
+    check(rc, "b200_paged_attn_decode")
+    return out
+
+
+def kv_append(k_new, v_new, k_pool, v_pool, block_table, positions, status: torch.Tensor | None = None):
+    """Write this step's K/V rows [B, Hkv, D] into page slot `positions[b]` of each row."""
+    _need(k_new, "k_new", k_pool.dtype)
+    _need(v_new, "v_new", k_pool.dtype)
+    _need(k_pool, "k_pool")
+    _need(v_pool, "v_pool", k_pool.dtype)
+    _need(block_table, "block_table", torch.int32)
+    _need(positions, "positions", torch.int32)
+    B, Hkv, D = k_new.shape
+    nb, Hkv2, page, D2 = k_pool.shape
+    if (Hkv2, D2) != (Hkv, D):
+        raise ValueError("k_new does not match the pool layout")
+    rc = _lib.load().b200_kv_append(
+        _ptr(k_new), _ptr(v_new), _ptr(k_pool), _ptr(v_pool), _ptr(block_table), _ptr(positions),
+        _ptr(status), B, Hkv, D, page, nb, block_table.shape[1], DTYPE_CODE[k_pool.dtype], _stream(),
+    )
+    check(rc, "b200_kv_append")
+
+
+# ------------------------------------------------------------------------ MoE
+
+
+def moe_route(logits: torch.Tensor, top_k: int, renormalize: bool = True):
+    """fp32 softmax top-k routing. Returns (ids [T,K] int32, weights [T,K] fp32)."""
+    _need(logits, "logits", torch.float32)
+    T, E = logits.shape
+    ids = torch.empty(T, top_k, dtype=torch.int32, device=logits.device)
+    w = torch.empty(T, top_k, dtype=torch.float32, device=logits.device)
+    rc = _lib.load().b200_moe_route(_ptr(logits), T, E, top_k, int(renormalize), _ptr(ids), _ptr(w), _stream())
+    check(rc, "b200_moe_route")
+    return ids, w
+
+
+class Permutation:
+    """Result of moe_permute: the stable sort of (token, slot) pairs by expert."""
+
+    __slots__ = ("sorted_pair_ids", "row_of_pair", "expert_offsets", "tiles", "num_tiles", "workspace")
+
+
+def moe_permute(topk_ids: torch.Tensor, num_experts: int) -> Permutation:
+    _need(topk_ids, "topk_ids", torch.int32)
+    T, K = topk_ids.shape
+    lib = _lib.load()
+    dev = topk_ids.device
+    p = Permutation()
+    p.sorted_pair_ids = torch.empty(T * K, dtype=torch.int32, device=dev)
+    p.row_of_pair = torch.empty(T * K, dtype=torch.int32, device=dev)
+    p.expert_offsets = torch.empty(num_experts + 1, dtype=torch.int32, device=dev)
+    p.tiles = torch.zeros(max(1, lib.b200_moe_max_tiles(T, num_experts, K)), 4, dtype=torch.int32, device=dev)
+    p.num_tiles = torch.zeros(1, dtype=torch.int32, device=dev)
+    p.workspace = torch.zeros(lib.b200_moe_permute_workspace_bytes(T, num_experts, K), dtype=torch.uint8, device=dev)
+    rc = lib.b200_moe_permute(
+        _ptr(topk_ids), T, num_experts, K, _ptr(p.sorted_pair_ids), _ptr(p.row_of_pair),
+        _ptr(p.expert_offsets), _ptr(p.tiles), _ptr(p.num_tiles), _ptr(p.workspace),
+        p.workspace.numel(), _stream(),
+    )
+    check(rc, "b200_moe_permute")
+    return p
+
+
+def act_quant_fp8(x: torch.Tensor, row_of_pair: torch.Tensor | None = None, top_k: int = 1):
+    """Per-row, per-128-column e4m3 quantisation; optionally scattered to sorted rows.
+
+    Returns (xq uint8 [rows, H], scale fp32 [rows, H/128])."""
+    _need(x, "x", torch.bfloat16)
+    T, H = x.shape
+    rows = T if row_of_pair is None else T * top_k
+    xq = torch.empty(rows, H, dtype=torch.uint8, device=x.device)
+    xs = torch.empty(rows, H // 128, dtype=torch.float32, device=x.device)
+    rc = _lib.load().b200_act_quant_fp8(_ptr(x), _ptr(row_of_pair), T, H, top_k, _ptr(xq), _ptr(xs), _stream())
+    check(rc, "b200_act_quant_fp8")
+    return xq, xs
+
+
+def _as_u8(t: torch.Tensor) -> torch.Tensor:
+    return t.view(torch.uint8) if t.dtype != torch.uint8 else t
+
+
+def moe_fp8_gemm_gate_up(xq, x_scale, w13, w13_scale_inv, perm: Permutation, status=None):
+    """h = silu(W13[:I] x) * (W13[I:] x) per sorted row, re-quantised to e4m3."""
+    xq, w13 = _as_u8(xq), _as_u8(w13)
+    _need(xq, "xq", torch.uint8)
+    _need(w13, "w13", torch.uint8)
+    _need(x_scale, "x_scale", torch.float32)
+    _need(w13_scale_inv, "w13_scale_inv", torch.float32)
+    rows, H = xq.shape
+    E, two_i, H2 = w13.shape
+    inter = two_i // 2
+    if H2 != H or tuple(w13_scale_inv.shape) != (E, two_i // 128, H // 128):
+        raise ValueError("w13 / scale shapes do not match")
+    hq = torch.empty(rows, inter, dtype=torch.uint8, device=xq.device)
+    hs = torch.empty(rows, inter // 128, dtype=torch.float32, device=xq.device)
+    rc = _lib.load().b200_moe_fp8_gemm_gate_up(
+        _ptr(xq), _ptr(x_scale), _ptr(w13), _ptr(w13_scale_inv), _ptr(perm.tiles), _ptr(perm.num_tiles),
+        _ptr(hq), _ptr(hs), _ptr(status), rows, E, H, inter, _stream(),
+    )
+    check(rc, "b200_moe_fp8_gemm_gate_up")
+    return hq, hs
+
+
+def moe_fp8_gemm_down(hq, h_scale, w2, w2_scale_inv, perm: Permutation, status=None):
+    """y = W2 h per sorted row, bf16."""
+    hq, w2 = _as_u8(hq), _as_u8(w2)
+    _need(hq, "hq", torch.uint8)
+    _need(w2, "w2", torch.uint8)
+    _need(h_scale, "h_scale", torch.float32)
+    _need(w2_scale_inv, "w2_scale_inv", torch.float32)
+    rows, inter = hq.shape
+    E, H, inter2 = w2.shape
+    if inter2 != inter or tuple(w2_scale_inv.shape) != (E, H // 128, inter // 128):
+        raise ValueError("w2 / scale shapes do not match")
+    y = torch.empty(rows, H, dtype=torch.bfloat16, device=hq.device)
+    rc = _lib.load().b200_moe_fp8_gemm_down(
+        _ptr(hq), _ptr(h_scale), _ptr(w2), _ptr(w2_scale_inv), _ptr(perm.tiles), _ptr(perm.num_tiles),
+        _ptr(y), _ptr(status), rows, E, H, inter, _stream(),
+    )
+    check(rc, "b200_moe_fp8_gemm_down")
+    return y
+
+
+def moe_combine(y_sorted, row_of_pair, topk_weights):
+    _need(y_sorted, "y_sorted", torch.bfloat16)
+    _need(row_of_pair, "row_of_pair", torch.int32)
+    _need(topk_weights, "topk_weights", torch.float32)
+    T, K = topk_weights.shape
+    H = y_sorted.shape[1]
+    out = torch.empty(T, H, dtype=torch.bfloat16, device=y_sorted.device)
+    rc = _lib.load().b200_moe_combine(_ptr(y_sorted), _ptr(row_of_pair), _ptr(topk_weights), T, H, K, _ptr(out), _stream())
+    check(rc, "b200_moe_combine")
+    return out
+
+
+def moe_fp8_workspace(num_tokens, num_experts, top_k, hidden, inter, device):
+    n = _lib.load().b200_moe_fp8_workspace_bytes(num_tokens, num_experts, top_k, hidden, inter)
+    return torch.zeros(n, dtype=torch.uint8, device=device)
+
+
+def moe_fp8_forward(x, router_logits, w13, w13_scale_inv, w2, w2_scale_inv, top_k, renormalize=True,
+                    workspace=None, out=None):
+    """The whole FP8 MoE layer on one stream: route, permute, quantise, two grouped GEMMs, combine."""
+    w13, w2 = _as_u8(w13), _as_u8(w2)
+    _need(x, "x", torch.bfloat16)
+    _need(router_logits, "router_logits", torch.float32)
+    _need(w13, "w13", torch.uint8)
+    _need(w2, "w2", torch.uint8)
+    _need(w13_scale_inv, "w13_scale_inv", torch.float32)
+    _need(w2_scale_inv, "w2_scale_inv", torch.float32)
+    T, H = x.shape
+    E, two_i, _ = w13.shape
+    inter = two_i // 2
+    if workspace is None:
+        workspace = moe_fp8_workspace(T, E, top_k, H, inter, x.device)
+    if out is None:
+        out = torch.empty_like(x)
+    rc = _lib.load().b200_moe_fp8_forward(
+        _ptr(x), _ptr(router_logits), _ptr(w13), _ptr(w13_scale_inv), _ptr(w2), _ptr(w2_scale_inv),
+        _ptr(out), _ptr(workspace), workspace.numel(), T, E, top_k, H, inter, int(renormalize), _stream(),
+    )
+    check(rc, "b200_moe_fp8_forward")
+    return out
