@@ -1,0 +1,287 @@
+"""Paged decode engine: one Qwen3-MoE-shaped decode step on block tables.
+
+This is the model-forward side of the reference's hot entry
+``TorchBackend.decode_step_batched``
+(src/inference_server/backends/torch_backend.py:305-322), rebuilt so that a
+step reads the KV page pools in place instead of a dense left-padded cache:
+
+  per layer   RMSNorm -> fused q/k/v projection -> per-head q/k RMSNorm -> RoPE
+              -> ``b200_kv_append`` (page write) -> ``b200_paged_attn_decode``
+              -> o projection + residual -> RMSNorm -> router projection
+              -> ``b200_moe_fp8_forward`` (+ residual)
+  final       RMSNorm -> lm_head -> argmax
+
+The paged attention and the FP8 MoE layer are this package's CUDA kernels; the
+dense projections are library GEMMs (torch.matmul, bf16) and the small
+element-wise pieces are torch ops.  The whole step is captured once per batch
+size in a CUDA graph; block table, context lengths and input tokens live in
+static device buffers that the graph reads.
+
+Pools use the reference layout [num_blocks, n_kv_heads, 16, head_dim] per layer
+(src/inference_server/kv_cache/block_manager.py:33-49) and can be the very
+tensors a reference ``BlockManager`` allocated.
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass
+
+import torch
+
+from . import ops, quant
+
+PAGE = 16
+
+
+@dataclass(frozen=True)
+class ModelConfig:
+    name: str
+    vocab_size: int
+    hidden: int
+    layers: int
+    q_heads: int
+    kv_heads: int
+    head_dim: int
+    experts: int
+    top_k: int
+    moe_inter: int
+    rope_theta: float = 1e6
+    rms_eps: float = 1e-6
+    norm_topk_prob: bool = True
+
+
+CONFIGS = {
+    # BASELINE config 4: Qwen3-30B-A3B shape
+    "qwen3-30b-a3b": ModelConfig("qwen3-30b-a3b", 151936, 2048, 48, 32, 4, 128, 128, 8, 768),
+    # BASELINE config 5: Qwen3-235B-A22B shape (needs expert parallelism to fit)
+    "qwen3-235b-a22b": ModelConfig("qwen3-235b-a22b", 151936, 4096, 94, 64, 4, 128, 128, 8, 1536),
+    # BASELINE config 1: the tiny parity model
+    "tiny": ModelConfig("tiny", 4096, 512, 2, 8, 2, 64, 16, 4, 256),
+}
+
+
+class LayerWeights:
+    """Weights of one decoder layer, already in their run-time formats."""
+
+    __slots__ = ("ln1", "wqkv", "q_norm", "k_norm", "wo", "ln2", "router", "w13", "w13_scale", "w2", "w2_scale")
+
+
+def rms_norm(x: torch.Tensor, weight: torch.Tensor, eps: float) -> torch.Tensor:
+    """weight * (x / rms(x)) with the statistics in fp32 (the model's RMSNorm)."""
+    xf = x.float()
+    xf = xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps)
+    return weight * xf.to(x.dtype)
+
+
+def rope_tables(head_dim: int, theta: float, max_pos: int, device, dtype):
+    inv = 1.0 / (theta ** (torch.arange(0, head_dim, 2, dtype=torch.float32, device=device) / head_dim))
+    ang = torch.arange(max_pos, dtype=torch.float32, device=device)[:, None] * inv[None, :]
+    emb = torch.cat([ang, ang], dim=-1)
+    return emb.cos().to(dtype), emb.sin().to(dtype)
+
+
+def apply_rope(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> torch.Tensor:
+    """x [..., heads, D]; cos/sin broadcastable [..., 1, D]; rotate-half convention."""
+    half = x.shape[-1] // 2
+    rot = torch.cat([-x[..., half:], x[..., :half]], dim=-1)
+    return x * cos + rot * sin
+
+
+def random_layer(cfg: ModelConfig, device, gen: torch.Generator, std: float = 0.02) -> LayerWeights:
+    """Random-init weights (N(0, std)), experts quantised to e4m3 128x128 blocks on the device."""
+    H, D = cfg.hidden, cfg.head_dim
+    w = LayerWeights()
+    bf = torch.bfloat16
+
+    def rn(*shape):
+        return torch.randn(*shape, device=device, generator=gen, dtype=torch.float32) * std
+
+    w.ln1 = torch.ones(H, device=device, dtype=bf)
+    w.ln2 = torch.ones(H, device=device, dtype=bf)
+    w.q_norm = torch.ones(D, device=device, dtype=bf)
+    w.k_norm = torch.ones(D, device=device, dtype=bf)
+    w.wqkv = rn((cfg.q_heads + 2 * cfg.kv_heads) * D, H).to(bf)
+    w.wo = rn(H, cfg.q_heads * D).to(bf)
+    w.router = rn(cfg.experts, H).to(bf)
+    w.w13, w.w13_scale = quant.quantize_weight_blocks(rn(cfg.experts, 2 * cfg.moe_inter, H))
+    w.w2, w.w2_scale = quant.quantize_weight_blocks(rn(cfg.experts, H, cfg.moe_inter))
+    return w
+
+
+class DecodeEngine:
+    """Owns weights, KV page pools and the per-batch-size CUDA graphs of the decode step."""
+
+    def __init__(self, cfg: ModelConfig, num_blocks: int, max_batch: int, max_pages_per_seq: int,
+                 device: str | torch.device = "cuda", seed: int = 0, layers: list[LayerWeights] | None = None,
+                 embed: torch.Tensor | None = None, lm_head: torch.Tensor | None = None,
+                 final_norm: torch.Tensor | None = None, k_pools=None, v_pools=None, use_graphs: bool = True,
+                 split_tokens: int | None = None):
+        if not torch.cuda.is_available():
+            raise RuntimeError("DecodeEngine needs a CUDA device; this path has no CPU implementation")
+        self.cfg = cfg
+        self.device = torch.device(device)
+        self.max_batch = max_batch
+        self.max_pages = max_pages_per_seq
+        self.num_blocks = num_blocks
+        self.use_graphs = use_graphs
+        bf = torch.bfloat16
+        gen = torch.Generator(device=self.device).manual_seed(seed)
+        self.layers = layers if layers is not None else [random_layer(cfg, self.device, gen) for _ in range(cfg.layers)]
+        std = 0.02
+        self.embed = embed if embed is not None else (
+            torch.randn(cfg.vocab_size, cfg.hidden, device=self.device, generator=gen) * std).to(bf)
+        self.lm_head = lm_head if lm_head is not None else (
+            torch.randn(cfg.vocab_size, cfg.hidden, device=self.device, generator=gen) * std).to(bf)
+        self.final_norm = final_norm if final_norm is not None else torch.ones(cfg.hidden, device=self.device, dtype=bf)
+        shape = (num_blocks, cfg.kv_heads, PAGE, cfg.head_dim)
+        self.k_pools = k_pools if k_pools is not None else [torch.zeros(shape, device=self.device, dtype=bf) for _ in range(cfg.layers)]
+        self.v_pools = v_pools if v_pools is not None else [torch.zeros(shape, device=self.device, dtype=bf) for _ in range(cfg.layers)]
+        self.cos, self.sin = rope_tables(cfg.head_dim, cfg.rope_theta, max_pages_per_seq * PAGE, self.device, bf)
+        self.scale = cfg.head_dim ** -0.5
+        self.split_tokens = split_tokens or ops.default_split_tokens(max_batch, cfg.kv_heads, max_pages_per_seq * PAGE)
+
+        # static step state (read by the captured graphs)
+        self.tokens = torch.zeros(max_batch, dtype=torch.int64, device=self.device)
+        self.ctx_lens = torch.zeros(max_batch, dtype=torch.int32, device=self.device)
+        self.block_table = torch.zeros(max_batch, max_pages_per_seq, dtype=torch.int32, device=self.device)
+        self.next_tokens = torch.zeros(max_batch, dtype=torch.int64, device=self.device)
+        self.attn_ws = ops.paged_attn_workspace(max_batch, cfg.q_heads, cfg.head_dim, max_pages_per_seq, PAGE,
+                                                self.split_tokens, self.device)
+        self.moe_ws = ops.moe_fp8_workspace(max_batch, cfg.experts, cfg.top_k, cfg.hidden, cfg.moe_inter, self.device)
+        self._graphs: dict[int, torch.cuda.CUDAGraph] = {}
+        self.kernel_launches_per_step = cfg.layers * (1 + 2 + 1 + 2 + 1 + 2 + 1)  # append, attn x2, route, permute x2, quant, gemm x2, combine
+
+    # ------------------------------------------------------------------ step
+    def _layer(self, x: torch.Tensor, w: LayerWeights, li: int, B: int, pos: torch.Tensor, new_len: torch.Tensor,
+               table: torch.Tensor) -> torch.Tensor:
+        cfg = self.cfg
+        D, Hq, Hkv = cfg.head_dim, cfg.q_heads, cfg.kv_heads
+        h = rms_norm(x, w.ln1, cfg.rms_eps)
+        qkv = torch.matmul(h, w.wqkv.t()).view(B, Hq + 2 * Hkv, D)
+        q = rms_norm(qkv[:, :Hq], w.q_norm, cfg.rms_eps)
+        k = rms_norm(qkv[:, Hq:Hq + Hkv], w.k_norm, cfg.rms_eps)
+        v = qkv[:, Hq + Hkv:].contiguous()
+        cos = self.cos[pos.long()].unsqueeze(1)
+        sin = self.sin[pos.long()].unsqueeze(1)
+        q = apply_rope(q, cos, sin).contiguous()
+        k = apply_rope(k, cos, sin).contiguous()
+        ops.kv_append(k, v, self.k_pools[li], self.v_pools[li], table, pos, self.attn_ws)
+        attn = ops.paged_attn_decode(q, self.k_pools[li], self.v_pools[li], table, new_len, self.scale,
+                                     self.split_tokens, self.attn_ws)
+        x = x + torch.matmul(attn.view(B, Hq * D), w.wo.t())
+        h = rms_norm(x, w.ln2, cfg.rms_eps)
+        logits = torch.matmul(h, w.router.t()).float()
+        y = ops.moe_fp8_forward(h, logits, w.w13, w.w13_scale, w.w2, w.w2_scale, cfg.top_k, cfg.norm_topk_prob,
+                                self.moe_ws)
+        return x + y
+
+    def _step_eager(self, B: int) -> None:
+        """One decode step over rows [0, B) of the static buffers; advances ctx_lens by one."""
+        tokens = self.tokens[:B]
+        pos = self.ctx_lens[:B]
+        table = self.block_table[:B]
+        new_len = pos + 1
+        x = self.embed[tokens]
+        for li, w in enumerate(self.layers):
+            x = self._layer(x, w, li, B, pos, new_len, table)
+        x = rms_norm(x, self.final_norm, self.cfg.rms_eps)
+        self.last_logits = torch.matmul(x, self.lm_head.t())
+        self.next_tokens[:B] = self.last_logits.argmax(dim=-1)
+        self.ctx_lens[:B] += 1
+
+    def step(self, B: int) -> torch.Tensor:
+        """Run one decode step for the first B rows of the static state; returns next tokens (device)."""
+        if B < 1 or B > self.max_batch:
+            raise ValueError(f"batch {B} outside [1, {self.max_batch}]")
+        if not self.use_graphs:
+            self._step_eager(B)
+            return self.next_tokens[:B]
+        g = self._graphs.get(B)
+        if g is None:
+            saved = self.ctx_lens.clone()
+            stream = torch.cuda.Stream(device=self.device)
+            stream.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(stream):
+                for _ in range(2):  # warm-up: library handles, function attributes, tensor maps
+                    self._step_eager(B)
+            torch.cuda.current_stream().wait_stream(stream)
+            torch.cuda.synchronize()
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                self._step_eager(B)
+            self.ctx_lens.copy_(saved)  # warm-up and capture advanced nothing the caller asked for
+            torch.cuda.synchronize()
+            self._graphs[B] = g
+        g.replay()
+        return self.next_tokens[:B]
+
+    # --------------------------------------------------------------- prefill
+    @torch.no_grad()
+    def prefill(self, token_ids: list[int], block_ids: list[int], cached_tokens: int = 0) -> tuple[int, torch.Tensor]:
+        """Prompt pass for one sequence; writes K/V of tokens [cached_tokens, n) into `block_ids` pages.
+
+        Outside the per-step hot path: attention over the prompt is torch SDPA on
+        the gathered pages; the MoE layers run the same FP8 kernels as decode.
+        Returns (first generated token, last-position logits)."""
+        cfg = self.cfg
+        n = len(token_ids)
+        if n == 0 or cached_tokens >= n:
+            raise ValueError("prefill needs at least one uncached token")
+        if len(block_ids) * PAGE < n:
+            raise ValueError("not enough pages for the prompt")
+        D, Hq, Hkv = cfg.head_dim, cfg.q_heads, cfg.kv_heads
+        new = n - cached_tokens
+        ids = torch.tensor(token_ids[cached_tokens:], device=self.device)
+        pos = torch.arange(cached_tokens, n, device=self.device)
+        bt = torch.tensor(block_ids, device=self.device, dtype=torch.long)
+        page_of = bt[pos // PAGE]
+        slot_of = pos % PAGE
+        x = self.embed[ids]
+        cos, sin = self.cos[pos].unsqueeze(1), self.sin[pos].unsqueeze(1)
+        n_pages = (n + PAGE - 1) // PAGE
+        for li, w in enumerate(self.layers):
+            h = rms_norm(x, w.ln1, cfg.rms_eps)
+            qkv = torch.matmul(h, w.wqkv.t()).view(new, Hq + 2 * Hkv, D)
+            q = apply_rope(rms_norm(qkv[:, :Hq], w.q_norm, cfg.rms_eps), cos, sin)
+            k = apply_rope(rms_norm(qkv[:, Hq:Hq + Hkv], w.k_norm, cfg.rms_eps), cos, sin)
+            v = qkv[:, Hq + Hkv:]
+            self.k_pools[li][page_of, :, slot_of, :] = k
+            self.v_pools[li][page_of, :, slot_of, :] = v
+            kd = self.k_pools[li][bt[:n_pages]].permute(1, 0, 2, 3).reshape(Hkv, n_pages * PAGE, D)[:, :n]
+            vd = self.v_pools[li][bt[:n_pages]].permute(1, 0, 2, 3).reshape(Hkv, n_pages * PAGE, D)[:, :n]
+            rep = Hq // Hkv
+            mask = pos[:, None] >= torch.arange(n, device=self.device)[None, :]
+            o = torch.nn.functional.scaled_dot_product_attention(
+                q.transpose(0, 1).unsqueeze(0), kd.repeat_interleave(rep, 0).unsqueeze(0),
+                vd.repeat_interleave(rep, 0).unsqueeze(0), attn_mask=mask, scale=self.scale)
+            x = x + torch.matmul(o[0].transpose(0, 1).reshape(new, Hq * D), w.wo.t())
+            h = rms_norm(x, w.ln2, cfg.rms_eps)
+            logits = torch.matmul(h, w.router.t()).float()
+            x = x + ops.moe_fp8_forward(h.contiguous(), logits, w.w13, w.w13_scale, w.w2, w.w2_scale, cfg.top_k,
+                                        cfg.norm_topk_prob)
+        x = rms_norm(x[-1:], self.final_norm, cfg.rms_eps)
+        logits = torch.matmul(x, self.lm_head.t())[0]
+        return int(logits.argmax()), logits
+
+    # ------------------------------------------------------------- accounting
+    def weight_bytes_per_step(self, experts_hit_per_layer: float | None = None) -> dict:
+        """Bytes one decode step must stream from HBM, by stream (for the step roofline)."""
+        cfg = self.cfg
+        per_expert = 3 * cfg.hidden * cfg.moe_inter
+        hit = cfg.experts if experts_hit_per_layer is None else experts_hit_per_layer
+        dense = ((cfg.q_heads + 2 * cfg.kv_heads) * cfg.head_dim * cfg.hidden + cfg.hidden * cfg.q_heads * cfg.head_dim
+                 + cfg.experts * cfg.hidden) * 2
+        return {
+            "experts": cfg.layers * hit * per_expert,
+            "dense": cfg.layers * dense,
+            "lm_head": cfg.vocab_size * cfg.hidden * 2,
+            "kv_per_token": cfg.layers * 2 * cfg.kv_heads * cfg.head_dim * 2,
+        }
+
+
+def kv_bytes_per_token_layer(cfg: ModelConfig) -> int:
+    return 2 * cfg.kv_heads * cfg.head_dim * 2
+
+
+def pages_for(tokens: int) -> int:
+    return math.ceil(tokens / PAGE)
