@@ -63,10 +63,10 @@ int b200_read_status(const void* status_word, void* stream);
  *   out          [batch, num_q_heads, head_dim], same dtype as q
  *   workspace    b200_paged_attn_workspace_bytes(...) bytes; starts with the
  *                status word
- *   split_tokens tokens per split of the KV length, a multiple of 64
+ *   split_tokens tokens per split of the KV length, a multiple of 16
  *
  * bf16 pools with page_size 16, head_dim 64 or 128 and at most 16 q heads per
- * kv head take the TMA split-K kernel; anything else (fp32, other pages or head
+ * kv head and 1, 2, 4 or 8 kv heads take the TMA split-K kernel; anything else (fp32, other pages or head
  * sizes up to 256) takes a plain fp32-arithmetic kernel without a split.
  */
 size_t b200_paged_attn_workspace_bytes(int batch, int num_q_heads, int head_dim,

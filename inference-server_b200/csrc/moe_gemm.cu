@@ -8,7 +8,9 @@
 //     C[r, n] = sum_kb  a_scale[r, kb] * w_scale[n / 128, kb]
 //                       * sum_{k in kb} A[r, k] * W[n, k]
 //
-// One persistent CTA per SM, 10 warps:
+// One persistent CTA per SM, 3 warpgroups (12 warps).  Warpgroup 0 holds the two
+// single-thread roles and gives most of its registers back (setmaxnreg) so that
+// the 8 promotion warps can hold 128 accumulators plus two TMEM loads in flight:
 //   warp 0      TMA producer: per 128-wide K block one A box (128 sorted rows x
 //               128 B) and two W boxes (128 rows x 128 B each) into a 4-stage
 //               ring, 128-byte swizzle, completion by mbarrier bytes.
@@ -16,7 +18,7 @@
 //               kind::f8f6f4) per K block into one of two 256-column TMEM
 //               accumulators and commits to the stage-empty and
 //               accumulator-full barriers.
-//   warps 2-9   promotion + epilogue: each thread owns one row and 128 of the 256
+//   warps 4-11  promotion + epilogue: each thread owns one row and 128 of the 256
 //               columns; per K block it reads the raw block sum from TMEM
 //               (tcgen05.ld 32x32b), multiplies by the two scales and adds into
 //               fp32 registers, then frees the accumulator.  fp32 block scales
@@ -27,6 +29,7 @@
 //               so SwiGLU and the per-row amax over the 128 outputs stay inside
 //               two threads; h is written as e4m3 + scale, ready for the down GEMM.
 //   down        tile columns = 256 rows of W2; writes bf16 rows in sorted order.
+// SwiGLU is evaluated in fp32 on the fp32 accumulators and quantised directly.
 // A tile is 128 consecutive sorted rows of one expert (see MoeTile); rows past
 // the expert's count are computed on whatever the box holds and never stored.
 
@@ -43,12 +46,24 @@ constexpr int kABytes = kTileM * kBlockK;
 constexpr int kBBytes = kTileN * kBlockK;
 constexpr int kStageBytesG = kABytes + kBBytes;
 constexpr int kEpiWarps = 8;
-constexpr int kGemmThreads = (2 + kEpiWarps) * 32;
+constexpr int kGemmThreads = (4 + kEpiWarps) * 32;  // warps 2, 3 idle: roles are per warpgroup
 constexpr int kTmemCols = 512;
 constexpr int kGemmSmem = kGemmStages * kStageBytesG + 1024 /* align */ + 128 /* barriers */ +
                           16 /* tmem base */ + 2 * 2 * kTileM * 4 /* amax exchange */;
 
 enum : int { kModeGateUp = 0, kModeDown = 1 };
+
+// Optional timeline trace for tuning: compiled in only with -DB200_GEMM_TRACE.
+#ifdef B200_GEMM_TRACE
+__device__ long long* g_gemm_trace = nullptr;  // [role 0..3][4096] clock64 stamps of CTA 0
+#define B200_TRACE(role, idx)                                                         \
+  do {                                                                                \
+    if (blockIdx.x == 0 && g_gemm_trace != nullptr && (idx) < 4096)                   \
+      g_gemm_trace[(role) * 4096 + (idx)] = clock64();                                \
+  } while (0)
+#else
+#define B200_TRACE(role, idx) do { } while (0)
+#endif
 
 struct GemmParams {
   const float* a_scale;  // [rows, k_blocks]
@@ -103,6 +118,8 @@ moe_fp8_gemm_kernel(const __grid_constant__ CUtensorMap a_map,
 
   const int total = (*p.num_tiles) * p.n_tiles;
 
+  if (warp < 4) {
+  asm volatile("setmaxnreg.dec.sync.aligned.u32 40;");
   if (warp == 0) {
     // ------------------------------------------------------------ TMA ------
     if (lane == 0) {
@@ -125,6 +142,7 @@ moe_fp8_gemm_kernel(const __grid_constant__ CUtensorMap a_map,
           const uint32_t slot = it % kGemmStages, phase = (it / kGemmStages) & 1;
           alive = mbar_wait(bar_empty + 8 * slot, phase ^ 1, p.err);
           if (!alive) break;
+          B200_TRACE(0, it);
           const uint32_t sa = ring + slot * kStageBytesG, sb = sa + kABytes;
           mbar_arrive_expect_tx(bar_full + 8 * slot, kStageBytesG);
           tma_load_2d(sa, &a_map, bar_full + 8 * slot, kb * kBlockK, tile.row0);
@@ -143,9 +161,11 @@ moe_fp8_gemm_kernel(const __grid_constant__ CUtensorMap a_map,
         for (int kb = 0; kb < p.k_blocks; ++kb, ++it) {
           const uint32_t slot = it % kGemmStages, phase = (it / kGemmStages) & 1;
           const uint32_t buf = it & 1, aphase = (it >> 1) & 1;
-          alive = mbar_wait(bar_full + 8 * slot, phase, p.err) &&
-                  mbar_wait(bar_tempty + 8 * buf, aphase ^ 1, p.err);
+          alive = mbar_wait(bar_full + 8 * slot, phase, p.err);
+          B200_TRACE(1, 2 * it);
+          alive = alive && mbar_wait(bar_tempty + 8 * buf, aphase ^ 1, p.err);
           if (!alive) break;
+          B200_TRACE(1, 2 * it + 1);
           tc_fence_after();
           const uint32_t sa = ring + slot * kStageBytesG, sb = sa + kABytes;
           const uint64_t a_desc = umma_desc_k128(sa), b_desc = umma_desc_k128(sb);
@@ -158,10 +178,12 @@ moe_fp8_gemm_kernel(const __grid_constant__ CUtensorMap a_map,
         }
       }
     }
+  }
   } else {
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 232;");
     // ------------------------------------------- promotion + epilogue ------
     const int quarter = warp & 3;        // TMEM lane quarter this warp may read
-    const int half = (warp - 2) >> 2;    // which 128 of the tile's 256 columns
+    const int half = (warp - 4) >> 2;    // which 128 of the tile's 256 columns
     const int r = quarter * 32 + lane;   // row inside the tile
     const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
     uint32_t it = 0, tile_it = 0;
@@ -191,43 +213,54 @@ moe_fp8_gemm_kernel(const __grid_constant__ CUtensorMap a_map,
         const float s0 = sa * __ldg(bs0 + kb), s1 = sa * __ldg(bs1 + kb);
         alive = mbar_wait(bar_tfull + 8 * buf, aphase, p.err);
         if (!alive) break;
+        if (threadIdx.x == 128) B200_TRACE(2, 2 * it);
         tc_fence_after();
         const uint32_t t0 = lane_addr + buf * kTileN;
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
-          uint32_t col;
-          float s;
+        for (int c = 0; c < 4; c += 2) {
+          uint32_t col0, col1;
+          float sc0, sc1;
           if (MODE == kModeGateUp) {
-            col = (c < 2 ? 0 : 128) + half * 64 + (c & 1) * 32;
-            s = c < 2 ? s0 : s1;
+            col0 = (c < 2 ? 0 : 128) + half * 64;
+            col1 = col0 + 32;
+            sc0 = sc1 = c < 2 ? s0 : s1;
           } else {
-            col = half * 128 + c * 32;
-            s = s0;
+            col0 = half * 128 + c * 32;
+            col1 = col0 + 32;
+            sc0 = sc1 = s0;
           }
-          uint32_t v[32];
-          tmem_ld32(t0 + col, v);
+          uint32_t v0[32], v1[32];
+          tmem_ld32(t0 + col0, v0);
+          tmem_ld32(t0 + col1, v1);
           tmem_ld_wait();
+          if (c == 2) {
+            // everything this thread needs from the accumulator is in registers
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_tempty + 8 * buf);
+          }
 #pragma unroll
-          for (int i = 0; i < 32; ++i) acc[c * 32 + i] = fmaf(__uint_as_float(v[i]), s, acc[c * 32 + i]);
+          for (int i = 0; i < 32; ++i) {
+            acc[c * 32 + i] = fmaf(__uint_as_float(v0[i]), sc0, acc[c * 32 + i]);
+            acc[c * 32 + 32 + i] = fmaf(__uint_as_float(v1[i]), sc1, acc[c * 32 + 32 + i]);
+          }
         }
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(bar_tempty + 8 * buf);
+        if (threadIdx.x == 128) B200_TRACE(2, 2 * it + 1);
       }
       if (!alive) break;
+      if (threadIdx.x == 128) B200_TRACE(3, 4 * tile_it);
 
       if (MODE == kModeGateUp) {
         // acc[0..63] = gate, acc[64..127] = up for inter columns j*128 + half*64 + i
         float amax = 0.f;
 #pragma unroll
         for (int i = 0; i < 64; ++i) {
-          const float g = __bfloat162float(__float2bfloat16(acc[i]));
-          const float u = __bfloat162float(__float2bfloat16(acc[64 + i]));
-          const float a = __bfloat162float(__float2bfloat16(g / (1.f + expf(-g))));
-          const float h = __bfloat162float(__float2bfloat16(a * u));
+          const float g = acc[i];
+          const float h = __fdividef(g, 1.f + __expf(-g)) * acc[64 + i];  // no slow-path branch: the loop must pipeline
           acc[i] = h;
           amax = fmaxf(amax, fabsf(h));
         }
+        if (threadIdx.x == 128) B200_TRACE(3, 4 * tile_it + 1);
         float* ax = amax_sm + (tile_it & 1) * 2 * kTileM;
         ax[half * kTileM + r] = amax;
         // The partner thread (same row, other column half) holds the rest of the
@@ -238,8 +271,10 @@ moe_fp8_gemm_kernel(const __grid_constant__ CUtensorMap a_map,
         if (lane == 0) mbar_arrive(bar_amax + 8 * (tile_it & 1));
         alive = mbar_wait(bar_amax + 8 * (tile_it & 1), (tile_it >> 1) & 1, p.err);
         if (!alive) break;
+        if (threadIdx.x == 128) B200_TRACE(3, 4 * tile_it + 2);
         amax = fmaxf(amax, ax[(half ^ 1) * kTileM + r]);
         const float s = amax > 0.f ? amax / 448.f : 1.f;
+        const float inv_s = 1.f / s;
         if (row_ok) {
           uint8_t* dst = p.hq + grow * p.inter + j * 128 + half * 64;
 #pragma unroll
@@ -247,11 +282,12 @@ moe_fp8_gemm_kernel(const __grid_constant__ CUtensorMap a_map,
             uint32_t wd[4];
 #pragma unroll
             for (int q = 0; q < 4; ++q) {
-              uint32_t x = 0;
-#pragma unroll
-              for (int b = 0; b < 4; ++b)
-                x |= static_cast<uint32_t>(to_e4m3(acc[c * 16 + q * 4 + b] / s)) << (8 * b);
-              wd[q] = x;
+              const int b = c * 16 + q * 4;
+              const uint32_t lo = __nv_cvt_float2_to_fp8x2(make_float2(acc[b] * inv_s, acc[b + 1] * inv_s),
+                                                           __NV_SATFINITE, __NV_E4M3);
+              const uint32_t hi = __nv_cvt_float2_to_fp8x2(make_float2(acc[b + 2] * inv_s, acc[b + 3] * inv_s),
+                                                           __NV_SATFINITE, __NV_E4M3);
+              wd[q] = lo | (hi << 16);
             }
             *reinterpret_cast<uint4*>(dst + c * 16) = make_uint4(wd[0], wd[1], wd[2], wd[3]);
           }
@@ -271,6 +307,7 @@ moe_fp8_gemm_kernel(const __grid_constant__ CUtensorMap a_map,
           }
         }
       }
+      if (threadIdx.x == 128) B200_TRACE(3, 4 * tile_it + 3);
     }
   }
 
@@ -305,6 +342,13 @@ static int launch_gemm(const CUtensorMap& a_map, const CUtensorMap& b_map, const
 }  // namespace b200
 
 using namespace b200;
+
+#ifdef B200_GEMM_TRACE
+extern "C" int b200_set_gemm_trace(void* buf) {
+  long long* p = static_cast<long long*>(buf);
+  return cudaMemcpyToSymbol(b200::g_gemm_trace, &p, sizeof(p)) == cudaSuccess ? 0 : -4;
+}
+#endif
 
 static int aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 

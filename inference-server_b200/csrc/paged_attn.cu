@@ -9,71 +9,69 @@
 // reference layout [num_blocks, n_kv_heads, block_size, head_dim]
 // (src/inference_server/kv_cache/block_manager.py:33-49).
 //
-// Main kernel (bf16 pools, page 16, head_dim 64 or 128):
-//   grid  = (batch, max_splits, n_kv_heads), block = 4 consumer warps + 1
+// Main kernel (bf16 pools, page 16, head_dim 64 or 128, 1/2/4/8 kv heads):
+//   grid  = (batch, max_splits), block = one consumer warp per kv head + 1
 //           producer warp.  One CTA owns `split_tokens` consecutive tokens of one
-//           (sequence, kv head).
-//   load  = the producer warp looks page ids up in the block table and issues
-//           one TMA box (16 rows x 128 bytes, 128-byte swizzle) per page half
-//           for K and for V into a 3-stage ring of 64-token stages; stage
-//           hand-over is by mbarrier (full: transaction bytes, empty: 4 warps).
-//   math  = consumer warp w owns page w of every stage: S = Q K^T with
-//           mma.sync m16n8k16 (rows = the <=16 query heads of the kv group),
-//           online softmax in fp32 with quad shuffles, O += P V.
-//   out   = the 4 warps merge through shared memory and write one fp32 partial
-//           (o, m, l) per (sequence, q head, split); a second kernel folds the
-//           splits in fixed order and writes bf16.
+//           sequence, for ALL kv heads: in the pool the kv heads of a page are
+//           adjacent, so a page is one contiguous 16*Hkv*D*2-byte read for K and
+//           one for V, which is what keeps the DRAM row buffers busy.
+//   load  = the producer warp looks the page id up in the block table and issues
+//           one TMA box (16*Hkv rows x 128 bytes, 128-byte swizzle) per 128-byte
+//           column half for K and for V into a ring of one-page stages; stage
+//           hand-over is by mbarrier (full: transaction bytes, empty: Hkv warps).
+//   math  = consumer warp w owns kv head w: S = Q K^T with mma.sync m16n8k16
+//           (rows = the <=16 query heads of the kv group), online softmax in
+//           fp32 with quad shuffles, O += P V.  Warps never exchange data.
+//   out   = each warp writes one fp32 partial (o, m, l) per (sequence, q head,
+//           split); a second kernel folds the splits in fixed order -> bf16.
 // The kernel is HBM-bound: per token and kv head it reads 2*D*2 bytes once.
 //
 // Generic kernel: any head_dim <= 256, any page size, fp32 or bf16 pools, no
 // split, fp32 arithmetic throughout.  It serves shapes the main kernel does not
 // (the tiny fp32 parity model) and is not tuned.
 
+#include <stdlib.h>
+
 #include "common.cuh"
 #include "host.h"
 
 namespace b200 {
 
-constexpr int kPage = 16;         // tokens per page in the main kernel
-constexpr int kStagePages = 4;    // pages per pipeline stage
-constexpr int kStages = 3;        // pipeline depth
-constexpr int kConsumerWarps = 4;
-constexpr int kAttnThreads = (kConsumerWarps + 1) * 32;
+constexpr int kPage = 16;               // tokens per page in the main kernel
 constexpr int kBoxBytes = kPage * 128;  // one TMA box: 16 rows x 128 bytes
 
-template <int D>
+// D: head_dim.  HKV: kv heads = consumer warps.  STAGES: pipeline depth in pages.
+// CTAS: CTAs resident per SM the launch bounds aim for.
+template <int D, int HKV, int STAGES, int CTAS>
 struct AttnCfg {
-  static constexpr int kHalves = D / 64;                       // 128-byte column halves per row
-  static constexpr int kPageBytes = 2 * kHalves * kBoxBytes;   // K then V
-  static constexpr int kStageBytes = kStagePages * kPageBytes;
-  static constexpr int kRingBytes = kStages * kStageBytes;
-  static constexpr int kORow = D + 8;                          // padded fp32 row of the merge buffer
-  static constexpr int kSmemBytes = kRingBytes + 1024 /* alignment slack */ + 64 /* barriers */ + 512 /* m, l */;
-  static_assert(kConsumerWarps * 16 * kORow * 4 <= kRingBytes, "merge buffer must fit in the ring");
+  static constexpr int kThreads = (HKV + 1) * 32;
+  static constexpr int kHalves = D / 64;                     // 128-byte column halves per row
+  static constexpr int kHeadBytes = kBoxBytes;               // one head's 16 rows x 128 B inside a box
+  static constexpr int kBoxAll = HKV * kBoxBytes;            // one TMA box: all kv heads of a page half
+  static constexpr int kStageBytes = 2 * kHalves * kBoxAll;  // K halves then V halves
+  static constexpr int kRingBytes = STAGES * kStageBytes;
+  static constexpr int kSmemBytes = kRingBytes + 1024 /* alignment slack */ + 16 * STAGES /* barriers */;
 };
 
-template <int D>
-__global__ void __launch_bounds__(kAttnThreads, 2)
+template <int D, int HKV, int STAGES, int CTAS>
+__global__ void __launch_bounds__((HKV + 1) * 32, CTAS)
 paged_attn_decode_kernel(const __grid_constant__ CUtensorMap k_map,
                          const __grid_constant__ CUtensorMap v_map,
                          const __nv_bfloat16* __restrict__ q,
                          const int* __restrict__ block_table,
                          const int* __restrict__ ctx_lens,
                          float* __restrict__ part_o, float2* __restrict__ part_ml,
-                         int* __restrict__ err, int num_q_heads, int num_kv_heads,
-                         int num_blocks, int max_pages, int split_tokens, int max_splits,
-                         float scale_log2) {
+                         int* __restrict__ err, int num_q_heads, int num_blocks, int max_pages,
+                         int split_tokens, int max_splits, float scale_log2) {
 #ifdef B200_DEVICE_OK
-  using Cfg = AttnCfg<D>;
+  using Cfg = AttnCfg<D, HKV, STAGES, CTAS>;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t ring = (smem_u32(smem_raw) + 1023u) & ~1023u;
-  uint8_t* ring_ptr = smem_raw + (ring - smem_u32(smem_raw));
-  const uint32_t bars = ring + Cfg::kRingBytes;  // full[kStages], empty[kStages]
-  float* ml_sm = reinterpret_cast<float*>(ring_ptr + Cfg::kRingBytes + 64);  // [4 warps][16 rows][2]
+  const uint32_t bars = ring + Cfg::kRingBytes;  // full[STAGES], empty[STAGES]
 
-  const int b = blockIdx.x, split = blockIdx.y, kvh = blockIdx.z;
+  const int b = blockIdx.x, split = blockIdx.y;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int group = num_q_heads / num_kv_heads;
+  const int group = num_q_heads / HKV;
 
   int L = ctx_lens[b];
   if (L < 0 || L > max_pages * kPage) {
@@ -84,56 +82,54 @@ paged_attn_decode_kernel(const __grid_constant__ CUtensorMap k_map,
   if (start >= L) return;  // uniform for the whole CTA
   const int end = min(L, start + split_tokens);
   const int npages = (end - start + kPage - 1) / kPage;
-  const int nstages = (npages + kStagePages - 1) / kStagePages;
   const int first_page = start / kPage;
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < kStages; ++s) {
+    for (int s = 0; s < STAGES; ++s) {
       mbar_init(bars + 8 * s, 1);
-      mbar_init(bars + 8 * (kStages + s), kConsumerWarps);
+      mbar_init(bars + 8 * (STAGES + s), HKV);
     }
     fence_mbar_init();
     fence_proxy_async();
   }
   __syncthreads();
 
-  if (warp == kConsumerWarps) {
+  if (warp == HKV) {
     // ------------------------------------------------------------ producer --
     if (lane == 0) {
       tma_prefetch_desc(&k_map);
       tma_prefetch_desc(&v_map);
     }
     const int* table_row = block_table + static_cast<size_t>(b) * max_pages + first_page;
-    // lane -> (page, K or V, column half)
-    const int lp = lane / (2 * Cfg::kHalves);
-    const int lkv = (lane / Cfg::kHalves) & 1;
-    const int lh = lane % Cfg::kHalves;
-    for (int i = 0; i < nstages; ++i) {
-      const int slot = i % kStages;
-      const uint32_t phase = (i / kStages) & 1;
-      const int pages = min(kStagePages, npages - i * kStagePages);
-      int id = 0;
-      if (lp < pages && lane < kStagePages * 2 * Cfg::kHalves) {
-        id = table_row[i * kStagePages + lp];
-        if (id < 0 || id >= num_blocks) {
+    // lane -> (K or V, column half); one box each
+    const int lkv = lane / Cfg::kHalves, lh = lane % Cfg::kHalves;
+    const bool issuer = lane < 2 * Cfg::kHalves;
+    // page ids of this split, 32 at a time, one per lane
+    int ids = 0;
+    for (int i = 0; i < npages; ++i) {
+      if ((i & 31) == 0) {
+        ids = i + lane < npages ? table_row[i + lane] : 0;
+        if (ids < 0 || ids >= num_blocks) {
           set_error(err, kErrDevBadBlockId);
-          id = 0;
+          ids = 0;
         }
       }
-      if (!mbar_wait(bars + 8 * (kStages + slot), phase ^ 1, err)) break;
-      if (lane == 0) mbar_arrive_expect_tx(bars + 8 * slot, pages * Cfg::kPageBytes);
+      const int id = __shfl_sync(0xffffffffu, ids, i & 31);
+      const int slot = i % STAGES;
+      const uint32_t phase = (i / STAGES) & 1;
+      if (!mbar_wait(bars + 8 * (STAGES + slot), phase ^ 1, err)) break;
+      if (lane == 0) mbar_arrive_expect_tx(bars + 8 * slot, Cfg::kStageBytes);
       __syncwarp();
-      if (lp < pages && lane < kStagePages * 2 * Cfg::kHalves) {
-        const uint32_t dst = ring + slot * Cfg::kStageBytes + lp * Cfg::kPageBytes +
-                             (lkv * Cfg::kHalves + lh) * kBoxBytes;
-        const int y = (id * num_kv_heads + kvh) * kPage;
-        tma_load_2d(dst, lkv ? &v_map : &k_map, bars + 8 * slot, lh * 64, y);
+      if (issuer) {
+        const uint32_t dst = ring + slot * Cfg::kStageBytes + (lkv * Cfg::kHalves + lh) * Cfg::kBoxAll;
+        tma_load_2d(dst, lkv ? &v_map : &k_map, bars + 8 * slot, lh * 64, id * (HKV * kPage));
       }
     }
     return;
   }
 
   // --------------------------------------------------------------- consumers --
+  const int kvh = warp;      // this warp's kv head
   const int gq = lane >> 2;  // fragment row (query head inside the kv group)
   const int tq = lane & 3;
   const bool hi_rows = group > 8;
@@ -168,27 +164,26 @@ paged_attn_decode_kernel(const __grid_constant__ CUtensorMap k_map,
   const int v_sub = lj >> 1;             //    matrices 0,1 -> first n-tile; 2,3 -> second n-tile
 
   bool alive = true;
-  for (int i = 0; i < nstages && alive; ++i) {
-    const int slot = i % kStages;
-    const uint32_t phase = (i / kStages) & 1;
+  for (int i = 0; i < npages && alive; ++i) {
+    const int slot = i % STAGES;
+    const uint32_t phase = (i / STAGES) & 1;
     alive = mbar_wait(bars + 8 * slot, phase, err);
-    const int page = i * kStagePages + warp;
-    if (alive && page < npages) {
-      const uint32_t kbase = ring + slot * Cfg::kStageBytes + warp * Cfg::kPageBytes;
-      const uint32_t vbase = kbase + Cfg::kHalves * kBoxBytes;
+    if (alive) {
+      const uint32_t kbase = ring + slot * Cfg::kStageBytes + kvh * Cfg::kHeadBytes;
+      const uint32_t vbase = kbase + Cfg::kHalves * Cfg::kBoxAll;
 
       float s0[4] = {0.f, 0.f, 0.f, 0.f}, s1[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
       for (int ks = 0; ks < D / 16; ++ks) {
         const int cidx = ks * 2 + k_sub;
         uint32_t b00, b01, b10, b11;
-        ldmatrix_x4(kbase + (cidx >> 3) * kBoxBytes + swz128(k_tok, cidx & 7), b00, b01, b10, b11);
+        ldmatrix_x4(kbase + (cidx >> 3) * Cfg::kBoxAll + swz128(k_tok, cidx & 7), b00, b01, b10, b11);
         mma_bf16_16816(s0, qa[ks], b00, b01);
         mma_bf16_16816(s1, qa[ks], b10, b11);
       }
 
-      const int tok0 = start + page * kPage + 2 * tq;  // token of s0[0]; s0[1] is +1, s1[*] is +8
-      if (start + page * kPage + kPage > L) {
+      const int tok0 = start + i * kPage + 2 * tq;  // token of s0[0]; s0[1] is +1, s1[*] is +8
+      if (start + i * kPage + kPage > L) {
         if (tok0 >= L) s0[0] = s0[2] = -INFINITY;
         if (tok0 + 1 >= L) s0[1] = s0[3] = -INFINITY;
         if (tok0 + 8 >= L) s1[0] = s1[2] = -INFINITY;
@@ -225,13 +220,14 @@ paged_attn_decode_kernel(const __grid_constant__ CUtensorMap k_map,
       pa[2] = pack_bf16x2(p10, p11);
       pa[3] = pack_bf16x2(p12, p13);
 
+      const bool rescale = __any_sync(0xffffffffu, a0 != 1.f || a1 != 1.f);
 #pragma unroll
       for (int np = 0; np < D / 16; ++np) {
-        o[2 * np][0] *= a0;
-        o[2 * np][1] *= a0;
-        o[2 * np + 1][0] *= a0;
-        o[2 * np + 1][1] *= a0;
-        if (hi_rows) {
+        if (rescale) {
+          o[2 * np][0] *= a0;
+          o[2 * np][1] *= a0;
+          o[2 * np + 1][0] *= a0;
+          o[2 * np + 1][1] *= a0;
           o[2 * np][2] *= a1;
           o[2 * np][3] *= a1;
           o[2 * np + 1][2] *= a1;
@@ -239,13 +235,13 @@ paged_attn_decode_kernel(const __grid_constant__ CUtensorMap k_map,
         }
         const int cidx = np * 2 + v_sub;
         uint32_t v0, v1, v2, v3;
-        ldmatrix_x4_trans(vbase + (cidx >> 3) * kBoxBytes + swz128(v_tok, cidx & 7), v0, v1, v2, v3);
+        ldmatrix_x4_trans(vbase + (cidx >> 3) * Cfg::kBoxAll + swz128(v_tok, cidx & 7), v0, v1, v2, v3);
         mma_bf16_16816(o[2 * np], pa, v0, v1);
         mma_bf16_16816(o[2 * np + 1], pa, v2, v3);
       }
     }
     __syncwarp();
-    if (lane == 0) mbar_arrive(bars + 8 * (kStages + slot));
+    if (lane == 0) mbar_arrive(bars + 8 * (STAGES + slot));
   }
 
   l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
@@ -253,46 +249,18 @@ paged_attn_decode_kernel(const __grid_constant__ CUtensorMap k_map,
   l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
   l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
 
-  // Every consumer warp has waited on every stage, so the ring is idle and can
-  // be reused as the merge buffer once all four warps are here.
-  asm volatile("bar.sync 1, %0;" ::"r"(kConsumerWarps * 32) : "memory");
-  float* o_sm = reinterpret_cast<float*>(ring_ptr);  // [warp][16][kORow]
-  {
-    float* ow = o_sm + (warp * 16) * Cfg::kORow;
+  // Each warp owns its kv head's query rows: write the split partial directly.
+  const size_t row0 = (static_cast<size_t>(b) * num_q_heads + kvh * group + gq) * max_splits + split;
+  const size_t row1 = row0 + static_cast<size_t>(8) * max_splits;
 #pragma unroll
-    for (int n = 0; n < D / 8; ++n) {
-      const int d = n * 8 + 2 * tq;
-      if (gq < group) *reinterpret_cast<float2*>(ow + gq * Cfg::kORow + d) = make_float2(o[n][0], o[n][1]);
-      if (gq + 8 < group)
-        *reinterpret_cast<float2*>(ow + (gq + 8) * Cfg::kORow + d) = make_float2(o[n][2], o[n][3]);
-    }
-    if (tq == 0) {
-      ml_sm[(warp * 16 + gq) * 2 + 0] = m0;
-      ml_sm[(warp * 16 + gq) * 2 + 1] = l0;
-      ml_sm[(warp * 16 + gq + 8) * 2 + 0] = hi_rows ? m1 : -INFINITY;
-      ml_sm[(warp * 16 + gq + 8) * 2 + 1] = hi_rows ? l1 : 0.f;
-    }
+  for (int n = 0; n < D / 8; ++n) {
+    const int d = n * 8 + 2 * tq;
+    if (gq < group) *reinterpret_cast<float2*>(part_o + row0 * D + d) = make_float2(o[n][0], o[n][1]);
+    if (gq + 8 < group) *reinterpret_cast<float2*>(part_o + row1 * D + d) = make_float2(o[n][2], o[n][3]);
   }
-  asm volatile("bar.sync 1, %0;" ::"r"(kConsumerWarps * 32) : "memory");
-
-  for (int idx = threadIdx.x; idx < group * D; idx += kConsumerWarps * 32) {
-    const int g = idx / D, d = idx % D;
-    float mw[kConsumerWarps], mmax = -INFINITY;
-#pragma unroll
-    for (int w = 0; w < kConsumerWarps; ++w) {
-      mw[w] = ml_sm[(w * 16 + g) * 2];
-      mmax = fmaxf(mmax, mw[w]);
-    }
-    float acc = 0.f, lsum = 0.f;
-#pragma unroll
-    for (int w = 0; w < kConsumerWarps; ++w) {
-      const float wgt = mw[w] == -INFINITY ? 0.f : exp2f(mw[w] - mmax);
-      acc += wgt * o_sm[(w * 16 + g) * Cfg::kORow + d];
-      lsum += wgt * ml_sm[(w * 16 + g) * 2 + 1];
-    }
-    const size_t row = (static_cast<size_t>(b) * num_q_heads + kvh * group + g) * max_splits + split;
-    part_o[row * D + d] = acc;
-    if (d == 0) part_ml[row] = make_float2(mmax, lsum);
+  if (tq == 0) {
+    if (gq < group) part_ml[row0] = make_float2(m0, l0);
+    if (gq + 8 < group) part_ml[row1] = make_float2(m1, l1);
   }
 #endif
 }
@@ -465,32 +433,31 @@ static AttnWorkspace carve(void* ws, int batch, int hq, int D, int max_splits) {
   return w;
 }
 
-template <int D>
+template <int D, int HKV, int STAGES, int CTAS>
 static int launch_main(const void* q, const void* k_pool, const void* v_pool,
                        const int* block_table, const int* ctx_lens, void* out,
-                       const AttnWorkspace& w, int batch, int hq, int hkv, int num_blocks,
-                       int max_pages, float scale, int split_tokens, int max_splits,
-                       cudaStream_t stream) {
-  using Cfg = AttnCfg<D>;
+                       const AttnWorkspace& w, int batch, int hq, int num_blocks, int max_pages,
+                       float scale, int split_tokens, int max_splits, cudaStream_t stream) {
+  using Cfg = AttnCfg<D, HKV, STAGES, CTAS>;
   CUtensorMap kmap, vmap;
-  const uint64_t rows = static_cast<uint64_t>(num_blocks) * hkv * kPage;
-  int rc = get_tensor_map_2d(k_pool, rows, D, 2, kPage, 64, &kmap);
+  const uint64_t rows = static_cast<uint64_t>(num_blocks) * HKV * kPage;
+  int rc = get_tensor_map_2d(k_pool, rows, D, 2, HKV * kPage, 64, &kmap);
   if (rc) return rc;
-  rc = get_tensor_map_2d(v_pool, rows, D, 2, kPage, 64, &vmap);
+  rc = get_tensor_map_2d(v_pool, rows, D, 2, HKV * kPage, 64, &vmap);
   if (rc) return rc;
   static bool attr_done[64] = {false};
   int dev = 0;
   B200_CUDA(cudaGetDevice(&dev));
   if (dev < 64 && !attr_done[dev]) {
-    B200_CUDA(cudaFuncSetAttribute(paged_attn_decode_kernel<D>,
+    B200_CUDA(cudaFuncSetAttribute(paged_attn_decode_kernel<D, HKV, STAGES, CTAS>,
                                    cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
     attr_done[dev] = true;
   }
-  dim3 grid(batch, max_splits, hkv);
+  dim3 grid(batch, max_splits);
   const float scale_log2 = scale * 1.4426950408889634f;
-  paged_attn_decode_kernel<D><<<grid, kAttnThreads, Cfg::kSmemBytes, stream>>>(
+  paged_attn_decode_kernel<D, HKV, STAGES, CTAS><<<grid, Cfg::kThreads, Cfg::kSmemBytes, stream>>>(
       kmap, vmap, static_cast<const __nv_bfloat16*>(q), block_table, ctx_lens, w.o, w.ml, w.err, hq,
-      hkv, num_blocks, max_pages, split_tokens, max_splits, scale_log2);
+      num_blocks, max_pages, split_tokens, max_splits, scale_log2);
   B200_CUDA(cudaGetLastError());
   paged_attn_reduce_kernel<<<dim3(hq, batch), D, 0, stream>>>(
       w.o, w.ml, ctx_lens, static_cast<__nv_bfloat16*>(out), hq, D, max_splits, split_tokens,
@@ -535,27 +502,44 @@ extern "C" int b200_paged_attn_decode(const void* q, const void* k_pool, const v
   cudaStream_t st = as_stream(stream);
   const int group = num_q_heads / num_kv_heads;
   const bool fast = dtype == 0 && page_size == kPage && (head_dim == 64 || head_dim == 128) &&
-                    group <= 16 && split_tokens > 0;
+                    group <= 16 && split_tokens > 0 &&
+                    (num_kv_heads == 1 || num_kv_heads == 2 || num_kv_heads == 4 || num_kv_heads == 8);
   if (fast) {
-    B200_REQUIRE(split_tokens % (kPage * kStagePages) == 0,
-                 "paged_attn_decode: split_tokens %d not a multiple of %d", split_tokens,
-                 kPage * kStagePages);
+    B200_REQUIRE(split_tokens % kPage == 0, "paged_attn_decode: split_tokens %d not a multiple of %d",
+                 split_tokens, kPage);
     B200_REQUIRE((reinterpret_cast<uintptr_t>(k_pool) & 15) == 0 &&
                      (reinterpret_cast<uintptr_t>(v_pool) & 15) == 0 &&
                      (reinterpret_cast<uintptr_t>(q) & 3) == 0,
                  "paged_attn_decode: pools must be 16-byte aligned");
     const int ms = max_splits_of(max_pages_per_seq, page_size, split_tokens);
-    B200_REQUIRE(ms <= 65535 && num_kv_heads <= 65535, "paged_attn_decode: grid too large");
+    B200_REQUIRE(ms <= 65535, "paged_attn_decode: grid too large");
     AttnWorkspace w = carve(workspace, batch, num_q_heads, head_dim, ms);
     if (workspace_bytes < w.bytes) {
       set_detail("paged_attn_decode: workspace %zu < required %zu", workspace_bytes, w.bytes);
       return -kErrWorkspace;
     }
-    if (head_dim == 128)
-      return launch_main<128>(q, k_pool, v_pool, block_table, ctx_lens, out, w, batch, num_q_heads,
-                              num_kv_heads, num_blocks, max_pages_per_seq, scale, split_tokens, ms, st);
-    return launch_main<64>(q, k_pool, v_pool, block_table, ctx_lens, out, w, batch, num_q_heads,
-                           num_kv_heads, num_blocks, max_pages_per_seq, scale, split_tokens, ms, st);
+#define B200_ATTN_ARGS q, k_pool, v_pool, block_table, ctx_lens, out, w, batch, num_q_heads, num_blocks, \
+                       max_pages_per_seq, scale, split_tokens, ms, st
+    static const int variant = getenv("B200_ATTN_VARIANT") ? atoi(getenv("B200_ATTN_VARIANT")) : 0;
+    if (head_dim == 128) {
+      switch (num_kv_heads) {
+        case 1: return launch_main<128, 1, 8, 4>(B200_ATTN_ARGS);
+        case 2: return launch_main<128, 2, 6, 2>(B200_ATTN_ARGS);
+        case 4:
+          if (variant == 1) return launch_main<128, 4, 2, 3>(B200_ATTN_ARGS);
+          if (variant == 2) return launch_main<128, 4, 6, 1>(B200_ATTN_ARGS);
+          if (variant == 3) return launch_main<128, 4, 4, 1>(B200_ATTN_ARGS);
+          return launch_main<128, 4, 3, 2>(B200_ATTN_ARGS);
+        default: return launch_main<128, 8, 3, 1>(B200_ATTN_ARGS);
+      }
+    }
+    switch (num_kv_heads) {
+      case 1: return launch_main<64, 1, 8, 4>(B200_ATTN_ARGS);
+      case 2: return launch_main<64, 2, 6, 4>(B200_ATTN_ARGS);
+      case 4: return launch_main<64, 4, 6, 2>(B200_ATTN_ARGS);
+      default: return launch_main<64, 8, 3, 2>(B200_ATTN_ARGS);
+    }
+#undef B200_ATTN_ARGS
   }
   int* err = static_cast<int*>(workspace);
   dim3 grid(num_q_heads, batch);

@@ -42,13 +42,14 @@ def read_status(status: torch.Tensor, where: str = "device status") -> None:
 
 
 def default_split_tokens(batch: int, num_kv_heads: int, max_ctx: int, num_sms: int = 148) -> int:
-    """Tokens per KV split: large enough to amortise the pipeline fill, small
-    enough that batch * kv_heads * splits covers a few waves of CTAs."""
-    target_ctas = 4 * num_sms
-    per_seq = max(1, target_ctas // max(1, batch * num_kv_heads))
-    split = (max_ctx + per_seq - 1) // per_seq
+    """Tokens per KV split.  One CTA covers one split of one sequence (all kv
+    heads): aim for a few waves of CTAs, keep a split at least 128 tokens so the
+    pipeline fill is amortised, at most 1024 so ragged lengths still balance."""
+    target_ctas = 6 * num_sms
+    per_seq = max(1, target_ctas // max(1, batch))
+    split = (max_ctx // 2 + per_seq - 1) // per_seq  # typical row is about half the table width
     split = ((split + 63) // 64) * 64
-    return int(min(max(split, 256), 2048))
+    return int(min(max(split, 128), 1024))
 
 
 def paged_attn_workspace(batch, num_q_heads, head_dim, max_pages, page_size, split_tokens, device):

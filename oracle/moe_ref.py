@@ -91,12 +91,14 @@ def moe_fp8_ref(x, router_logits, w13_q, w13_s, w2_q, w2_s, top_k: int, renormal
     """The FP8 expert layer on CPU.
 
     Follows transformers ``FP8Experts.forward`` / ``fp8_grouped_mm_experts_forward``:
-    per (token, expert) pair  gate_up = W13 q(x)  (block-scaled product, result
-    bf16), h = silu(gate) * up in bf16 (``_apply_gate``: first half of the rows
-    is the gate), h re-quantised per row per 128, y = W2 q(h) (bf16), then
+    per (token, expert) pair  gate_up = W13 q(x)  (block-scaled product),
+    h = silu(gate) * up (``_apply_gate``: first half of the rows is the gate),
+    h re-quantised per row per 128, y = W2 q(h) (bf16), then
     out[t] = sum_k w[t,k] * y in fp32, rounded to bf16.  The block-scaled product
     equals dequant(A) @ dequant(W)^T up to fp32 rounding, which is how it is
-    evaluated here.
+    evaluated here.  One stated difference from that code: gate_up and h stay in
+    fp32 until h is quantised (there they pass through bf16), which is the more
+    accurate of the two and what the CUDA kernel does.
     """
     x = x.detach().cpu()
     T, H = x.shape
@@ -120,10 +122,9 @@ def moe_fp8_ref(x, router_logits, w13_q, w13_s, w2_q, w2_s, top_k: int, renormal
             continue
         a = xd[tok_of_row[lo:hi]]
         w13 = dequant_weight(w13_q[e], w13_s[e])
-        gu = _bf16(a @ w13.t())
+        gu = a @ w13.t()
         g, u = gu[:, :inter], gu[:, inter:]
-        act = _bf16(torch.nn.functional.silu(g))
-        h = _bf16(act * u)
+        h = torch.nn.functional.silu(g) * u
         hq, hs = act_quant_ref(h)
         hq_all[lo:hi], hs_all[lo:hi] = hq, hs
         h_all[lo:hi] = h
