@@ -1,0 +1,300 @@
+#!/usr/bin/env python
+"""Decode-throughput benchmark of the B200 decode hot path.
+
+    python bench.py --gpus N --steps K --warmup W            # this build
+    python bench.py --impl reference --gpus N --steps K ...  # the reference's CPU path
+
+Workload (BASELINE config 4): a random-init Qwen3-30B-A3B-shaped FP8 model in
+continuous-batching decode, 256 concurrent sequences per GPU, prompts uniform in
+512..4096 tokens, KV page size 16.  A *step* is one decode step of the whole
+batch: 48 x (KV append, paged attention, FP8 MoE) + dense projections + lm_head +
+argmax.  Prefill is not part of the metric: the KV pages are filled with N(0,1)
+values at the prompt lengths (all layers share one random pool image) and only
+decode steps are timed.  Inputs are synthetic and seeded.
+
+One JSON line is printed by rank 0:
+  value     decode tokens/s with the step's inputs already on the device (CUDA
+            graph replays, timed with CUDA events, max over ranks)
+  e2e       the same through B200Backend.decode_step_batched with HOST token
+            buffers: per step one host->device copy of the tokens and one
+            device->host read of the next tokens
+  roofline  paged attention kernel (the dominant kernel): algorithmic KV bytes
+            per launch / measured launch time, against the measured HBM peak
+  cpu_baseline  the reference's decode step on this machine's host cores
+            (oracle/ref_decode.py), a bounded sample extrapolated over layers
+"""
+from __future__ import annotations
+
+import argparse
+import importlib
+import json
+import os
+import subprocess
+import sys
+import tempfile
+import time
+
+import numpy as np
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+PAGE = 16
+# dram read+write bytes per algorithmic byte of the attention kernel, from the ncu capture summarised in
+# profiles/paged_attn_decode_small_case.md (same kernel, 16 rows x 4096 tokens; traffic grows with the pages read)
+ATTN_TRAFFIC_PER_ALG_BYTE = 1.047
+
+
+def pkg(sub):
+    return importlib.import_module("inference-server_b200." + sub)
+
+
+def measured_peak_gbs():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(path) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured (MEASURED_PEAKS.json hbm_gbs)"
+    except Exception:
+        return 6650.0, "fallback (6.65 TB/s, no MEASURED_PEAKS.json)"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index = index
+        self.proc = None
+        self.path = None
+
+    def __enter__(self):
+        try:
+            fd, self.path = tempfile.mkstemp(suffix=".csv")
+            os.close(fd)
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100",
+                 "-i", str(self.index)], stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
+        except Exception:
+            self.proc = None
+        return self
+
+    def __exit__(self, *exc):
+        if self.proc is not None:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except Exception:
+                self.proc.kill()
+
+    def summary(self) -> dict:
+        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": []}
+        try:
+            rows = [r.strip().split(",") for r in open(self.path) if r.strip()]
+            os.unlink(self.path)
+        except Exception:
+            return out
+        sm = [float(r[0]) for r in rows if len(r) >= 6]
+        if not sm:
+            return out
+        out["sm_mhz"] = float(np.median(sm))
+        out["sm_max_mhz"] = float(rows[0][1])
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for j, n in enumerate(names):
+            if any(r[2 + j].strip().lower().startswith("active") for r in rows if len(r) >= 6):
+                out["reasons"].append(n)
+        out["samples"] = len(sm)
+        return out
+
+
+def build_workload(cfg, batch: int, gen_tokens: int, seed: int):
+    rng = np.random.default_rng(seed)
+    prompt_lens = rng.integers(512, 4097, size=batch).tolist()
+    pages = [(L + gen_tokens + PAGE - 1) // PAGE for L in prompt_lens]
+    max_pages = max(pages)
+    total = sum(pages) + 64
+    perm = rng.permutation(total)
+    table = np.zeros((batch, max_pages), dtype=np.int32)
+    off = 0
+    for b, n in enumerate(pages):
+        table[b, :n] = perm[off:off + n]
+        off += n
+    return prompt_lens, table, total, max_pages
+
+
+def reference_arm(args, cfg, prompt_lens):
+    """The reference's own decode step on the host cores, bounded sample (see oracle/ref_decode.py)."""
+    from oracle.ref_decode import time_reference_decode
+
+    r = time_reference_decode(cfg, prompt_lens, steps=max(1, args.steps), warmup=max(0, args.warmup), sample_layers=1)
+    return r
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=32)
+    ap.add_argument("--warmup", type=int, default=4)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--model", default="qwen3-30b-a3b")
+    ap.add_argument("--batch", type=int, default=256, help="concurrent sequences per GPU")
+    ap.add_argument("--gen-tokens", type=int, default=256)
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    cfg = pkg("engine").CONFIGS[args.model]
+    prompt_lens, table, num_blocks, max_pages = build_workload(cfg, args.batch, args.gen_tokens, seed=rank)
+    config = {"workload": f"{args.model} continuous-batching decode, {args.batch} sequences/GPU, prompts U{{512..4096}}, "
+                          f"page {PAGE}, FP8 experts (BASELINE config 4)",
+              "batch_per_gpu": args.batch, "mean_ctx": float(np.mean(prompt_lens)), "parallelism": f"dp{world}",
+              "kv": "synthetic N(0,1) pages at the prompt lengths; prefill not timed",
+              "l2": "each step streams >90 GB of KV and weights, far larger than the 126 MB L2"}
+
+    if args.impl == "reference":
+        if rank != 0:
+            return
+        torch.set_num_threads(os.cpu_count() or torch.get_num_threads())
+        steps = min(args.steps, 3)
+        warm = min(args.warmup, 1)
+        args.steps, args.warmup = steps, warm
+        r = reference_arm(args, cfg, prompt_lens)
+        line = {"impl": "reference", "metric": "decode tok/s", "value": r["tok_per_s"], "unit": "tok/s", "n_gpus": args.gpus,
+                "steps": steps, "warmup": warm, "ms_per_step": r["step_s_full"] * 1e3, "higher_is_better": True,
+                "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "config": config,
+                "cpu_baseline": {"value": r["tok_per_s"], "unit": "tok/s", "cores": r["threads"], "kind": "port",
+                                 "sample": r["sample"]},
+                "e2e": {"value": r["tok_per_s"], "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+        print(json.dumps(line))
+        return
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the decode path has no CPU implementation "
+                         "(use --impl reference for the CPU baseline)")
+    pkg("_lib").load()  # fail loudly when the library is missing
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=dev)
+
+    eng_mod, ops, backend_mod = pkg("engine"), pkg("ops"), pkg("backend")
+    t_setup = time.time()
+    engine = eng_mod.DecodeEngine(cfg, num_blocks=num_blocks, max_batch=args.batch, max_pages_per_seq=max_pages,
+                                  device=dev, seed=rank)
+    # KV image: one random pool, shared by all layers (contents do not affect timing)
+    g = torch.Generator(device=dev).manual_seed(1000 + rank)
+    engine.k_pools[0].normal_(generator=g)
+    engine.v_pools[0].normal_(generator=g)
+    for li in range(1, cfg.layers):
+        engine.k_pools[li].copy_(engine.k_pools[0])
+        engine.v_pools[li].copy_(engine.v_pools[0])
+    engine.block_table.copy_(torch.from_numpy(table))
+    engine.ctx_lens.copy_(torch.tensor(prompt_lens, dtype=torch.int32))
+    engine.tokens.copy_(torch.randint(0, cfg.vocab_size, (args.batch,), generator=torch.Generator().manual_seed(rank)))
+    B = args.batch
+    torch.cuda.synchronize()
+    setup_s = time.time() - t_setup
+
+    def barrier():
+        if world > 1:
+            torch.distributed.barrier()
+        torch.cuda.synchronize()
+
+    # ---- kernel-path throughput: inputs resident, graph replays
+    for _ in range(max(3, args.warmup)):
+        engine.tokens[:B].copy_(engine.step(B))
+    barrier()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler(local_rank) as clocks:
+        ev0.record()
+        for _ in range(args.steps):
+            engine.tokens[:B].copy_(engine.step(B))
+        ev1.record()
+        barrier()
+    ms = ev0.elapsed_time(ev1)
+    clock_info = clocks.summary()
+    ops.read_status(engine.attn_ws, "attention workspace status after the timed region")
+    ops.read_status(engine.moe_ws, "MoE workspace status after the timed region")
+
+    # ---- end to end through the backend API with host buffers
+    backend = backend_mod.B200Backend(engine)
+    ctx_now = engine.ctx_lens[:B].cpu().tolist()
+    batch = backend_mod.PagedBatch(rows=[backend_mod.SeqKV(block_ids=table[b][table[b] >= 0].tolist()[:(prompt_lens[b] + args.gen_tokens + PAGE - 1) // PAGE],
+                                                           ctx_len=ctx_now[b]) for b in range(B)])
+    tok_host = torch.randint(0, cfg.vocab_size, (B, 1)).pin_memory()
+    for _ in range(3):
+        nxt, batch = backend.decode_step_batched(tok_host, batch)
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        nxt, batch = backend.decode_step_batched(tok_host, batch)
+        tok_host.copy_(nxt.view(B, 1))
+    barrier()
+    e2e_s = time.perf_counter() - t0
+
+    # ---- attention kernel alone, on the same pools (each layer's pool is a different 2.7 GB region)
+    ctx_dev = engine.ctx_lens[:B].clone()
+    q = torch.randn(B, cfg.q_heads, cfg.head_dim, device=dev, dtype=torch.bfloat16)
+    out = torch.empty_like(q)
+    for li in range(4):
+        ops.paged_attn_decode(q, engine.k_pools[li], engine.v_pools[li], engine.block_table[:B], ctx_dev, engine.scale,
+                              engine.split_tokens, engine.attn_ws, out)
+    torch.cuda.synchronize()
+    a0, a1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a0.record()
+    for li in range(cfg.layers):
+        ops.paged_attn_decode(q, engine.k_pools[li], engine.v_pools[li], engine.block_table[:B], ctx_dev, engine.scale,
+                              engine.split_tokens, engine.attn_ws, out)
+    a1.record()
+    torch.cuda.synchronize()
+    attn_us = a0.elapsed_time(a1) * 1e3 / cfg.layers
+    lens_now = ctx_dev.cpu().numpy().astype(np.int64)
+    pages_now = (lens_now + PAGE - 1) // PAGE
+    alg_bytes = int(pages_now.sum()) * PAGE * cfg.kv_heads * cfg.head_dim * 2 * 2 + B * cfg.q_heads * cfg.head_dim * 2 * 2 \
+        + 4 * int(pages_now.sum()) + 4 * B
+    peak, peak_src = measured_peak_gbs()
+    achieved = alg_bytes / attn_us / 1e3  # GB/s
+
+    times = torch.tensor([ms, e2e_s * 1e3], device=dev, dtype=torch.float64)
+    if world > 1:
+        torch.distributed.all_reduce(times, op=torch.distributed.ReduceOp.MAX)
+    ms_max, e2e_ms_max = times.tolist()
+    total_tokens = world * B * args.steps
+    if rank != 0:
+        if world > 1:
+            torch.distributed.destroy_process_group()
+        return
+
+    line = {
+        "metric": "decode tok/s", "value": total_tokens / (ms_max / 1e3), "unit": "tok/s", "n_gpus": world,
+        "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": ms_max / args.steps, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "fp8 experts (e4m3, fp32 accumulate) + bf16 attention/dense",
+        "data": "synthetic", "config": config,
+        "e2e": {"value": total_tokens / (e2e_ms_max / 1e3), "unit": "tok/s", "h2d_bytes_per_step": B * 8,
+                "d2h_bytes_per_step": B * 8, "api": "B200Backend.decode_step_batched"},
+        "gpu_launches": engine.kernel_launches_per_step * args.steps,
+        "clocks": clock_info,
+        "roofline": {"kernel": "paged_attn_decode_kernel (+ split reduce)", "bound": "hbm", "achieved": achieved, "peak": peak,
+                     "unit": "GB/s", "frac": achieved / peak, "traffic": alg_bytes * ATTN_TRAFFIC_PER_ALG_BYTE,
+                     "algorithmic_bytes": alg_bytes, "us_per_launch": attn_us, "peak_source": peak_src,
+                     "launches_timed": cfg.layers},
+        "setup_s": setup_s,
+    }
+    if not args.no_cpu_baseline and world == 1:
+        from oracle.ref_decode import time_reference_decode
+        r = time_reference_decode(cfg, prompt_lens, steps=2, warmup=1, sample_layers=1)
+        line["cpu_baseline"] = {"value": r["tok_per_s"], "unit": "tok/s", "cores": r["threads"], "kind": "port",
+                                "sample": r["sample"]}
+    print(json.dumps(line))
+    if world > 1:
+        torch.distributed.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

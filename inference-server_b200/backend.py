@@ -1,0 +1,361 @@
+"""B200Backend: the reference's backend interface on paged KV instead of dense caches.
+
+Mirrors ``InferenceBackend`` (src/inference_server/backends/base.py:10-138) and the
+behaviour of ``TorchBackend`` (src/inference_server/backends/torch_backend.py) method
+for method, so ``ContinuousBatchScheduler`` (src/inference_server/scheduler.py) can
+drive it unchanged:
+
+  reference (dense)                                this backend (paged)
+  -----------------------------------------------  ------------------------------------
+  per-row kv = HF DynamicCache [1,H,L,D]           ``SeqKV``: page ids + context length
+  batched_kv = left-padded DynamicCache [B,H,S,D]  ``PagedBatch``: list of ``SeqKV`` rows
+  splice_into_batched: re-pad + torch.cat          append a row          (:337-362)
+  remove_row_from_cache: torch.cat without row     delete a row, free its private pages (:327-335)
+  decode_step_batched: model(...) on dense cache   block table + graph replay (:305-322)
+  kv_length: keys.shape[2]                         max context length    (:364)
+
+The ``attention_mask`` and ``position_ids`` the scheduler passes
+(scheduler.py:386-397) are accepted and ignored: context lengths are backend
+state.  ``next_tokens`` comes back as a CPU tensor so the scheduler's per-row
+``.item()`` (scheduler.py:399-402) costs one device read per step.
+
+If a reference ``CacheManager`` is attached (``set_cache_adapter``,
+base.py:16-18) and owns bf16 pools of the right shape, the engine reads and
+writes those very pools (kv_cache/block_manager.py:33-49), prefix hits from
+``lookup`` (kv_cache/cache_manager.py:41-80) are used in place as shared
+read-only pages, and prompts are registered with ``store`` (:82-127) exactly as
+TorchBackend does.  Without an adapter the backend keeps its own free list.
+
+The module has no CPU path for the arithmetic: constructing the engine needs a
+CUDA device.  ``PagedBatch``/``SeqKV`` bookkeeping is plain Python and is what
+the CPU tests exercise with a stub engine.
+"""
+from __future__ import annotations
+
+import threading
+from dataclasses import dataclass, field
+from typing import Generator
+
+import torch
+
+PAGE = 16
+
+
+@dataclass
+class SeqKV:
+    """KV handle of one sequence: which pages hold it and how many tokens are valid."""
+
+    block_ids: list[int]
+    ctx_len: int
+    private_blocks: list = field(default_factory=list)  # allocator handles this row must give back
+    reserve_tokens: int = 0
+
+
+@dataclass
+class PagedBatch:
+    """The opaque ``batched_kv`` the scheduler carries: rows in ``_active`` order."""
+
+    rows: list[SeqKV] = field(default_factory=list)
+    dirty: bool = True  # block table on the device needs a refresh
+
+
+class _FreeListAllocator:
+    """Page allocator used when no reference CacheManager is attached."""
+
+    def __init__(self, num_blocks: int):
+        self.free = list(range(num_blocks - 1, -1, -1))
+
+    def allocate(self, n: int) -> list[int]:
+        if n > len(self.free):
+            raise MemoryError(f"Requested {n} blocks but only {len(self.free)} available")
+        return [self.free.pop() for _ in range(n)]
+
+    def release(self, ids: list[int]) -> None:
+        self.free.extend(ids)
+
+
+class B200Backend:
+    """Implements the reference backend contract; see the module docstring."""
+
+    cache_adapter = None
+    last_cache_hit_tokens: int = 0
+
+    def __init__(self, engine=None, eos_ids: set[int] | None = None, max_new_tokens: int = 256):
+        self.engine = engine
+        self._eos_ids: set[int] = set(eos_ids or ())
+        self._lock = threading.Lock()  # the scheduler takes backend._lock (scheduler.py:184)
+        self._alloc = _FreeListAllocator(engine.num_blocks) if engine is not None else None
+        self.max_new_tokens = max_new_tokens
+        self._table_cpu = None
+        self._lens_cpu = None
+
+    # ------------------------------------------------------------ lifecycle
+    def set_cache_adapter(self, adapter) -> None:
+        """Attach a reference CacheManager (base.py:16-18) and adopt its pools when they fit."""
+        self.cache_adapter = adapter
+        bm = getattr(adapter, "block_manager", None)
+        eng = self.engine
+        if bm is None or eng is None or not getattr(bm, "k_pools", None):
+            return
+        want = (eng.cfg.kv_heads, PAGE, eng.cfg.head_dim)
+        ok = (len(bm.k_pools) == eng.cfg.layers and all(
+            tuple(p.shape[1:]) == want and p.dtype == torch.bfloat16 and p.device.type == "cuda" for p in bm.k_pools))
+        if not ok:
+            raise ValueError("CacheManager pools do not match the engine (need bf16 CUDA pools "
+                             f"[num_blocks, {want[0]}, {want[1]}, {want[2]}] per layer, block_size 16)")
+        eng.k_pools, eng.v_pools = bm.k_pools, bm.v_pools
+        eng.num_blocks = bm.total_blocks
+        eng._graphs.clear()
+        self._alloc = None  # pages now come from the reference BlockManager
+
+    def load_model(self, model_name: str) -> None:
+        """Build a random-init engine of a named shape (no checkpoints are available offline)."""
+        from .engine import CONFIGS, DecodeEngine
+
+        if model_name not in CONFIGS:
+            raise ValueError(f"unknown model shape {model_name!r}; available: {sorted(CONFIGS)}")
+        cfg = CONFIGS[model_name]
+        self.engine = DecodeEngine(cfg, num_blocks=4096, max_batch=64, max_pages_per_seq=256)
+        self._alloc = _FreeListAllocator(self.engine.num_blocks)
+
+    def kv_shape_per_layer(self) -> list[tuple[int, int]]:
+        cfg = self.engine.cfg
+        return [(cfg.kv_heads, cfg.head_dim)] * cfg.layers
+
+    @property
+    def kv_dtype(self) -> torch.dtype:
+        return torch.bfloat16
+
+    @property
+    def device(self):
+        return self.engine.device
+
+    @property
+    def device_str(self) -> str:
+        """The scheduler builds its token/mask tensors on this device (scheduler.py:173):
+        host memory, so that they cost no device work."""
+        return "cpu"
+
+    def is_eos(self, token_id: int) -> bool:
+        return token_id in self._eos_ids
+
+    def kv_length(self, kv) -> int:
+        if isinstance(kv, PagedBatch):
+            return max((r.ctx_len for r in kv.rows), default=0)
+        return kv.ctx_len
+
+    # ---------------------------------------------------------------- pages
+    def _take_pages(self, n: int) -> tuple[list[int], list]:
+        if n <= 0:
+            return [], []
+        if self._alloc is not None:
+            ids = self._alloc.allocate(n)
+            return ids, ids
+        bm = self.cache_adapter.block_manager
+        while n > bm.free_blocks:
+            if not self.cache_adapter._evict_one():
+                raise MemoryError(f"Requested {n} blocks but only {bm.free_blocks} available")
+        blocks = bm.allocate(n)
+        return [b.block_id for b in blocks], blocks
+
+    def _give_back(self, handles: list) -> None:
+        if not handles:
+            return
+        if self._alloc is not None:
+            self._alloc.release(handles)
+        else:
+            self.cache_adapter.block_manager.free(handles)
+
+    # -------------------------------------------------------------- prefill
+    def _lookup(self, token_ids: list[int], session_id: str):
+        """Prefix lookup as TorchBackend does (torch_backend.py:113-119), keeping only the
+        leading run of full pages: the kernels need every page but the last to be full."""
+        cache = self.cache_adapter
+        if cache is None or not getattr(cache.block_manager, "k_pools", None):
+            return 0, []
+        matched, blocks = cache.lookup(token_ids, session_id=session_id)
+        keep = []
+        for blk in blocks:
+            if blk.num_tokens_stored != PAGE:
+                break
+            keep.append(blk)
+        for blk in blocks[len(keep):]:
+            blk.release()  # not used by this row
+        usable = min(len(keep) * PAGE, len(token_ids) - 1)  # always leave one token to run
+        usable -= usable % PAGE
+        for blk in keep[usable // PAGE:]:
+            blk.release()
+        return usable, [b.block_id for b in keep[: usable // PAGE]]
+
+    def prefill(self, token_ids: list[int], session_id: str = "default"):
+        """(per_row_kv, first_token_id, kv_length), as base.py:57-61."""
+        matched, shared_ids = self._lookup(token_ids, session_id)
+        self.last_cache_hit_tokens = matched
+        n = len(token_ids)
+        total_pages = (n + self.max_new_tokens + PAGE - 1) // PAGE
+        ids, handles = self._take_pages(total_pages - len(shared_ids))
+        kv = SeqKV(block_ids=shared_ids + ids, ctx_len=n, private_blocks=handles)
+        first, _ = self.engine.prefill(token_ids, kv.block_ids, cached_tokens=matched)
+        self._store(token_ids, kv, matched, session_id)
+        return kv, first, n
+
+    def _store(self, token_ids, kv: SeqKV, matched: int, session_id: str) -> None:
+        """Register the prompt with the reference cache (torch_backend.py:143-145)."""
+        cache = self.cache_adapter
+        if cache is None or matched >= len(token_ids) or not getattr(cache.block_manager, "k_pools", None):
+            return
+        n = len(token_ids)
+        n_pages = (n + PAGE - 1) // PAGE
+        bt = torch.tensor(kv.block_ids[:n_pages], device=self.engine.device)
+        per_layer = []
+        for kp, vp in zip(self.engine.k_pools, self.engine.v_pools):
+            k = kp[bt].permute(1, 0, 2, 3).reshape(kp.shape[1], n_pages * PAGE, kp.shape[3])[:, :n]
+            v = vp[bt].permute(1, 0, 2, 3).reshape(vp.shape[1], n_pages * PAGE, vp.shape[3])[:, :n]
+            per_layer.append((k, v))
+        cache.store(token_ids, per_layer, skip_tokens=matched, session_id=session_id)
+
+    def prefill_lookup(self, token_ids: list[int], session_id: str = "default"):
+        matched, shared_ids = self._lookup(token_ids, session_id)
+        self.last_cache_hit_tokens = matched
+        if matched == 0:
+            return None, 0
+        return SeqKV(block_ids=shared_ids, ctx_len=matched, reserve_tokens=len(token_ids)), matched
+
+    def prefill_chunk(self, chunk_token_ids: list[int], partial_kv):
+        """Forward one chunk on top of partial_kv (base.py:71-78)."""
+        kv = partial_kv if partial_kv is not None else SeqKV(block_ids=[], ctx_len=0)
+        new_len = kv.ctx_len + len(chunk_token_ids)
+        need = (new_len + self.max_new_tokens + PAGE - 1) // PAGE - len(kv.block_ids)
+        ids, handles = self._take_pages(need)
+        kv.block_ids += ids
+        kv.private_blocks += handles
+        hist = getattr(kv, "_tokens", [None] * kv.ctx_len)
+        tokens = hist + list(chunk_token_ids)
+        last, _ = self.engine.prefill(tokens, kv.block_ids, cached_tokens=kv.ctx_len)
+        kv._tokens = tokens
+        kv.ctx_len = new_len
+        return kv, last, new_len
+
+    def prefill_store(self, token_ids, full_kv, matched: int, session_id: str = "default") -> None:
+        self._store(token_ids, full_kv, matched, session_id)
+
+    # --------------------------------------------------------------- batching
+    def splice_into_batched(self, batched_kv, new_kv, new_kv_len: int):
+        batch = batched_kv if batched_kv is not None else PagedBatch()
+        batch.rows.append(new_kv)
+        batch.dirty = True
+        return batch
+
+    def stack_caches_left_padded(self, per_row_caches: list, max_kv_len: int):
+        return PagedBatch(rows=list(per_row_caches))
+
+    def remove_row_from_cache(self, batched_kv, row_idx: int):
+        row = batched_kv.rows.pop(row_idx)
+        self._give_back(row.private_blocks)
+        row.private_blocks = []
+        batched_kv.dirty = True
+        return batched_kv
+
+    def _sync_table(self, batch: PagedBatch) -> int:
+        eng = self.engine
+        B = len(batch.rows)
+        if B > eng.max_batch:
+            raise ValueError(f"batch {B} exceeds the engine's max_batch {eng.max_batch}")
+        if batch.dirty or self._table_cpu is None:
+            if self._table_cpu is None:
+                self._table_cpu = torch.zeros(eng.max_batch, eng.max_pages, dtype=torch.int32).pin_memory()
+                self._lens_cpu = torch.zeros(eng.max_batch, dtype=torch.int32).pin_memory()
+            self._table_cpu.zero_()
+            for i, row in enumerate(batch.rows):
+                if len(row.block_ids) > eng.max_pages:
+                    raise ValueError("sequence needs more pages than the block table is wide")
+                self._table_cpu[i, : len(row.block_ids)] = torch.tensor(row.block_ids, dtype=torch.int32)
+                self._lens_cpu[i] = row.ctx_len
+            eng.block_table.copy_(self._table_cpu, non_blocking=True)
+            eng.ctx_lens.copy_(self._lens_cpu, non_blocking=True)
+            batch.dirty = False
+        return B
+
+    def decode_step_batched(self, current_tokens, batched_kv, attention_mask=None, position_ids=None):
+        """One decode step for every row (base.py:89-99).  Returns (next_tokens [B] on the host, batched_kv)."""
+        eng = self.engine
+        batch: PagedBatch = batched_kv
+        for row in batch.rows:
+            if row.ctx_len + 1 > len(row.block_ids) * PAGE:
+                ids, handles = self._take_pages(1)
+                row.block_ids += ids
+                row.private_blocks += handles
+                batch.dirty = True
+        B = self._sync_table(batch)
+        tok = current_tokens.reshape(-1).to(torch.int64)
+        eng.tokens[:B].copy_(tok, non_blocking=True)
+        nxt = eng.step(B)
+        out = nxt.to("cpu")  # synchronises: the scheduler reads every row right away
+        for row in batch.rows:
+            row.ctx_len += 1
+        return out, batch
+
+    # ------------------------------------------- legacy whole-request entry points
+    def generate(self, token_ids: list[int], max_tokens: int, template_prefix_len: int = 0,
+                 session_id: str = "default") -> list[int]:
+        return list(self.stream(token_ids, max_tokens, template_prefix_len, session_id))
+
+    def stream(self, token_ids: list[int], max_tokens: int, template_prefix_len: int = 0,
+               session_id: str = "default") -> Generator[int, None, None]:
+        """Prefill then decode one sequence, yielding tokens (torch_backend.py:387-425 without the
+        model-specific thinking-channel filter)."""
+        with self._lock:
+            kv, tok, _ = self.prefill(token_ids, session_id)
+            batch = self.splice_into_batched(None, kv, kv.ctx_len)
+            try:
+                for _ in range(max_tokens):
+                    if tok in self._eos_ids:
+                        break
+                    yield tok
+                    nxt, batch = self.decode_step_batched(torch.tensor([[tok]]), batch)
+                    tok = int(nxt[0])
+            finally:
+                self.remove_row_from_cache(batch, 0)
+                if self.cache_adapter is not None:
+                    self.cache_adapter.release(token_ids, session_id=session_id)
+
+    def generate_batch(self, batch_token_ids: list[list[int]], max_tokens: list[int],
+                       session_ids: list[str] | None = None) -> list[list[int]]:
+        """Per-row prefill, batched decode (torch_backend.py:149-235)."""
+        session_ids = session_ids or ["default"] * len(batch_token_ids)
+        with self._lock:
+            batch, cur = None, []
+            for ids, sid in zip(batch_token_ids, session_ids):
+                kv, first, n = self.prefill(ids, sid)
+                batch = self.splice_into_batched(batch, kv, n)
+                cur.append(first)
+            out = [[] for _ in cur]
+            done = [False] * len(cur)
+            try:
+                for _ in range(max(max_tokens)):
+                    for i, t in enumerate(cur):
+                        if done[i]:
+                            continue
+                        if t in self._eos_ids or len(out[i]) >= max_tokens[i]:
+                            done[i] = True
+                        else:
+                            out[i].append(t)
+                    if all(done):
+                        break
+                    nxt, batch = self.decode_step_batched(torch.tensor(cur).view(-1, 1), batch)
+                    cur = [int(t) for t in nxt]
+                return out
+            finally:
+                while batch is not None and batch.rows:
+                    self.remove_row_from_cache(batch, 0)
+                if self.cache_adapter is not None:
+                    for ids, sid in zip(batch_token_ids, session_ids):
+                        self.cache_adapter.release(ids, session_id=sid)
+
+    def generate_step(self, token_ids: list[int], kv_cache=None):
+        """Single step (base.py:41-45): prefill when there is no cache, else one decode step."""
+        if kv_cache is None:
+            kv, first, n = self.prefill(token_ids)
+            return first, self.splice_into_batched(None, kv, n)
+        nxt, batch = self.decode_step_batched(torch.tensor([[token_ids[-1]]]), kv_cache)
+        return int(nxt[0]), batch
