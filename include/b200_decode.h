@@ -93,6 +93,40 @@ int b200_kv_append(const void* k_new, const void* v_new, void* k_pool, void* v_p
                    int batch, int num_kv_heads, int head_dim, int page_size, int num_blocks,
                    int max_pages_per_seq, int dtype, void* stream);
 
+/* ----------------------------------------------------- fused step glue -- */
+
+/*
+ * Replaces: the residual add and RMSNorm ops of the decoder layer inside the
+ * forward called at torch_backend.py:314-320 (statistics in fp32, eps inside the
+ * square root, normalised value rounded to bf16 before the weight multiply).
+ *
+ *   x       [num_rows, hidden] bf16 residual stream; updated in place to
+ *           x + delta when delta is not NULL
+ *   delta   [num_rows, hidden] bf16 or NULL
+ *   out     [num_rows, hidden] bf16 = weight * normalise(x)
+ */
+int b200_add_rmsnorm(void* x, const void* delta, const void* weight, float eps, int num_rows,
+                     int hidden, void* out, void* stream);
+
+/*
+ * Replaces: per-head q/k RMSNorm, rotary embedding (rotate-half) and the KV
+ * cache growth of the attention module under the same forward, writing k and v
+ * straight into their page slot (kv_cache/cache_manager.py:185-214 for prompts).
+ *
+ *   qkv        [batch, num_q_heads + 2*num_kv_heads, head_dim] bf16: q heads,
+ *              then k heads, then v heads
+ *   cos/sin    [max_positions, head_dim] bf16 tables
+ *   positions  [batch] int32 index of this step's token
+ *   q_out      [batch, num_q_heads, head_dim] bf16
+ */
+int b200_qk_norm_rope_append(const void* qkv, const void* q_norm_weight, const void* k_norm_weight,
+                             const void* cos_table, const void* sin_table,
+                             const int32_t* positions, const int32_t* block_table, void* q_out,
+                             void* k_pool, void* v_pool, void* status_word, int batch,
+                             int num_q_heads, int num_kv_heads, int head_dim, float eps,
+                             int page_size, int num_blocks, int max_pages_per_seq,
+                             int max_positions, void* stream);
+
 /* ------------------------------------------------------------------- MoE -- */
 
 /*

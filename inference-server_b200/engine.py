@@ -5,15 +5,14 @@ This is the model-forward side of the reference's hot entry
 (src/inference_server/backends/torch_backend.py:305-322), rebuilt so that a
 step reads the KV page pools in place instead of a dense left-padded cache:
 
-  per layer   RMSNorm -> fused q/k/v projection -> per-head q/k RMSNorm -> RoPE
-              -> ``b200_kv_append`` (page write) -> ``b200_paged_attn_decode``
-              -> o projection + residual -> RMSNorm -> router projection
-              -> ``b200_moe_fp8_forward`` (+ residual)
-  final       RMSNorm -> lm_head -> argmax
+  per layer   ``b200_add_rmsnorm`` (residual + RMSNorm) -> fused q/k/v projection
+              -> ``b200_qk_norm_rope_append`` (per-head q/k RMSNorm, RoPE, page write)
+              -> ``b200_paged_attn_decode`` -> o projection
+              -> ``b200_add_rmsnorm`` -> router projection -> ``b200_moe_fp8_forward``
+  final       ``b200_add_rmsnorm`` -> lm_head -> argmax
 
-The paged attention and the FP8 MoE layer are this package's CUDA kernels; the
-dense projections are library GEMMs (torch.matmul, bf16) and the small
-element-wise pieces are torch ops.  The whole step is captured once per batch
+The element-wise glue, paged attention and the FP8 MoE layer are this package's
+CUDA kernels; the dense projections are library GEMMs (torch.matmul, bf16).  The whole step is captured once per batch
 size in a CUDA graph; block table, context lengths and input tokens live in
 static device buffers that the graph reads.
 
@@ -149,43 +148,38 @@ class DecodeEngine:
                                                 self.split_tokens, self.device)
         self.moe_ws = ops.moe_fp8_workspace(max_batch, cfg.experts, cfg.top_k, cfg.hidden, cfg.moe_inter, self.device)
         self._graphs: dict[int, torch.cuda.CUDAGraph] = {}
-        self.kernel_launches_per_step = cfg.layers * (1 + 2 + 1 + 2 + 1 + 2 + 1)  # append, attn x2, route, permute x2, quant, gemm x2, combine
+        # per layer: 2 x add_rmsnorm, qk_norm_rope_append, attention x2, route, permute x2, quant, gemm x2, combine; + final norm
+        self.kernel_launches_per_step = cfg.layers * 12 + 1
 
     # ------------------------------------------------------------------ step
-    def _layer(self, x: torch.Tensor, w: LayerWeights, li: int, B: int, pos: torch.Tensor, new_len: torch.Tensor,
-               table: torch.Tensor) -> torch.Tensor:
+    def _step_eager(self, B: int) -> None:
+        """One decode step over rows [0, B) of the static buffers; advances ctx_lens by one.
+
+        Per layer: fused residual+RMSNorm, qkv GEMM, fused q/k norm + RoPE + page write, paged
+        attention, o GEMM, fused residual+RMSNorm, router GEMM, FP8 MoE.  `x` is the residual
+        stream (updated in place), `delta` the not-yet-added output of the previous block."""
         cfg = self.cfg
         D, Hq, Hkv = cfg.head_dim, cfg.q_heads, cfg.kv_heads
-        h = rms_norm(x, w.ln1, cfg.rms_eps)
-        qkv = torch.matmul(h, w.wqkv.t()).view(B, Hq + 2 * Hkv, D)
-        q = rms_norm(qkv[:, :Hq], w.q_norm, cfg.rms_eps)
-        k = rms_norm(qkv[:, Hq:Hq + Hkv], w.k_norm, cfg.rms_eps)
-        v = qkv[:, Hq + Hkv:].contiguous()
-        cos = self.cos[pos.long()].unsqueeze(1)
-        sin = self.sin[pos.long()].unsqueeze(1)
-        q = apply_rope(q, cos, sin).contiguous()
-        k = apply_rope(k, cos, sin).contiguous()
-        ops.kv_append(k, v, self.k_pools[li], self.v_pools[li], table, pos, self.attn_ws)
-        attn = ops.paged_attn_decode(q, self.k_pools[li], self.v_pools[li], table, new_len, self.scale,
-                                     self.split_tokens, self.attn_ws)
-        x = x + torch.matmul(attn.view(B, Hq * D), w.wo.t())
-        h = rms_norm(x, w.ln2, cfg.rms_eps)
-        logits = torch.matmul(h, w.router.t()).float()
-        y = ops.moe_fp8_forward(h, logits, w.w13, w.w13_scale, w.w2, w.w2_scale, cfg.top_k, cfg.norm_topk_prob,
-                                self.moe_ws)
-        return x + y
-
-    def _step_eager(self, B: int) -> None:
-        """One decode step over rows [0, B) of the static buffers; advances ctx_lens by one."""
         tokens = self.tokens[:B]
         pos = self.ctx_lens[:B]
         table = self.block_table[:B]
         new_len = pos + 1
         x = self.embed[tokens]
+        delta = None
         for li, w in enumerate(self.layers):
-            x = self._layer(x, w, li, B, pos, new_len, table)
-        x = rms_norm(x, self.final_norm, self.cfg.rms_eps)
-        self.last_logits = torch.matmul(x, self.lm_head.t())
+            h = ops.add_rmsnorm(x, delta, w.ln1, cfg.rms_eps)
+            qkv = torch.matmul(h, w.wqkv.t()).view(B, Hq + 2 * Hkv, D)
+            q = ops.qk_norm_rope_append(qkv, w.q_norm, w.k_norm, self.cos, self.sin, pos, table, self.k_pools[li],
+                                        self.v_pools[li], Hq, cfg.rms_eps, self.attn_ws)
+            attn = ops.paged_attn_decode(q, self.k_pools[li], self.v_pools[li], table, new_len, self.scale,
+                                         self.split_tokens, self.attn_ws)
+            o = torch.matmul(attn.view(B, Hq * D), w.wo.t())
+            h = ops.add_rmsnorm(x, o, w.ln2, cfg.rms_eps)
+            logits = torch.matmul(h, w.router.t()).float()
+            delta = ops.moe_fp8_forward(h, logits, w.w13, w.w13_scale, w.w2, w.w2_scale, cfg.top_k,
+                                        cfg.norm_topk_prob, self.moe_ws)
+        h = ops.add_rmsnorm(x, delta, self.final_norm, cfg.rms_eps)
+        self.last_logits = torch.matmul(h, self.lm_head.t())
         self.next_tokens[:B] = self.last_logits.argmax(dim=-1)
         self.ctx_lens[:B] += 1
 

@@ -121,6 +121,48 @@ def kv_append(k_new, v_new, k_pool, v_pool, block_table, positions, status: torc
     check(rc, "b200_kv_append")
 
 
+# ------------------------------------------------------------ fused step glue
+
+
+def add_rmsnorm(x: torch.Tensor, delta: torch.Tensor | None, weight: torch.Tensor, eps: float,
+                out: torch.Tensor | None = None) -> torch.Tensor:
+    """x += delta (in place, when given); returns weight * rmsnorm(x)."""
+    _need(x, "x", torch.bfloat16)
+    _need(weight, "weight", torch.bfloat16)
+    if delta is not None:
+        _need(delta, "delta", torch.bfloat16)
+    rows, H = x.shape
+    if out is None:
+        out = torch.empty_like(x)
+    rc = _lib.load().b200_add_rmsnorm(_ptr(x), _ptr(delta), _ptr(weight), float(eps), rows, H, _ptr(out), _stream())
+    check(rc, "b200_add_rmsnorm")
+    return out
+
+
+def qk_norm_rope_append(qkv, q_norm_w, k_norm_w, cos, sin, positions, block_table, k_pool, v_pool, num_q_heads,
+                        eps: float, status=None, q_out=None) -> torch.Tensor:
+    """Per-head q/k RMSNorm + RoPE; q returned [B, Hq, D], k and v written into their page slots."""
+    _need(qkv, "qkv", torch.bfloat16)
+    _need(cos, "cos", torch.bfloat16)
+    _need(sin, "sin", torch.bfloat16)
+    _need(positions, "positions", torch.int32)
+    _need(block_table, "block_table", torch.int32)
+    _need(k_pool, "k_pool", torch.bfloat16)
+    _need(v_pool, "v_pool", torch.bfloat16)
+    B, heads, D = qkv.shape
+    nb, Hkv, page, D2 = k_pool.shape
+    if D2 != D or heads != num_q_heads + 2 * Hkv:
+        raise ValueError("qkv does not match the pool layout")
+    if q_out is None:
+        q_out = torch.empty(B, num_q_heads, D, dtype=torch.bfloat16, device=qkv.device)
+    rc = _lib.load().b200_qk_norm_rope_append(
+        _ptr(qkv), _ptr(q_norm_w), _ptr(k_norm_w), _ptr(cos), _ptr(sin), _ptr(positions), _ptr(block_table),
+        _ptr(q_out), _ptr(k_pool), _ptr(v_pool), _ptr(status), B, num_q_heads, Hkv, D, float(eps), page, nb,
+        block_table.shape[1], cos.shape[0], _stream())
+    check(rc, "b200_qk_norm_rope_append")
+    return q_out
+
+
 # ------------------------------------------------------------------------ MoE
 
 
