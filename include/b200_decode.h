@@ -62,7 +62,10 @@ int b200_read_status(const void* status_word, void* stream);
  *   ctx_lens     [batch] int32 tokens to attend to (including this step's)
  *   out          [batch, num_q_heads, head_dim], same dtype as q
  *   workspace    b200_paged_attn_workspace_bytes(...) bytes; starts with the
- *                status word
+ *                status word; zero it once before first use (it also holds the
+ *                per-sequence arrival counters of the split fold, which every
+ *                call leaves at zero).  Calls sharing a workspace must not
+ *                overlap on the GPU.
  *   split_tokens tokens per split of the KV length, a multiple of 16
  *
  * bf16 pools with page_size 16, head_dim 64 or 128 and at most 16 q heads per
@@ -134,11 +137,12 @@ int b200_qk_norm_rope_append(const void* qkv, const void* q_norm_weight, const v
  * torch_backend.py:314-320 (fp32 softmax over experts, top-k, optional
  * renormalisation).  Ties between equal logits go to the lower expert id.
  *
- *   logits       [num_tokens, num_experts] fp32
+ *   logits       [num_tokens, num_experts], logits_dtype B200_DTYPE_F32 or
+ *                B200_DTYPE_BF16 (the router projection's own output type)
  *   topk_ids     [num_tokens, top_k] int32, value-descending
  *   topk_weights [num_tokens, top_k] fp32
  */
-int b200_moe_route(const float* logits, int num_tokens, int num_experts, int top_k,
+int b200_moe_route(const void* logits, int logits_dtype, int num_tokens, int num_experts, int top_k,
                    int renormalize, int32_t* topk_ids, float* topk_weights, void* stream);
 
 /*
@@ -161,6 +165,16 @@ int b200_moe_permute(const int32_t* topk_ids, int num_tokens, int num_experts, i
                      int32_t* sorted_pair_ids, int32_t* row_of_pair, int32_t* expert_offsets,
                      void* tiles, int32_t* num_tiles, void* workspace, size_t workspace_bytes,
                      void* stream);
+
+/*
+ * b200_moe_permute and b200_act_quant_fp8 (below) in one pass: the token rows of
+ * x [num_tokens, hidden] bf16 are quantised and written straight to their sorted
+ * rows of xq / x_scale.  Same outputs, one kernel fewer on the step's critical path.
+ */
+int b200_moe_permute_quant(const int32_t* topk_ids, const void* x, int num_tokens, int num_experts,
+                           int top_k, int hidden, int32_t* sorted_pair_ids, int32_t* row_of_pair,
+                           int32_t* expert_offsets, void* tiles, int32_t* num_tiles, void* xq,
+                           float* x_scale, void* workspace, size_t workspace_bytes, void* stream);
 
 /*
  * Replaces: the dynamic per-token activation quantisation of the FP8 expert
@@ -210,19 +224,41 @@ int b200_moe_combine(const void* y_sorted, const int32_t* row_of_pair, const flo
                      int num_tokens, int hidden, int top_k, void* out, void* stream);
 
 /*
+ * b200_moe_combine followed by b200_add_rmsnorm in one kernel: the combined
+ * expert output is rounded to bf16, added to the residual stream x (in place)
+ * and the result is normalised with `weight` into `out`.
+ */
+int b200_moe_combine_add_rmsnorm(const void* y_sorted, const int32_t* row_of_pair,
+                                 const float* topk_weights, void* x, const void* weight, float eps,
+                                 int num_tokens, int hidden, int top_k, void* out, void* stream);
+
+/*
  * The whole FP8 MoE layer for one batch of tokens: route, permute, quantise,
  * gate/up GEMM, down GEMM, combine, in that order on `stream`.
  *
- *   x [num_tokens, hidden] bf16, router_logits [num_tokens, num_experts] fp32,
- *   out [num_tokens, hidden] bf16, workspace b200_moe_fp8_workspace_bytes(...).
+ *   x [num_tokens, hidden] bf16, router_logits [num_tokens, num_experts] of
+ *   logits_dtype, out [num_tokens, hidden] bf16, workspace
+ *   b200_moe_fp8_workspace_bytes(...) bytes, 256-byte aligned, zero before first use.
+ *
+ * The _add_rmsnorm form ends with b200_moe_combine_add_rmsnorm instead of
+ * b200_moe_combine: `residual` [num_tokens, hidden] is updated in place and
+ * `normed_out` receives norm_weight * rmsnorm(residual) - the input of the next
+ * decoder layer.
  */
 size_t b200_moe_fp8_workspace_bytes(int num_tokens, int num_experts, int top_k, int hidden,
                                     int inter);
-int b200_moe_fp8_forward(const void* x, const float* router_logits, const void* w13,
+int b200_moe_fp8_forward(const void* x, const void* router_logits, int logits_dtype, const void* w13,
                          const float* w13_scale_inv, const void* w2, const float* w2_scale_inv,
                          void* out, void* workspace, size_t workspace_bytes, int num_tokens,
                          int num_experts, int top_k, int hidden, int inter, int renormalize,
                          void* stream);
+int b200_moe_fp8_forward_add_rmsnorm(const void* x, const void* router_logits, int logits_dtype,
+                                     const void* w13, const float* w13_scale_inv, const void* w2,
+                                     const float* w2_scale_inv, void* residual,
+                                     const void* norm_weight, float eps, void* normed_out,
+                                     void* workspace, size_t workspace_bytes, int num_tokens,
+                                     int num_experts, int top_k, int hidden, int inter,
+                                     int renormalize, void* stream);
 
 #ifdef __cplusplus
 }

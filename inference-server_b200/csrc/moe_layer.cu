@@ -59,12 +59,11 @@ extern "C" size_t b200_moe_fp8_workspace_bytes(int num_tokens, int num_experts, 
   return carve_moe(num_tokens, num_experts, top_k, hidden, inter).total;
 }
 
-extern "C" int b200_moe_fp8_forward(const void* x, const float* router_logits, const void* w13,
-                                    const float* w13_scale_inv, const void* w2,
-                                    const float* w2_scale_inv, void* out, void* workspace,
-                                    size_t workspace_bytes, int num_tokens, int num_experts,
-                                    int top_k, int hidden, int inter, int renormalize,
-                                    void* stream) {
+static int moe_forward_impl(const void* x, const void* router_logits, int logits_dtype, const void* w13,
+                            const float* w13_scale_inv, const void* w2, const float* w2_scale_inv,
+                            void* out, void* residual, const void* norm_weight, float eps, void* workspace,
+                            size_t workspace_bytes, int num_tokens, int num_experts, int top_k, int hidden,
+                            int inter, int renormalize, void* stream) {
   B200_REQUIRE(x && router_logits && w13 && w13_scale_inv && w2 && w2_scale_inv && out && workspace,
                "moe_fp8_forward: null pointer");
   B200_REQUIRE(num_tokens >= 0 && num_experts > 0 && top_k > 0 && hidden > 0 && inter > 0,
@@ -88,15 +87,13 @@ extern "C" int b200_moe_fp8_forward(const void* x, const float* router_logits, c
   void* status = ws;
   const int rows = num_tokens * top_k;
 
-  int rc = b200_moe_route(router_logits, num_tokens, num_experts, top_k, renormalize, topk_ids,
-                          topk_w, stream);
+  int rc = b200_moe_route(router_logits, logits_dtype, num_tokens, num_experts, top_k, renormalize,
+                          topk_ids, topk_w, stream);
   if (rc) return rc;
-  rc = b200_moe_permute(topk_ids, num_tokens, num_experts, top_k, sorted_pair, row_of_pair,
-                        expert_offsets, tiles, num_tiles, ws + c.permute_ws,
-                        b200_moe_permute_workspace_bytes(num_tokens, num_experts, top_k), stream);
-  if (rc) return rc;
-  rc = b200_act_quant_fp8(x, row_of_pair, num_tokens, hidden, top_k, ws + c.xq,
-                          reinterpret_cast<float*>(ws + c.xs), stream);
+  rc = b200_moe_permute_quant(topk_ids, x, num_tokens, num_experts, top_k, hidden, sorted_pair, row_of_pair,
+                              expert_offsets, tiles, num_tiles, ws + c.xq, reinterpret_cast<float*>(ws + c.xs),
+                              ws + c.permute_ws, b200_moe_permute_workspace_bytes(num_tokens, num_experts, top_k),
+                              stream);
   if (rc) return rc;
   rc = b200_moe_fp8_gemm_gate_up(ws + c.xq, reinterpret_cast<float*>(ws + c.xs), w13, w13_scale_inv,
                                  tiles, num_tiles, ws + c.hq, reinterpret_cast<float*>(ws + c.hs),
@@ -106,5 +103,32 @@ extern "C" int b200_moe_fp8_forward(const void* x, const float* router_logits, c
                               tiles, num_tiles, ws + c.y, status, rows, num_experts, hidden, inter,
                               stream);
   if (rc) return rc;
+  if (residual != nullptr)
+    return b200_moe_combine_add_rmsnorm(ws + c.y, row_of_pair, topk_w, residual, norm_weight, eps, num_tokens,
+                                        hidden, top_k, out, stream);
   return b200_moe_combine(ws + c.y, row_of_pair, topk_w, num_tokens, hidden, top_k, out, stream);
+}
+
+extern "C" int b200_moe_fp8_forward(const void* x, const void* router_logits, int logits_dtype,
+                                    const void* w13, const float* w13_scale_inv, const void* w2,
+                                    const float* w2_scale_inv, void* out, void* workspace,
+                                    size_t workspace_bytes, int num_tokens, int num_experts,
+                                    int top_k, int hidden, int inter, int renormalize,
+                                    void* stream) {
+  return moe_forward_impl(x, router_logits, logits_dtype, w13, w13_scale_inv, w2, w2_scale_inv, out, nullptr,
+                          nullptr, 0.f, workspace, workspace_bytes, num_tokens, num_experts, top_k, hidden, inter,
+                          renormalize, stream);
+}
+
+extern "C" int b200_moe_fp8_forward_add_rmsnorm(const void* x, const void* router_logits, int logits_dtype,
+                                                const void* w13, const float* w13_scale_inv, const void* w2,
+                                                const float* w2_scale_inv, void* residual,
+                                                const void* norm_weight, float eps, void* normed_out,
+                                                void* workspace, size_t workspace_bytes, int num_tokens,
+                                                int num_experts, int top_k, int hidden, int inter,
+                                                int renormalize, void* stream) {
+  B200_REQUIRE(residual && norm_weight && normed_out, "moe_fp8_forward_add_rmsnorm: null pointer");
+  return moe_forward_impl(x, router_logits, logits_dtype, w13, w13_scale_inv, w2, w2_scale_inv, normed_out,
+                          residual, norm_weight, eps, workspace, workspace_bytes, num_tokens, num_experts, top_k,
+                          hidden, inter, renormalize, stream);
 }

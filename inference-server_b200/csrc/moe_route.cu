@@ -25,8 +25,12 @@ namespace b200 {
 constexpr int kRouteWarps = 4;
 constexpr int kRouteMaxPerLane = 8;  // num_experts <= 256
 
+__device__ __forceinline__ float logit_f32(const float* p, size_t i) { return p[i]; }
+__device__ __forceinline__ float logit_f32(const __nv_bfloat16* p, size_t i) { return __bfloat162float(p[i]); }
+
+template <typename LT>
 __global__ void __launch_bounds__(kRouteWarps * 32)
-moe_route_kernel(const float* __restrict__ logits, int T, int E, int K, int renorm,
+moe_route_kernel(const LT* __restrict__ logits, int T, int E, int K, int renorm,
                  int* __restrict__ topk_ids, float* __restrict__ topk_w) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int t = blockIdx.x * kRouteWarps + warp;
@@ -36,7 +40,7 @@ moe_route_kernel(const float* __restrict__ logits, int T, int E, int K, int reno
 #pragma unroll
   for (int j = 0; j < kRouteMaxPerLane; ++j) {
     const int e = lane + 32 * j;
-    v[j] = e < E ? logits[static_cast<size_t>(t) * E + e] : -INFINITY;
+    v[j] = e < E ? logit_f32(logits, static_cast<size_t>(t) * E + e) : -INFINITY;
     mx = fmaxf(mx, v[j]);
   }
   mx = warp_max(mx);
@@ -200,6 +204,119 @@ __global__ void act_quant_scatter_kernel(const __nv_bfloat16* __restrict__ x,
   }
 }
 
+// Exclusive prefix sums of v[0..n) into out[0..n] (out[n] = total); n <= 1024, all threads call.
+__device__ __forceinline__ void block_exclusive_scan(const int* v, int* out, int n, int* warp_tot) {
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int nthreads = blockDim.x;
+  int carry = 0;
+  for (int base = 0; base < n; base += nthreads) {
+    const int i = base + tid;
+    const int x = i < n ? v[i] : 0;
+    int inc = x;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int y = __shfl_up_sync(0xffffffffu, inc, o);
+      if (lane >= o) inc += y;
+    }
+    if (lane == 31) warp_tot[warp] = inc;
+    __syncthreads();
+    int woff = 0, total = 0;
+    for (int w = 0; w < (nthreads + 31) / 32; ++w) {
+      const int t = warp_tot[w];
+      if (w < warp) woff += t;
+      total += t;
+    }
+    if (i < n) out[i] = carry + woff + inc - x;
+    carry += total;
+    __syncthreads();
+  }
+  if (tid == 0) out[n] = carry;
+  __syncthreads();
+}
+
+// Scatter + activation quantisation in one pass.  One CTA per token, 8 columns per
+// thread: every CTA rebuilds the expert offsets from the counts (a 128-entry scan),
+// places the token's K pairs, quantises the token row once and writes it to its K
+// sorted rows.  CTA 0 also publishes the offsets and the row tiles.
+__global__ void moe_scatter_quant_kernel(const __nv_bfloat16* __restrict__ x, const int* __restrict__ topk_ids,
+                                         const int* __restrict__ rank, const int* __restrict__ counts,
+                                         int E, int K, int H, int tile_rows, int* __restrict__ sorted_pair,
+                                         int* __restrict__ row_of_pair, int* __restrict__ expert_offsets,
+                                         MoeTile* __restrict__ tiles, int* __restrict__ num_tiles,
+                                         uint8_t* __restrict__ xq, float* __restrict__ xs,
+                                         int* __restrict__ err) {
+  extern __shared__ int sm[];  // cnt[E], off[E+1], ntile[E], toff[E+1], warp_tot[32], dst[K]
+  int* cnt = sm;
+  int* off = cnt + E;
+  int* ntile = off + E + 1;
+  int* toff = ntile + E;
+  int* warp_tot = toff + E + 1;
+  int* dst = warp_tot + 32;
+  const int t = blockIdx.x, tid = threadIdx.x;
+  for (int e = tid; e < E; e += blockDim.x) {
+    cnt[e] = counts[e];
+    ntile[e] = (cnt[e] + tile_rows - 1) / tile_rows;
+  }
+  __syncthreads();
+  block_exclusive_scan(cnt, off, E, warp_tot);
+  if (t == 0) {
+    block_exclusive_scan(ntile, toff, E, warp_tot);
+    for (int e = tid; e <= E; e += blockDim.x) expert_offsets[e] = off[e];
+    for (int e = tid; e < E; e += blockDim.x)
+      for (int j = 0; j < ntile[e]; ++j) {
+        MoeTile tl;
+        tl.expert = e;
+        tl.row0 = off[e] + j * tile_rows;
+        tl.rows = min(tile_rows, cnt[e] - j * tile_rows);
+        tl.pad = 0;
+        tiles[toff[e] + j] = tl;
+      }
+    if (tid == 0) *num_tiles = toff[E];
+  }
+  if (tid < K) {
+    const int pair = t * K + tid;
+    const int e = topk_ids[pair];
+    int d = -1;
+    if (e < 0 || e >= E) {
+      set_error(err, kErrDevBadExpert);
+    } else {
+      d = off[e] + rank[pair];
+      sorted_pair[d] = pair;
+      row_of_pair[pair] = d;
+    }
+    dst[tid] = d;
+  }
+  __syncthreads();
+
+  const uint4 raw = *reinterpret_cast<const uint4*>(x + static_cast<size_t>(t) * H + tid * 8);
+  const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
+  float f[8];
+  float amax = 0.f;
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const float2 p = __bfloat1622float2(h2[j]);
+    f[2 * j] = p.x;
+    f[2 * j + 1] = p.y;
+    amax = fmaxf(amax, fmaxf(fabsf(p.x), fabsf(p.y)));
+  }
+#pragma unroll
+  for (int o = 8; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+  const float s = amax > 0.f ? amax / 448.f : 1.f;
+  uint32_t lo = 0, hi = 0;
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    lo |= static_cast<uint32_t>(to_e4m3(f[j] / s)) << (8 * j);
+    hi |= static_cast<uint32_t>(to_e4m3(f[4 + j] / s)) << (8 * j);
+  }
+  const int groups = H / 128;
+  for (int k = 0; k < K; ++k) {
+    const int row = dst[k];
+    if (row < 0) continue;
+    *reinterpret_cast<uint2*>(xq + static_cast<size_t>(row) * H + tid * 8) = make_uint2(lo, hi);
+    if ((tid & 15) == 0) xs[static_cast<size_t>(row) * groups + (tid >> 4)] = s;
+  }
+}
+
 // ------------------------------------------------------------- combine ------
 __global__ void moe_combine_kernel(const __nv_bfloat16* __restrict__ y,
                                    const int* __restrict__ row_of_pair,
@@ -226,15 +343,69 @@ __global__ void moe_combine_kernel(const __nv_bfloat16* __restrict__ y,
   *reinterpret_cast<uint4*>(out + static_cast<size_t>(t) * H + tid * 8) = o;
 }
 
+// combine fused with the next block's residual add and RMSNorm:
+//   delta = bf16(sum_k w * y);  x = bf16(x + delta);  out = weight * rmsnorm(x)
+__global__ void moe_combine_add_rmsnorm_kernel(const __nv_bfloat16* __restrict__ y,
+                                               const int* __restrict__ row_of_pair,
+                                               const float* __restrict__ topk_w, int H, int K,
+                                               __nv_bfloat16* __restrict__ x,
+                                               const __nv_bfloat16* __restrict__ weight, float eps,
+                                               __nv_bfloat16* __restrict__ out) {
+  __shared__ float red[32];
+  const int t = blockIdx.x, tid = threadIdx.x;
+  float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+  for (int k = 0; k < K; ++k) {
+    const int row = row_of_pair[static_cast<size_t>(t) * K + k];
+    const float w = topk_w[static_cast<size_t>(t) * K + k];
+    const uint4 raw = *reinterpret_cast<const uint4*>(y + static_cast<size_t>(row) * H + tid * 8);
+    const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float2 p = __bfloat1622float2(h2[j]);
+      acc[2 * j] += w * p.x;
+      acc[2 * j + 1] += w * p.y;
+    }
+  }
+  const size_t base = static_cast<size_t>(t) * H + tid * 8;
+  uint4 xr = *reinterpret_cast<const uint4*>(x + base);
+  __nv_bfloat162* x2 = reinterpret_cast<__nv_bfloat162*>(&xr);
+  float f[8], ss = 0.f;
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    x2[j] = __hadd2(x2[j], __floats2bfloat162_rn(acc[2 * j], acc[2 * j + 1]));
+    const float2 p = __bfloat1622float2(x2[j]);
+    f[2 * j] = p.x;
+    f[2 * j + 1] = p.y;
+    ss += p.x * p.x + p.y * p.y;
+  }
+  *reinterpret_cast<uint4*>(x + base) = xr;
+  ss = warp_sum(ss);
+  if ((tid & 31) == 0) red[tid >> 5] = ss;
+  __syncthreads();
+  float tot = (tid & 31) < (blockDim.x + 31) / 32 ? red[tid & 31] : 0.f;
+  tot = warp_sum(tot);
+  const float inv = rsqrtf(tot / static_cast<float>(H) + eps);
+  const uint4 wraw = *reinterpret_cast<const uint4*>(weight + tid * 8);
+  const __nv_bfloat162* w2 = reinterpret_cast<const __nv_bfloat162*>(&wraw);
+  uint4 o;
+  __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+  for (int j = 0; j < 4; ++j)
+    o2[j] = __hmul2(w2[j], __floats2bfloat162_rn(f[2 * j] * inv, f[2 * j + 1] * inv));
+  *reinterpret_cast<uint4*>(out + base) = o;
+}
+
 }  // namespace b200
 
 using namespace b200;
 
-extern "C" int b200_moe_route(const float* logits, int num_tokens, int num_experts, int top_k,
-                              int renormalize, int32_t* topk_ids, float* topk_weights,
+extern "C" int b200_moe_route(const void* logits, int logits_dtype, int num_tokens, int num_experts,
+                              int top_k, int renormalize, int32_t* topk_ids, float* topk_weights,
                               void* stream) {
   B200_REQUIRE(logits && topk_ids && topk_weights, "moe_route: null pointer");
   B200_REQUIRE(num_tokens >= 0, "moe_route: negative token count");
+  B200_REQUIRE(logits_dtype == 0 || logits_dtype == 1, "moe_route: logits dtype %d is neither 0 (bf16) nor 1 (f32)",
+               logits_dtype);
   B200_REQUIRE(num_experts > 0 && num_experts <= 32 * kRouteMaxPerLane,
                "moe_route: num_experts %d outside [1, %d]", num_experts, 32 * kRouteMaxPerLane);
   B200_REQUIRE(top_k > 0 && top_k <= 32 && top_k <= num_experts,
@@ -243,8 +414,13 @@ extern "C" int b200_moe_route(const float* logits, int num_tokens, int num_exper
   if (rc) return rc;
   if (num_tokens == 0) return 0;
   const int blocks = (num_tokens + kRouteWarps - 1) / kRouteWarps;
-  moe_route_kernel<<<blocks, kRouteWarps * 32, 0, as_stream(stream)>>>(
-      logits, num_tokens, num_experts, top_k, renormalize, topk_ids, topk_weights);
+  if (logits_dtype == 1)
+    moe_route_kernel<float><<<blocks, kRouteWarps * 32, 0, as_stream(stream)>>>(
+        static_cast<const float*>(logits), num_tokens, num_experts, top_k, renormalize, topk_ids, topk_weights);
+  else
+    moe_route_kernel<__nv_bfloat16><<<blocks, kRouteWarps * 32, 0, as_stream(stream)>>>(
+        static_cast<const __nv_bfloat16*>(logits), num_tokens, num_experts, top_k, renormalize, topk_ids,
+        topk_weights);
   B200_CUDA(cudaGetLastError());
   return 0;
 }
@@ -292,6 +468,66 @@ extern "C" int b200_moe_permute(const int32_t* topk_ids, int num_tokens, int num
   moe_scatter_kernel<<<blocks, kScatterThreads, (2 * num_experts + 1) * sizeof(int), st>>>(
       topk_ids, rank, counts, n_pairs, num_experts, 128, sorted_pair_ids, row_of_pair,
       expert_offsets, static_cast<MoeTile*>(tiles), num_tiles, err);
+  B200_CUDA(cudaGetLastError());
+  return 0;
+}
+
+extern "C" int b200_moe_permute_quant(const int32_t* topk_ids, const void* x, int num_tokens,
+                                      int num_experts, int top_k, int hidden, int32_t* sorted_pair_ids,
+                                      int32_t* row_of_pair, int32_t* expert_offsets, void* tiles,
+                                      int32_t* num_tiles, void* xq, float* x_scale, void* workspace,
+                                      size_t workspace_bytes, void* stream) {
+  B200_REQUIRE(topk_ids && x && sorted_pair_ids && row_of_pair && expert_offsets && tiles && num_tiles && xq &&
+                   x_scale && workspace,
+               "moe_permute_quant: null pointer");
+  B200_REQUIRE(num_tokens >= 0 && num_experts > 0 && num_experts <= 1024 && top_k > 0,
+               "moe_permute_quant: bad dimensions T=%d E=%d K=%d", num_tokens, num_experts, top_k);
+  B200_REQUIRE(hidden > 0 && hidden % 256 == 0 && hidden <= 8192 && top_k <= hidden / 8,
+               "moe_permute_quant: hidden %d must be a multiple of 256, <= 8192 and >= 8 * top_k", hidden);
+  B200_REQUIRE((reinterpret_cast<uintptr_t>(x) & 15) == 0 && (reinterpret_cast<uintptr_t>(xq) & 7) == 0,
+               "moe_permute_quant: x must be 16-byte and xq 8-byte aligned");
+  const size_t need = b200_moe_permute_workspace_bytes(num_tokens, num_experts, top_k);
+  if (workspace_bytes < need) {
+    set_detail("moe_permute_quant: workspace %zu < required %zu", workspace_bytes, need);
+    return -kErrWorkspace;
+  }
+  int rc = check_device(nullptr);
+  if (rc) return rc;
+  if (num_tokens == 0) return 0;
+  cudaStream_t st = as_stream(stream);
+  uint8_t* p = static_cast<uint8_t*>(workspace);
+  int* err = reinterpret_cast<int*>(p);
+  int* counts = reinterpret_cast<int*>(p + 256);
+  int* rank = reinterpret_cast<int*>(p + 256 + ((static_cast<size_t>(num_experts) * 4 + 255) & ~size_t(255)));
+  moe_rank_kernel<<<num_experts, kRankThreads, 0, st>>>(topk_ids, num_tokens * top_k, rank, counts);
+  B200_CUDA(cudaGetLastError());
+  const size_t smem = (4 * static_cast<size_t>(num_experts) + 2 + 32 + top_k) * sizeof(int);
+  moe_scatter_quant_kernel<<<num_tokens, hidden / 8, smem, st>>>(
+      static_cast<const __nv_bfloat16*>(x), topk_ids, rank, counts, num_experts, top_k, hidden, 128,
+      sorted_pair_ids, row_of_pair, expert_offsets, static_cast<MoeTile*>(tiles), num_tiles,
+      static_cast<uint8_t*>(xq), x_scale, err);
+  B200_CUDA(cudaGetLastError());
+  return 0;
+}
+
+extern "C" int b200_moe_combine_add_rmsnorm(const void* y_sorted, const int32_t* row_of_pair,
+                                            const float* topk_weights, void* x, const void* weight,
+                                            float eps, int num_tokens, int hidden, int top_k, void* out,
+                                            void* stream) {
+  B200_REQUIRE(y_sorted && row_of_pair && topk_weights && x && weight && out,
+               "moe_combine_add_rmsnorm: null pointer");
+  B200_REQUIRE(num_tokens >= 0 && hidden > 0 && hidden % 256 == 0 && hidden <= 8192 && top_k > 0,
+               "moe_combine_add_rmsnorm: bad dimensions T=%d H=%d K=%d", num_tokens, hidden, top_k);
+  B200_REQUIRE(((reinterpret_cast<uintptr_t>(y_sorted) | reinterpret_cast<uintptr_t>(x) |
+                 reinterpret_cast<uintptr_t>(weight) | reinterpret_cast<uintptr_t>(out)) & 15) == 0,
+               "moe_combine_add_rmsnorm: buffers must be 16-byte aligned");
+  int rc = check_device(nullptr);
+  if (rc) return rc;
+  if (num_tokens == 0) return 0;
+  moe_combine_add_rmsnorm_kernel<<<num_tokens, hidden / 8, 0, as_stream(stream)>>>(
+      static_cast<const __nv_bfloat16*>(y_sorted), row_of_pair, topk_weights, hidden, top_k,
+      static_cast<__nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(weight), eps,
+      static_cast<__nv_bfloat16*>(out));
   B200_CUDA(cudaGetLastError());
   return 0;
 }

@@ -22,8 +22,12 @@
 //   math  = consumer warp w owns kv head w: S = Q K^T with mma.sync m16n8k16
 //           (rows = the <=16 query heads of the kv group), online softmax in
 //           fp32 with quad shuffles, O += P V.  Warps never exchange data.
-//   out   = each warp writes one fp32 partial (o, m, l) per (sequence, q head,
-//           split); a second kernel folds the splits in fixed order -> bf16.
+//   out   = a sequence that fits one split is normalised and written as bf16
+//           straight from registers.  Otherwise each warp writes one fp32
+//           partial (o, m, l) per (sequence, q head, split) and bumps the
+//           sequence's arrival counter; the CTA that completes the count folds
+//           the splits in split order and writes bf16 (no second kernel, no
+//           waiting; the fold order does not depend on which CTA does it).
 // The kernel is HBM-bound: per token and kv head it reads 2*D*2 bytes once.
 //
 // Generic kernel: any head_dim <= 256, any page size, fp32 or bf16 pools, no
@@ -61,10 +65,12 @@ paged_attn_decode_kernel(const __grid_constant__ CUtensorMap k_map,
                          const int* __restrict__ block_table,
                          const int* __restrict__ ctx_lens,
                          float* __restrict__ part_o, float2* __restrict__ part_ml,
+                         int* __restrict__ done, __nv_bfloat16* __restrict__ out,
                          int* __restrict__ err, int num_q_heads, int num_blocks, int max_pages,
                          int split_tokens, int max_splits, float scale_log2) {
 #ifdef B200_DEVICE_OK
   using Cfg = AttnCfg<D, HKV, STAGES, CTAS>;
+  __shared__ int last_flag;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t ring = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const uint32_t bars = ring + Cfg::kRingBytes;  // full[STAGES], empty[STAGES]
@@ -79,7 +85,12 @@ paged_attn_decode_kernel(const __grid_constant__ CUtensorMap k_map,
     L = L < 0 ? 0 : max_pages * kPage;
   }
   const int start = split * split_tokens;
-  if (start >= L) return;  // uniform for the whole CTA
+  if (start >= L) {  // uniform for the whole CTA
+    if (L == 0 && split == 0)  // a row with no context attends to nothing: zeros
+      for (int i = threadIdx.x; i < num_q_heads * D; i += blockDim.x)
+        out[static_cast<size_t>(b) * num_q_heads * D + i] = __float2bfloat16(0.f);
+    return;
+  }
   const int end = min(L, start + split_tokens);
   const int npages = (end - start + kPage - 1) / kPage;
   const int first_page = start / kPage;
@@ -249,6 +260,21 @@ paged_attn_decode_kernel(const __grid_constant__ CUtensorMap k_map,
   l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
   l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
 
+  const int nsplits = (L + split_tokens - 1) / split_tokens;  // CTAs working on this sequence
+  if (nsplits == 1) {
+    // The whole sequence was this CTA's: normalise and write the result, no partials.
+    const float i0 = 1.f / l0, i1 = hi_rows ? 1.f / l1 : 0.f;
+    __nv_bfloat16* o0 = out + (static_cast<size_t>(b) * num_q_heads + kvh * group + gq) * D;
+    __nv_bfloat16* o1 = o0 + static_cast<size_t>(8) * D;
+#pragma unroll
+    for (int n = 0; n < D / 8; ++n) {
+      const int d = n * 8 + 2 * tq;
+      if (gq < group) *reinterpret_cast<uint32_t*>(o0 + d) = pack_bf16x2(o[n][0] * i0, o[n][1] * i0);
+      if (gq + 8 < group) *reinterpret_cast<uint32_t*>(o1 + d) = pack_bf16x2(o[n][2] * i1, o[n][3] * i1);
+    }
+    return;
+  }
+
   // Each warp owns its kv head's query rows: write the split partial directly.
   const size_t row0 = (static_cast<size_t>(b) * num_q_heads + kvh * group + gq) * max_splits + split;
   const size_t row1 = row0 + static_cast<size_t>(8) * max_splits;
@@ -262,30 +288,33 @@ paged_attn_decode_kernel(const __grid_constant__ CUtensorMap k_map,
     if (gq < group) part_ml[row0] = make_float2(m0, l0);
     if (gq + 8 < group) part_ml[row1] = make_float2(m1, l1);
   }
-#endif
-}
 
-// Folds the per-split partials of one (sequence, q head) in split order.
-__global__ void paged_attn_reduce_kernel(const float* __restrict__ part_o,
-                                         const float2* __restrict__ part_ml,
-                                         const int* __restrict__ ctx_lens,
-                                         __nv_bfloat16* __restrict__ out, int num_q_heads, int D,
-                                         int max_splits, int split_tokens, int max_ctx) {
-  const int h = blockIdx.x, b = blockIdx.y, d = threadIdx.x;
-  int L = ctx_lens[b];
-  L = L < 0 ? 0 : (L > max_ctx ? max_ctx : L);
-  const int n = (L + split_tokens - 1) / split_tokens;
-  const size_t row = (static_cast<size_t>(b) * num_q_heads + h) * max_splits;
-  float mmax = -INFINITY;
-  for (int s = 0; s < n; ++s) mmax = fmaxf(mmax, part_ml[row + s].x);
-  float acc = 0.f, den = 0.f;
-  for (int s = 0; s < n; ++s) {
-    const float2 ml = part_ml[row + s];
-    const float w = exp2f(ml.x - mmax);
-    den += w * ml.y;
-    acc += w * part_o[(row + s) * D + d];
+  // Split fold without a second kernel and without waiting: every CTA of a
+  // sequence bumps a counter after its partials are visible; the one that sees
+  // the count complete folds all splits in split order (so the result does not
+  // depend on which CTA that is) and re-arms the counter for the next launch.
+  __threadfence();
+  asm volatile("bar.sync 1, %0;" ::"r"(HKV * 32) : "memory");
+  if (threadIdx.x == 0) last_flag = atomicAdd(done + b, 1) == nsplits - 1;
+  asm volatile("bar.sync 1, %0;" ::"r"(HKV * 32) : "memory");
+  if (!last_flag) return;
+  __threadfence();
+  if (threadIdx.x == 0) done[b] = 0;
+  for (int idx = threadIdx.x; idx < num_q_heads * D; idx += HKV * 32) {
+    const int h = idx / D, d = idx % D;
+    const size_t row = (static_cast<size_t>(b) * num_q_heads + h) * max_splits;
+    float mmax = -INFINITY;
+    for (int s = 0; s < nsplits; ++s) mmax = fmaxf(mmax, __ldcg(&part_ml[row + s].x));
+    float acc = 0.f, den = 0.f;
+    for (int s = 0; s < nsplits; ++s) {
+      const float2 ml = __ldcg(&part_ml[row + s]);
+      const float wgt = exp2f(ml.x - mmax);
+      den += wgt * ml.y;
+      acc += wgt * __ldcg(&part_o[(row + s) * D + d]);
+    }
+    out[(static_cast<size_t>(b) * num_q_heads + h) * D + d] = __float2bfloat16(acc / den);
   }
-  out[(static_cast<size_t>(b) * num_q_heads + h) * D + d] = __float2bfloat16(n > 0 ? acc / den : 0.f);
+#endif
 }
 
 // ------------------------------------------------------------ generic path --
@@ -411,6 +440,7 @@ __global__ void kv_append_kernel(const T* __restrict__ k_new, const T* __restric
 // ------------------------------------------------------------------ launch --
 struct AttnWorkspace {
   int* err;
+  int* done;  // [batch] arrival counters of the split fold; zero between launches
   float2* ml;
   float* o;
   size_t bytes;
@@ -425,6 +455,8 @@ static AttnWorkspace carve(void* ws, int batch, int hq, int D, int max_splits) {
   uint8_t* p = static_cast<uint8_t*>(ws);
   w.err = reinterpret_cast<int*>(p);
   size_t off = 256;
+  w.done = reinterpret_cast<int*>(p + off);
+  off += (static_cast<size_t>(batch) * sizeof(int) + 255) & ~size_t(255);
   w.ml = reinterpret_cast<float2*>(p + off);
   off += (static_cast<size_t>(batch) * hq * max_splits * sizeof(float2) + 255) & ~size_t(255);
   w.o = reinterpret_cast<float*>(p + off);
@@ -456,12 +488,8 @@ static int launch_main(const void* q, const void* k_pool, const void* v_pool,
   dim3 grid(batch, max_splits);
   const float scale_log2 = scale * 1.4426950408889634f;
   paged_attn_decode_kernel<D, HKV, STAGES, CTAS><<<grid, Cfg::kThreads, Cfg::kSmemBytes, stream>>>(
-      kmap, vmap, static_cast<const __nv_bfloat16*>(q), block_table, ctx_lens, w.o, w.ml, w.err, hq,
-      num_blocks, max_pages, split_tokens, max_splits, scale_log2);
-  B200_CUDA(cudaGetLastError());
-  paged_attn_reduce_kernel<<<dim3(hq, batch), D, 0, stream>>>(
-      w.o, w.ml, ctx_lens, static_cast<__nv_bfloat16*>(out), hq, D, max_splits, split_tokens,
-      max_pages * kPage);
+      kmap, vmap, static_cast<const __nv_bfloat16*>(q), block_table, ctx_lens, w.o, w.ml, w.done,
+      static_cast<__nv_bfloat16*>(out), w.err, hq, num_blocks, max_pages, split_tokens, max_splits, scale_log2);
   B200_CUDA(cudaGetLastError());
   return 0;
 }

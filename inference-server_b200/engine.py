@@ -5,11 +5,13 @@ This is the model-forward side of the reference's hot entry
 (src/inference_server/backends/torch_backend.py:305-322), rebuilt so that a
 step reads the KV page pools in place instead of a dense left-padded cache:
 
-  per layer   ``b200_add_rmsnorm`` (residual + RMSNorm) -> fused q/k/v projection
+  per layer   fused q/k/v projection
               -> ``b200_qk_norm_rope_append`` (per-head q/k RMSNorm, RoPE, page write)
               -> ``b200_paged_attn_decode`` -> o projection
-              -> ``b200_add_rmsnorm`` -> router projection -> ``b200_moe_fp8_forward``
-  final       ``b200_add_rmsnorm`` -> lm_head -> argmax
+              -> ``b200_add_rmsnorm`` (residual + RMSNorm) -> router projection
+              -> ``b200_moe_fp8_forward_add_rmsnorm`` (route, permute+quantise, two
+                 grouped GEMMs, combine + residual + the next layer's input norm)
+  final       lm_head -> argmax
 
 The element-wise glue, paged attention and the FP8 MoE layer are this package's
 CUDA kernels; the dense projections are library GEMMs (torch.matmul, bf16).  The whole step is captured once per batch
@@ -148,16 +150,16 @@ class DecodeEngine:
                                                 self.split_tokens, self.device)
         self.moe_ws = ops.moe_fp8_workspace(max_batch, cfg.experts, cfg.top_k, cfg.hidden, cfg.moe_inter, self.device)
         self._graphs: dict[int, torch.cuda.CUDAGraph] = {}
-        # per layer: 2 x add_rmsnorm, qk_norm_rope_append, attention x2, route, permute x2, quant, gemm x2, combine; + final norm
-        self.kernel_launches_per_step = cfg.layers * 12 + 1
+        # per layer: qk_norm_rope_append, attention, add_rmsnorm, route, rank, scatter+quant, gemm x2, combine+norm; + first norm
+        self.kernel_launches_per_step = cfg.layers * 9 + 1
 
     # ------------------------------------------------------------------ step
     def _step_eager(self, B: int) -> None:
         """One decode step over rows [0, B) of the static buffers; advances ctx_lens by one.
 
-        Per layer: fused residual+RMSNorm, qkv GEMM, fused q/k norm + RoPE + page write, paged
-        attention, o GEMM, fused residual+RMSNorm, router GEMM, FP8 MoE.  `x` is the residual
-        stream (updated in place), `delta` the not-yet-added output of the previous block."""
+        Per layer: qkv GEMM, fused q/k norm + RoPE + page write, paged attention, o GEMM, fused
+        residual+RMSNorm, router GEMM, FP8 MoE whose combine adds into the residual stream `x`
+        (in place) and applies the next layer's input norm."""
         cfg = self.cfg
         D, Hq, Hkv = cfg.head_dim, cfg.q_heads, cfg.kv_heads
         tokens = self.tokens[:B]
@@ -165,20 +167,20 @@ class DecodeEngine:
         table = self.block_table[:B]
         new_len = pos + 1
         x = self.embed[tokens]
-        delta = None
+        h = ops.add_rmsnorm(x, None, self.layers[0].ln1, cfg.rms_eps)
         for li, w in enumerate(self.layers):
-            h = ops.add_rmsnorm(x, delta, w.ln1, cfg.rms_eps)
             qkv = torch.matmul(h, w.wqkv.t()).view(B, Hq + 2 * Hkv, D)
             q = ops.qk_norm_rope_append(qkv, w.q_norm, w.k_norm, self.cos, self.sin, pos, table, self.k_pools[li],
                                         self.v_pools[li], Hq, cfg.rms_eps, self.attn_ws)
             attn = ops.paged_attn_decode(q, self.k_pools[li], self.v_pools[li], table, new_len, self.scale,
                                          self.split_tokens, self.attn_ws)
             o = torch.matmul(attn.view(B, Hq * D), w.wo.t())
-            h = ops.add_rmsnorm(x, o, w.ln2, cfg.rms_eps)
-            logits = torch.matmul(h, w.router.t()).float()
-            delta = ops.moe_fp8_forward(h, logits, w.w13, w.w13_scale, w.w2, w.w2_scale, cfg.top_k,
-                                        cfg.norm_topk_prob, self.moe_ws)
-        h = ops.add_rmsnorm(x, delta, self.final_norm, cfg.rms_eps)
+            h2 = ops.add_rmsnorm(x, o, w.ln2, cfg.rms_eps)
+            logits = torch.matmul(h2, w.router.t())  # bf16, routed as is
+            nxt = self.layers[li + 1].ln1 if li + 1 < len(self.layers) else self.final_norm
+            # MoE layer; its combine also adds into the residual stream and applies the next norm
+            h = ops.moe_fp8_forward(h2, logits, w.w13, w.w13_scale, w.w2, w.w2_scale, cfg.top_k, cfg.norm_topk_prob,
+                                    self.moe_ws, residual=x, norm_weight=nxt, eps=cfg.rms_eps)
         self.last_logits = torch.matmul(h, self.lm_head.t())
         self.next_tokens[:B] = self.last_logits.argmax(dim=-1)
         self.ctx_lens[:B] += 1

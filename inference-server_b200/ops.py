@@ -167,12 +167,15 @@ def qk_norm_rope_append(qkv, q_norm_w, k_norm_w, cos, sin, positions, block_tabl
 
 
 def moe_route(logits: torch.Tensor, top_k: int, renormalize: bool = True):
-    """fp32 softmax top-k routing. Returns (ids [T,K] int32, weights [T,K] fp32)."""
-    _need(logits, "logits", torch.float32)
+    """fp32 softmax top-k routing on fp32 or bf16 logits. Returns (ids [T,K] int32, weights [T,K] fp32)."""
+    _need(logits, "logits")
+    if logits.dtype not in DTYPE_CODE:
+        raise ValueError(f"logits must be float32 or bfloat16, got {logits.dtype}")
     T, E = logits.shape
     ids = torch.empty(T, top_k, dtype=torch.int32, device=logits.device)
     w = torch.empty(T, top_k, dtype=torch.float32, device=logits.device)
-    rc = _lib.load().b200_moe_route(_ptr(logits), T, E, top_k, int(renormalize), _ptr(ids), _ptr(w), _stream())
+    rc = _lib.load().b200_moe_route(_ptr(logits), DTYPE_CODE[logits.dtype], T, E, top_k, int(renormalize), _ptr(ids),
+                                    _ptr(w), _stream())
     check(rc, "b200_moe_route")
     return ids, w
 
@@ -202,6 +205,31 @@ def moe_permute(topk_ids: torch.Tensor, num_experts: int) -> Permutation:
     )
     check(rc, "b200_moe_permute")
     return p
+
+
+def moe_permute_quant(topk_ids: torch.Tensor, x: torch.Tensor, num_experts: int):
+    """moe_permute + act_quant_fp8 in one pass. Returns (Permutation, xq, x_scale)."""
+    _need(topk_ids, "topk_ids", torch.int32)
+    _need(x, "x", torch.bfloat16)
+    T, K = topk_ids.shape
+    H = x.shape[1]
+    lib = _lib.load()
+    dev = x.device
+    p = Permutation()
+    p.sorted_pair_ids = torch.empty(T * K, dtype=torch.int32, device=dev)
+    p.row_of_pair = torch.empty(T * K, dtype=torch.int32, device=dev)
+    p.expert_offsets = torch.empty(num_experts + 1, dtype=torch.int32, device=dev)
+    p.tiles = torch.zeros(max(1, lib.b200_moe_max_tiles(T, num_experts, K)), 4, dtype=torch.int32, device=dev)
+    p.num_tiles = torch.zeros(1, dtype=torch.int32, device=dev)
+    p.workspace = torch.zeros(lib.b200_moe_permute_workspace_bytes(T, num_experts, K), dtype=torch.uint8, device=dev)
+    xq = torch.empty(T * K, H, dtype=torch.uint8, device=dev)
+    xs = torch.empty(T * K, H // 128, dtype=torch.float32, device=dev)
+    rc = lib.b200_moe_permute_quant(
+        _ptr(topk_ids), _ptr(x), T, num_experts, K, H, _ptr(p.sorted_pair_ids), _ptr(p.row_of_pair),
+        _ptr(p.expert_offsets), _ptr(p.tiles), _ptr(p.num_tiles), _ptr(xq), _ptr(xs), _ptr(p.workspace),
+        p.workspace.numel(), _stream())
+    check(rc, "b200_moe_permute_quant")
+    return p, xq, xs
 
 
 def act_quant_fp8(x: torch.Tensor, row_of_pair: torch.Tensor | None = None, top_k: int = 1):
@@ -276,17 +304,39 @@ def moe_combine(y_sorted, row_of_pair, topk_weights):
     return out
 
 
+def moe_combine_add_rmsnorm(y_sorted, row_of_pair, topk_weights, x, weight, eps: float, out=None):
+    """x += bf16(sum_k w * y) in place; returns weight * rmsnorm(x)."""
+    _need(y_sorted, "y_sorted", torch.bfloat16)
+    _need(row_of_pair, "row_of_pair", torch.int32)
+    _need(topk_weights, "topk_weights", torch.float32)
+    _need(x, "x", torch.bfloat16)
+    _need(weight, "weight", torch.bfloat16)
+    T, K = topk_weights.shape
+    H = y_sorted.shape[1]
+    if out is None:
+        out = torch.empty_like(x)
+    rc = _lib.load().b200_moe_combine_add_rmsnorm(_ptr(y_sorted), _ptr(row_of_pair), _ptr(topk_weights), _ptr(x),
+                                                  _ptr(weight), float(eps), T, H, K, _ptr(out), _stream())
+    check(rc, "b200_moe_combine_add_rmsnorm")
+    return out
+
+
 def moe_fp8_workspace(num_tokens, num_experts, top_k, hidden, inter, device):
     n = _lib.load().b200_moe_fp8_workspace_bytes(num_tokens, num_experts, top_k, hidden, inter)
     return torch.zeros(n, dtype=torch.uint8, device=device)
 
 
 def moe_fp8_forward(x, router_logits, w13, w13_scale_inv, w2, w2_scale_inv, top_k, renormalize=True,
-                    workspace=None, out=None):
-    """The whole FP8 MoE layer on one stream: route, permute, quantise, two grouped GEMMs, combine."""
+                    workspace=None, out=None, residual=None, norm_weight=None, eps: float = 1e-6):
+    """The whole FP8 MoE layer on one stream: route, permute+quantise, two grouped GEMMs, combine.
+
+    With `residual` and `norm_weight` the combine is fused with the next residual add and RMSNorm:
+    `residual` is updated in place and the returned tensor is norm_weight * rmsnorm(residual)."""
     w13, w2 = _as_u8(w13), _as_u8(w2)
     _need(x, "x", torch.bfloat16)
-    _need(router_logits, "router_logits", torch.float32)
+    _need(router_logits, "router_logits")
+    if router_logits.dtype not in DTYPE_CODE:
+        raise ValueError(f"router_logits must be float32 or bfloat16, got {router_logits.dtype}")
     _need(w13, "w13", torch.uint8)
     _need(w2, "w2", torch.uint8)
     _need(w13_scale_inv, "w13_scale_inv", torch.float32)
@@ -298,9 +348,19 @@ def moe_fp8_forward(x, router_logits, w13, w13_scale_inv, w2, w2_scale_inv, top_
         workspace = moe_fp8_workspace(T, E, top_k, H, inter, x.device)
     if out is None:
         out = torch.empty_like(x)
-    rc = _lib.load().b200_moe_fp8_forward(
-        _ptr(x), _ptr(router_logits), _ptr(w13), _ptr(w13_scale_inv), _ptr(w2), _ptr(w2_scale_inv),
-        _ptr(out), _ptr(workspace), workspace.numel(), T, E, top_k, H, inter, int(renormalize), _stream(),
-    )
-    check(rc, "b200_moe_fp8_forward")
+    lib = _lib.load()
+    ld = DTYPE_CODE[router_logits.dtype]
+    if residual is None:
+        rc = lib.b200_moe_fp8_forward(
+            _ptr(x), _ptr(router_logits), ld, _ptr(w13), _ptr(w13_scale_inv), _ptr(w2), _ptr(w2_scale_inv),
+            _ptr(out), _ptr(workspace), workspace.numel(), T, E, top_k, H, inter, int(renormalize), _stream())
+        check(rc, "b200_moe_fp8_forward")
+    else:
+        _need(residual, "residual", torch.bfloat16)
+        _need(norm_weight, "norm_weight", torch.bfloat16)
+        rc = lib.b200_moe_fp8_forward_add_rmsnorm(
+            _ptr(x), _ptr(router_logits), ld, _ptr(w13), _ptr(w13_scale_inv), _ptr(w2), _ptr(w2_scale_inv),
+            _ptr(residual), _ptr(norm_weight), float(eps), _ptr(out), _ptr(workspace), workspace.numel(), T, E,
+            top_k, H, inter, int(renormalize), _stream())
+        check(rc, "b200_moe_fp8_forward_add_rmsnorm")
     return out

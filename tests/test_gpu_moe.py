@@ -84,6 +84,50 @@ def test_permute_skewed_routing_all_tokens_to_one_expert(ops):
     np.testing.assert_array_equal(p.tiles.cpu().numpy()[:n], r["tiles"])
 
 
+def test_route_bf16_logits_same_as_their_fp32_values(ops):
+    logits = torch.randn(300, 128, generator=torch.Generator().manual_seed(9)).bfloat16()  # many ties in bf16
+    ids, w = ops.moe_route(logits.to(DEV), 8, True)
+    rid, rw = oracle.route_ref(logits.float(), 8, True)
+    assert torch.equal(ids.cpu(), rid)
+    np.testing.assert_allclose(w.cpu().numpy(), rw.numpy(), rtol=3e-6, atol=1e-9)
+
+
+@pytest.mark.parametrize("T,E,K,H", [(1, 128, 8, 2048), (256, 128, 8, 2048), (1024, 128, 8, 2048), (33, 16, 4, 512)])
+def test_permute_quant_fused_bit_exact(ops, T, E, K, H):
+    g = torch.Generator().manual_seed(T + H)
+    logits = torch.randn(T, E, generator=g)
+    x = (torch.randn(T, H, generator=g) * 2).bfloat16()
+    ids, _ = oracle.route_ref(logits, K, True)
+    p, xq, xs = ops.moe_permute_quant(ids.to(DEV), x.to(DEV), E)
+    ops.read_status(p.workspace, "moe_permute_quant")
+    r = oracle.permute_ref(ids, E)
+    np.testing.assert_array_equal(p.sorted_pair_ids.cpu().numpy(), r["sorted_pair_ids"])
+    np.testing.assert_array_equal(p.row_of_pair.cpu().numpy(), r["row_of_pair"])
+    np.testing.assert_array_equal(p.expert_offsets.cpu().numpy(), r["expert_offsets"])
+    n = int(p.num_tiles.item())
+    assert n == len(r["tiles"])
+    np.testing.assert_array_equal(p.tiles.cpu().numpy()[:n], r["tiles"])
+    rq, rs = oracle.act_quant_ref(x)
+    tok = torch.from_numpy(r["sorted_pair_ids"]).long() // K
+    assert torch.equal(xq.cpu(), rq.view(torch.uint8)[tok])
+    assert torch.equal(xs.cpu(), rs[tok])
+
+
+def test_combine_add_rmsnorm_matches_unfused(ops):
+    g = torch.Generator().manual_seed(3)
+    T, K, H = 64, 8, 2048
+    y = torch.randn(T * K, H, generator=g).bfloat16().to(DEV)
+    rop = torch.randperm(T * K, generator=g).to(torch.int32).to(DEV)
+    w = torch.rand(T, K, generator=g).to(DEV)
+    x = torch.randn(T, H, generator=g).bfloat16().to(DEV)
+    nw = (1 + 0.1 * torch.randn(H, generator=g)).bfloat16().to(DEV)
+    x1, x2 = x.clone(), x.clone()
+    delta = ops.moe_combine(y, rop, w)
+    h1 = ops.add_rmsnorm(x1, delta, nw, 1e-6)
+    h2 = ops.moe_combine_add_rmsnorm(y, rop, w, x2, nw, 1e-6)
+    assert torch.equal(x1, x2) and torch.equal(h1, h2)  # same arithmetic, same bits
+
+
 def test_act_quant_bit_exact(ops):
     x = (torch.randn(37, 2048, generator=torch.Generator().manual_seed(0)) * 3).bfloat16()
     x[5, 128:256] = 0
