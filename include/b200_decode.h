@@ -62,10 +62,8 @@ int b200_read_status(const void* status_word, void* stream);
  *   ctx_lens     [batch] int32 tokens to attend to (including this step's)
  *   out          [batch, num_q_heads, head_dim], same dtype as q
  *   workspace    b200_paged_attn_workspace_bytes(...) bytes; starts with the
- *                status word; zero it once before first use (it also holds the
- *                per-sequence arrival counters of the split fold, which every
- *                call leaves at zero).  Calls sharing a workspace must not
- *                overlap on the GPU.
+ *                status word, then the per-split partial results.  Calls
+ *                sharing a workspace must not overlap on the GPU.
  *   split_tokens tokens per split of the KV length, a multiple of 16
  *
  * bf16 pools with page_size 16, head_dim 64 or 128 and at most 16 q heads per

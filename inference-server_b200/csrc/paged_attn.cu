@@ -24,10 +24,8 @@
 //           fp32 with quad shuffles, O += P V.  Warps never exchange data.
 //   out   = a sequence that fits one split is normalised and written as bf16
 //           straight from registers.  Otherwise each warp writes one fp32
-//           partial (o, m, l) per (sequence, q head, split) and bumps the
-//           sequence's arrival counter; the CTA that completes the count folds
-//           the splits in split order and writes bf16 (no second kernel, no
-//           waiting; the fold order does not depend on which CTA does it).
+//           partial (o, m, l) per (sequence, q head, split) and a second, small
+//           kernel folds the splits in split order and writes bf16.
 // The kernel is HBM-bound: per token and kv head it reads 2*D*2 bytes once.
 //
 // Generic kernel: any head_dim <= 256, any page size, fp32 or bf16 pools, no
@@ -65,12 +63,11 @@ paged_attn_decode_kernel(const __grid_constant__ CUtensorMap k_map,
                          const int* __restrict__ block_table,
                          const int* __restrict__ ctx_lens,
                          float* __restrict__ part_o, float2* __restrict__ part_ml,
-                         int* __restrict__ done, __nv_bfloat16* __restrict__ out,
+                         __nv_bfloat16* __restrict__ out,
                          int* __restrict__ err, int num_q_heads, int num_blocks, int max_pages,
                          int split_tokens, int max_splits, float scale_log2) {
 #ifdef B200_DEVICE_OK
   using Cfg = AttnCfg<D, HKV, STAGES, CTAS>;
-  __shared__ int last_flag;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t ring = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const uint32_t bars = ring + Cfg::kRingBytes;  // full[STAGES], empty[STAGES]
@@ -289,32 +286,71 @@ paged_attn_decode_kernel(const __grid_constant__ CUtensorMap k_map,
     if (gq + 8 < group) part_ml[row1] = make_float2(m1, l1);
   }
 
-  // Split fold without a second kernel and without waiting: every CTA of a
-  // sequence bumps a counter after its partials are visible; the one that sees
-  // the count complete folds all splits in split order (so the result does not
-  // depend on which CTA that is) and re-arms the counter for the next launch.
-  __threadfence();
-  asm volatile("bar.sync 1, %0;" ::"r"(HKV * 32) : "memory");
-  if (threadIdx.x == 0) last_flag = atomicAdd(done + b, 1) == nsplits - 1;
-  asm volatile("bar.sync 1, %0;" ::"r"(HKV * 32) : "memory");
-  if (!last_flag) return;
-  __threadfence();
-  if (threadIdx.x == 0) done[b] = 0;
-  for (int idx = threadIdx.x; idx < num_q_heads * D; idx += HKV * 32) {
-    const int h = idx / D, d = idx % D;
-    const size_t row = (static_cast<size_t>(b) * num_q_heads + h) * max_splits;
-    float mmax = -INFINITY;
-    for (int s = 0; s < nsplits; ++s) mmax = fmaxf(mmax, __ldcg(&part_ml[row + s].x));
-    float acc = 0.f, den = 0.f;
-    for (int s = 0; s < nsplits; ++s) {
-      const float2 ml = __ldcg(&part_ml[row + s]);
-      const float wgt = exp2f(ml.x - mmax);
-      den += wgt * ml.y;
-      acc += wgt * __ldcg(&part_o[(row + s) * D + d]);
-    }
-    out[(static_cast<size_t>(b) * num_q_heads + h) * D + d] = __float2bfloat16(acc / den);
-  }
 #endif
+}
+
+// Folds the per-split partials of one (sequence, q head) in split order: one warp
+// per row; lanes first cover the splits (max and normaliser by shuffles), then
+// head_dim in float4 pieces with the per-split weights broadcast from registers.
+// Sequences with a single split were already written by the main kernel.
+template <int D>
+__global__ void __launch_bounds__(128)
+paged_attn_reduce_kernel(const float* __restrict__ part_o, const float2* __restrict__ part_ml,
+                         const int* __restrict__ ctx_lens, __nv_bfloat16* __restrict__ out,
+                         int rows_total, int num_q_heads, int max_splits, int split_tokens, int max_ctx) {
+  const int row = blockIdx.x * 4 + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (row >= rows_total) return;
+  const int b = row / num_q_heads;
+  int L = ctx_lens[b];
+  L = L < 0 ? 0 : (L > max_ctx ? max_ctx : L);
+  const int n = (L + split_tokens - 1) / split_tokens;
+  if (n <= 1) return;
+  const size_t base = static_cast<size_t>(row) * max_splits;
+  float mmax = -INFINITY;
+  for (int s0 = 0; s0 < n; s0 += 32) {
+    const float m = s0 + lane < n ? part_ml[base + s0 + lane].x : -INFINITY;
+    mmax = fmaxf(mmax, warp_max(m));
+  }
+  float den = 0.f;
+  constexpr int V = D / 32;  // floats per lane
+  float acc[V];
+#pragma unroll
+  for (int j = 0; j < V; ++j) acc[j] = 0.f;
+  for (int s0 = 0; s0 < n; s0 += 32) {
+    float w = 0.f;
+    if (s0 + lane < n) {
+      const float2 ml = part_ml[base + s0 + lane];
+      w = exp2f(ml.x - mmax);
+      den += w * ml.y;
+    }
+    const int cnt = min(32, n - s0);
+    int s = 0;
+    for (; s + 4 <= cnt; s += 4) {
+      float v[4][V];
+#pragma unroll
+      for (int u = 0; u < 4; ++u)
+#pragma unroll
+        for (int j = 0; j < V; ++j) v[u][j] = part_o[(base + s0 + s + u) * D + lane * V + j];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const float wu = __shfl_sync(0xffffffffu, w, s + u);
+#pragma unroll
+        for (int j = 0; j < V; ++j) acc[j] += wu * v[u][j];
+      }
+    }
+    for (; s < cnt; ++s) {
+      const float wu = __shfl_sync(0xffffffffu, w, s);
+#pragma unroll
+      for (int j = 0; j < V; ++j) acc[j] += wu * part_o[(base + s0 + s) * D + lane * V + j];
+    }
+  }
+  den = warp_sum(den);
+  const float inv = 1.f / den;
+  __nv_bfloat16* dst = out + static_cast<size_t>(row) * D + lane * V;
+#pragma unroll
+  for (int j = 0; j < V; j += 2)
+    *reinterpret_cast<uint32_t*>(dst + j) = pack_bf16x2(acc[j] * inv, acc[j + 1] * inv);
 }
 
 // ------------------------------------------------------------ generic path --
@@ -440,7 +476,6 @@ __global__ void kv_append_kernel(const T* __restrict__ k_new, const T* __restric
 // ------------------------------------------------------------------ launch --
 struct AttnWorkspace {
   int* err;
-  int* done;  // [batch] arrival counters of the split fold; zero between launches
   float2* ml;
   float* o;
   size_t bytes;
@@ -455,8 +490,6 @@ static AttnWorkspace carve(void* ws, int batch, int hq, int D, int max_splits) {
   uint8_t* p = static_cast<uint8_t*>(ws);
   w.err = reinterpret_cast<int*>(p);
   size_t off = 256;
-  w.done = reinterpret_cast<int*>(p + off);
-  off += (static_cast<size_t>(batch) * sizeof(int) + 255) & ~size_t(255);
   w.ml = reinterpret_cast<float2*>(p + off);
   off += (static_cast<size_t>(batch) * hq * max_splits * sizeof(float2) + 255) & ~size_t(255);
   w.o = reinterpret_cast<float*>(p + off);
@@ -488,9 +521,16 @@ static int launch_main(const void* q, const void* k_pool, const void* v_pool,
   dim3 grid(batch, max_splits);
   const float scale_log2 = scale * 1.4426950408889634f;
   paged_attn_decode_kernel<D, HKV, STAGES, CTAS><<<grid, Cfg::kThreads, Cfg::kSmemBytes, stream>>>(
-      kmap, vmap, static_cast<const __nv_bfloat16*>(q), block_table, ctx_lens, w.o, w.ml, w.done,
+      kmap, vmap, static_cast<const __nv_bfloat16*>(q), block_table, ctx_lens, w.o, w.ml,
       static_cast<__nv_bfloat16*>(out), w.err, hq, num_blocks, max_pages, split_tokens, max_splits, scale_log2);
   B200_CUDA(cudaGetLastError());
+  if (max_splits > 1) {
+    const int rows = batch * hq;
+    paged_attn_reduce_kernel<D><<<(rows + 3) / 4, 128, 0, stream>>>(
+        w.o, w.ml, ctx_lens, static_cast<__nv_bfloat16*>(out), rows, hq, max_splits, split_tokens,
+        max_pages * kPage);
+    B200_CUDA(cudaGetLastError());
+  }
   return 0;
 }
 

@@ -150,8 +150,9 @@ class DecodeEngine:
                                                 self.split_tokens, self.device)
         self.moe_ws = ops.moe_fp8_workspace(max_batch, cfg.experts, cfg.top_k, cfg.hidden, cfg.moe_inter, self.device)
         self._graphs: dict[int, torch.cuda.CUDAGraph] = {}
-        # per layer: qk_norm_rope_append, attention, add_rmsnorm, route, rank, scatter+quant, gemm x2, combine+norm; + first norm
-        self.kernel_launches_per_step = cfg.layers * 9 + 1
+        # per layer: qk_norm_rope_append, attention + split reduce, add_rmsnorm, route, rank, scatter+quant, gemm x2,
+        # combine+norm; + the first norm
+        self.kernel_launches_per_step = cfg.layers * 10 + 1
 
     # ------------------------------------------------------------------ step
     def _step_eager(self, B: int) -> None:
