@@ -80,6 +80,44 @@ int b200_paged_attn_decode(const void* q, const void* k_pool, const void* v_pool
                            void* stream);
 
 /*
+ * Paged decode attention for callers that cannot allocate device memory.
+ * No counterpart in the reference: it exists for hosts of this library that own
+ * no allocator at the point of the call - a server whose device memory was
+ * carved up at start-up and is fully handed out, a plugin that is only lent its
+ * input and output buffers, or code that runs while a CUDA graph is being
+ * captured, where cudaMalloc is not permitted.
+ *
+ * Same arithmetic and the same kernels as b200_paged_attn_decode for bf16 pools
+ * with page_size 16, head_dim 64 or 128 and 1, 2, 4 or 8 kv heads (other shapes
+ * are refused: use b200_paged_attn_decode).  The per-split partial results go to
+ * a fixed B200_STATIC_SCRATCH_BYTES array inside the library image instead of a
+ * caller workspace; every GPU that loads the library holds that array until the
+ * process exits.  The call is refused with a "workspace too small" error when
+ *   batch * num_q_heads * ceil(max_pages_per_seq * 16 / split_tokens)
+ *         * (head_dim * 4 + 8)  bytes (the (m, l) block rounded up to 256)
+ * exceed it.  The function itself calls no cudaMalloc / cudaFree and no
+ * allocating library routine.
+ *
+ *   status_word  caller-owned 4-byte device word for device-side error codes,
+ *                zero before first use, or NULL.
+ *
+ * The first call on each device looks up the device address of the array
+ * (cudaGetSymbolAddress, with that device current) and keeps it; make that
+ * first call before starting any stream capture.  Nothing in the array has to
+ * start at zero and nothing is cleared: every call overwrites the slots it later
+ * reads.  All calls on one device share the array, so two calls whose kernels may
+ * overlap on the GPU (different streams without an ordering between them) race
+ * on it; order them, or give one of them a workspace of its own through
+ * b200_paged_attn_decode.
+ */
+#define B200_STATIC_SCRATCH_BYTES (32u << 20)
+int b200_paged_attn_decode_static(const void* q, const void* k_pool, const void* v_pool,
+                                  const int32_t* block_table, const int32_t* ctx_lens, void* out,
+                                  void* status_word, int batch, int num_q_heads, int num_kv_heads,
+                                  int head_dim, int page_size, int num_blocks, int max_pages_per_seq,
+                                  float scale, int split_tokens, void* stream);
+
+/*
  * Replaces: the per-step KV growth DynamicCache.update does with torch.cat
  * inside the forward called at torch_backend.py:314-320, and gives decode the
  * page write the reference only has for prompts

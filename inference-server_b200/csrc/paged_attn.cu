@@ -34,6 +34,8 @@
 
 #include <stdlib.h>
 
+#include <mutex>
+
 #include "common.cuh"
 #include "host.h"
 
@@ -655,4 +657,107 @@ extern "C" int b200_kv_append(const void* k_new, const void* v_new, void* k_pool
         max_pages_per_seq);
   B200_CUDA(cudaGetLastError());
   return 0;
+}
+
+// ------------------------------------------------- allocation-free variant --
+// Some hosts of this library cannot allocate device memory at the moment they
+// need attention: a serving process whose memory pool was sized up front and is
+// fully handed out, a plugin that is only lent buffers for its inputs and
+// outputs, or code running while a CUDA graph is being captured (cudaMalloc is
+// not allowed there).  For them the split partials live in a fixed array that is
+// part of the library image.  Every GPU that loads the library carries these
+// bytes until the process exits, so the size is kept modest.
+constexpr size_t kStaticScratchBytes = B200_STATIC_SCRATCH_BYTES;
+static __device__ __align__(256) unsigned char g_attn_static_scratch[kStaticScratchBytes];
+
+namespace b200 {
+// Device address of the array above, per device.  In host code the array's name
+// is only a handle for the runtime, not something a kernel can dereference; the
+// usable address comes from cudaGetSymbolAddress with that device current.
+static void* g_static_scratch_ptr[64] = {nullptr};
+static std::mutex g_static_scratch_mu;
+
+static int static_scratch_for_current_device(void** out) {
+  int dev = 0;
+  B200_CUDA(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) {
+    set_detail("paged_attn_decode_static: device index %d is outside the supported range", dev);
+    return -kErrUnsupported;
+  }
+  std::lock_guard<std::mutex> lock(g_static_scratch_mu);
+  if (g_static_scratch_ptr[dev] == nullptr) {
+    void* p = nullptr;
+    cudaError_t e = cudaGetSymbolAddress(&p, g_attn_static_scratch);
+    if (e != cudaSuccess) return cuda_fail(e, "cudaGetSymbolAddress(g_attn_static_scratch)");
+    g_static_scratch_ptr[dev] = p;
+  }
+  *out = g_static_scratch_ptr[dev];
+  return 0;
+}
+}  // namespace b200
+
+extern "C" int b200_paged_attn_decode_static(const void* q, const void* k_pool, const void* v_pool,
+                                             const int32_t* block_table, const int32_t* ctx_lens,
+                                             void* out, void* status_word, int batch,
+                                             int num_q_heads, int num_kv_heads, int head_dim,
+                                             int page_size, int num_blocks, int max_pages_per_seq,
+                                             float scale, int split_tokens, void* stream) {
+  B200_REQUIRE(q && k_pool && v_pool && block_table && ctx_lens && out,
+               "paged_attn_decode_static: null pointer");
+  B200_REQUIRE(batch > 0 && num_q_heads > 0 && num_kv_heads > 0 && num_blocks > 0 &&
+                   max_pages_per_seq > 0 && split_tokens > 0,
+               "paged_attn_decode_static: non-positive dimension");
+  B200_REQUIRE(num_q_heads % num_kv_heads == 0 && num_q_heads / num_kv_heads <= 16,
+               "paged_attn_decode_static: need at most 16 q heads per kv head (%d / %d)", num_q_heads,
+               num_kv_heads);
+  B200_REQUIRE(page_size == kPage && (head_dim == 64 || head_dim == 128) &&
+                   (num_kv_heads == 1 || num_kv_heads == 2 || num_kv_heads == 4 || num_kv_heads == 8),
+               "paged_attn_decode_static: only the split-K kernel is offered here (bf16, page 16, head_dim "
+               "64 or 128, 1/2/4/8 kv heads)");
+  B200_REQUIRE(split_tokens % kPage == 0, "paged_attn_decode_static: split_tokens %d not a multiple of %d",
+               split_tokens, kPage);
+  B200_REQUIRE((reinterpret_cast<uintptr_t>(k_pool) & 15) == 0 && (reinterpret_cast<uintptr_t>(v_pool) & 15) == 0 &&
+                   (reinterpret_cast<uintptr_t>(q) & 3) == 0,
+               "paged_attn_decode_static: pools must be 16-byte aligned");
+  int rc = check_device(nullptr);
+  if (rc) return rc;
+  const int ms = max_splits_of(max_pages_per_seq, page_size, split_tokens);
+  B200_REQUIRE(ms <= 65535, "paged_attn_decode_static: grid too large");
+  // Lay the partials out in the static array exactly as carve() does in a caller workspace,
+  // minus the status block: the status word here is the caller's.
+  const size_t ml_bytes = (static_cast<size_t>(batch) * num_q_heads * ms * sizeof(float2) + 255) & ~size_t(255);
+  const size_t o_bytes = static_cast<size_t>(batch) * num_q_heads * ms * head_dim * sizeof(float);
+  if (ml_bytes + o_bytes > kStaticScratchBytes) {
+    set_detail("paged_attn_decode_static: batch %d x %d heads x %d splits needs %zu bytes of split partials; the "
+               "built-in scratch holds %zu. Use fewer splits (larger split_tokens), a smaller batch, or "
+               "b200_paged_attn_decode with a workspace of your own.",
+               batch, num_q_heads, ms, ml_bytes + o_bytes, kStaticScratchBytes);
+    return -kErrWorkspace;
+  }
+  void* scratch = nullptr;
+  rc = static_scratch_for_current_device(&scratch);
+  if (rc) return rc;
+  AttnWorkspace w;
+  w.err = static_cast<int*>(status_word);
+  w.ml = reinterpret_cast<float2*>(scratch);
+  w.o = reinterpret_cast<float*>(static_cast<unsigned char*>(scratch) + ml_bytes);
+  w.bytes = ml_bytes + o_bytes;
+  cudaStream_t st = as_stream(stream);
+#define B200_ATTN_ARGS q, k_pool, v_pool, block_table, ctx_lens, out, w, batch, num_q_heads, num_blocks, \
+                       max_pages_per_seq, scale, split_tokens, ms, st
+  if (head_dim == 128) {
+    switch (num_kv_heads) {
+      case 1: return launch_main<128, 1, 8, 4>(B200_ATTN_ARGS);
+      case 2: return launch_main<128, 2, 6, 2>(B200_ATTN_ARGS);
+      case 4: return launch_main<128, 4, 3, 2>(B200_ATTN_ARGS);
+      default: return launch_main<128, 8, 3, 1>(B200_ATTN_ARGS);
+    }
+  }
+  switch (num_kv_heads) {
+    case 1: return launch_main<64, 1, 8, 4>(B200_ATTN_ARGS);
+    case 2: return launch_main<64, 2, 6, 4>(B200_ATTN_ARGS);
+    case 4: return launch_main<64, 4, 6, 2>(B200_ATTN_ARGS);
+    default: return launch_main<64, 8, 3, 2>(B200_ATTN_ARGS);
+  }
+#undef B200_ATTN_ARGS
 }
