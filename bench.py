@@ -143,6 +143,7 @@ def main():
     ap.add_argument("--batch", type=int, default=256, help="concurrent sequences per GPU")
     ap.add_argument("--gen-tokens", type=int, default=256)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-ep", action="store_true", help="N > 1: independent replicas instead of expert parallelism")
     args = ap.parse_args()
 
     rank = int(os.environ.get("RANK", "0"))
@@ -152,7 +153,9 @@ def main():
     prompt_lens, table, num_blocks, max_pages = build_workload(cfg, args.batch, args.gen_tokens, seed=rank)
     config = {"workload": f"{args.model} continuous-batching decode, {args.batch} sequences/GPU, prompts U{{512..4096}}, "
                           f"page {PAGE}, FP8 experts (BASELINE config 4)",
-              "batch_per_gpu": args.batch, "mean_ctx": float(np.mean(prompt_lens)), "parallelism": f"dp{world}",
+              "batch_per_gpu": args.batch, "mean_ctx": float(np.mean(prompt_lens)),
+              "parallelism": (f"dp{world} attention + ep{world} MoE (NCCL all-to-all)" if world > 1 and not args.no_ep
+                              else f"dp{world}"),
               "kv": "synthetic N(0,1) pages at the prompt lengths; prefill not timed",
               "l2": "each step streams >90 GB of KV and weights, far larger than the 126 MB L2"}
 
@@ -185,8 +188,9 @@ def main():
 
     eng_mod, ops, backend_mod = pkg("engine"), pkg("ops"), pkg("backend")
     t_setup = time.time()
+    ep_group = torch.distributed.group.WORLD if world > 1 and not args.no_ep else None
     engine = eng_mod.DecodeEngine(cfg, num_blocks=num_blocks, max_batch=args.batch, max_pages_per_seq=max_pages,
-                                  device=dev, seed=rank)
+                                  device=dev, seed=rank, ep_group=ep_group)
     # KV image: one random pool, shared by all layers (contents do not affect timing)
     g = torch.Generator(device=dev).manual_seed(1000 + rank)
     engine.k_pools[0].normal_(generator=g)
@@ -221,6 +225,8 @@ def main():
     clock_info = clocks.summary()
     ops.read_status(engine.attn_ws, "attention workspace status after the timed region")
     ops.read_status(engine.moe_ws, "MoE workspace status after the timed region")
+    if engine.ep_state is not None and bool(engine.ep_state.overflow):
+        raise SystemExit("expert-parallel dispatch overflowed its per-destination capacity; results are invalid")
 
     # ---- end to end through the backend API with host buffers
     backend = backend_mod.B200Backend(engine)

@@ -33,6 +33,7 @@ the CPU tests exercise with a stub engine.
 from __future__ import annotations
 
 import threading
+import weakref
 from dataclasses import dataclass, field
 from typing import Generator
 
@@ -229,10 +230,9 @@ class B200Backend:
         ids, handles = self._take_pages(need)
         kv.block_ids += ids
         kv.private_blocks += handles
-        hist = getattr(kv, "_tokens", [None] * kv.ctx_len)
-        tokens = hist + list(chunk_token_ids)
+        # only the tokens past `cached_tokens` are embedded; the earlier ones are already pages
+        tokens = [0] * kv.ctx_len + list(chunk_token_ids)
         last, _ = self.engine.prefill(tokens, kv.block_ids, cached_tokens=kv.ctx_len)
-        kv._tokens = tokens
         kv.ctx_len = new_len
         return kv, last, new_len
 
@@ -240,14 +240,30 @@ class B200Backend:
         self._store(token_ids, full_kv, matched, session_id)
 
     # --------------------------------------------------------------- batching
+    def _reclaim_rows(self, rows: list) -> None:
+        for row in rows:
+            self._give_back(row.private_blocks)
+            row.private_blocks = []
+        rows.clear()
+
     def splice_into_batched(self, batched_kv, new_kv, new_kv_len: int):
-        batch = batched_kv if batched_kv is not None else PagedBatch()
+        if batched_kv is None:
+            batch = PagedBatch()
+            # The scheduler drops the whole batch object when its last row finishes
+            # (scheduler.py:224-227) without calling remove_row_from_cache for it; give the pages of
+            # whatever rows are still listed back when the batch object goes away.
+            weakref.finalize(batch, self._reclaim_rows, batch.rows)
+        else:
+            batch = batched_kv
         batch.rows.append(new_kv)
         batch.dirty = True
         return batch
 
     def stack_caches_left_padded(self, per_row_caches: list, max_kv_len: int):
-        return PagedBatch(rows=list(per_row_caches))
+        batch = None
+        for kv in per_row_caches:
+            batch = self.splice_into_batched(batch, kv, kv.ctx_len)
+        return batch
 
     def remove_row_from_cache(self, batched_kv, row_idx: int):
         row = batched_kv.rows.pop(row_idx)
@@ -263,8 +279,9 @@ class B200Backend:
             raise ValueError(f"batch {B} exceeds the engine's max_batch {eng.max_batch}")
         if batch.dirty or self._table_cpu is None:
             if self._table_cpu is None:
-                self._table_cpu = torch.zeros(eng.max_batch, eng.max_pages, dtype=torch.int32).pin_memory()
-                self._lens_cpu = torch.zeros(eng.max_batch, dtype=torch.int32).pin_memory()
+                pin = torch.cuda.is_available()
+                self._table_cpu = torch.zeros(eng.max_batch, eng.max_pages, dtype=torch.int32, pin_memory=pin)
+                self._lens_cpu = torch.zeros(eng.max_batch, dtype=torch.int32, pin_memory=pin)
             self._table_cpu.zero_()
             for i, row in enumerate(batch.rows):
                 if len(row.block_ids) > eng.max_pages:

@@ -88,8 +88,10 @@ def apply_rope(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> torch.T
     return x * cos + rot * sin
 
 
-def random_layer(cfg: ModelConfig, device, gen: torch.Generator, std: float = 0.02) -> LayerWeights:
-    """Random-init weights (N(0, std)), experts quantised to e4m3 128x128 blocks on the device."""
+def random_layer(cfg: ModelConfig, device, gen: torch.Generator, std: float = 0.02,
+                 local_experts: int | None = None) -> LayerWeights:
+    """Random-init weights (N(0, std)), experts quantised to e4m3 128x128 blocks on the device.
+    With `local_experts` only that many experts are created (this rank's shard under expert parallelism)."""
     H, D = cfg.hidden, cfg.head_dim
     w = LayerWeights()
     bf = torch.bfloat16
@@ -104,9 +106,45 @@ def random_layer(cfg: ModelConfig, device, gen: torch.Generator, std: float = 0.
     w.wqkv = rn((cfg.q_heads + 2 * cfg.kv_heads) * D, H).to(bf)
     w.wo = rn(H, cfg.q_heads * D).to(bf)
     w.router = rn(cfg.experts, H).to(bf)
-    w.w13, w.w13_scale = quant.quantize_weight_blocks(rn(cfg.experts, 2 * cfg.moe_inter, H))
-    w.w2, w.w2_scale = quant.quantize_weight_blocks(rn(cfg.experts, H, cfg.moe_inter))
+    n_exp = local_experts or cfg.experts
+    w.w13, w.w13_scale = quant.quantize_weight_blocks(rn(n_exp, 2 * cfg.moe_inter, H))
+    w.w2, w.w2_scale = quant.quantize_weight_blocks(rn(n_exp, H, cfg.moe_inter))
     return w
+
+
+def layer_from_hf(layer, device) -> LayerWeights:
+    """Run-time weights of one ``Qwen3MoeDecoderLayer`` (the model class the reference loads for a
+    Qwen3-MoE checkpoint): projections in bf16, q/k/v fused, experts quantised to e4m3 128x128 blocks."""
+    bf = torch.bfloat16
+    at, mlp = layer.self_attn, layer.mlp
+    w = LayerWeights()
+
+    def dev(t):
+        return t.detach().to(device=device, dtype=bf).contiguous()
+
+    w.ln1, w.ln2 = dev(layer.input_layernorm.weight), dev(layer.post_attention_layernorm.weight)
+    w.q_norm, w.k_norm = dev(at.q_norm.weight), dev(at.k_norm.weight)
+    w.wqkv = dev(torch.cat([at.q_proj.weight, at.k_proj.weight, at.v_proj.weight], dim=0))
+    w.wo = dev(at.o_proj.weight)
+    w.router = dev(mlp.gate.weight)
+    w.w13, w.w13_scale = quant.quantize_weight_blocks(mlp.experts.gate_up_proj.detach().to(device).float())
+    w.w2, w.w2_scale = quant.quantize_weight_blocks(mlp.experts.down_proj.detach().to(device).float())
+    return w
+
+
+def engine_from_hf(model, num_blocks: int, max_batch: int, max_pages_per_seq: int, device="cuda", **kw):
+    """DecodeEngine holding the weights of a transformers ``Qwen3MoeForCausalLM``."""
+    c = model.config
+    cfg = ModelConfig("from-hf", c.vocab_size, c.hidden_size, c.num_hidden_layers, c.num_attention_heads,
+                      c.num_key_value_heads, c.head_dim, c.num_experts, c.num_experts_per_tok,
+                      c.moe_intermediate_size, float(c.rope_parameters["rope_theta"]), c.rms_norm_eps,
+                      bool(c.norm_topk_prob))
+    bf = torch.bfloat16
+    layers = [layer_from_hf(lyr, device) for lyr in model.model.layers]
+    return DecodeEngine(cfg, num_blocks, max_batch, max_pages_per_seq, device=device, layers=layers,
+                        embed=model.model.embed_tokens.weight.detach().to(device=device, dtype=bf).contiguous(),
+                        lm_head=model.lm_head.weight.detach().to(device=device, dtype=bf).contiguous(),
+                        final_norm=model.model.norm.weight.detach().to(device=device, dtype=bf).contiguous(), **kw)
 
 
 class DecodeEngine:
@@ -116,7 +154,7 @@ class DecodeEngine:
                  device: str | torch.device = "cuda", seed: int = 0, layers: list[LayerWeights] | None = None,
                  embed: torch.Tensor | None = None, lm_head: torch.Tensor | None = None,
                  final_norm: torch.Tensor | None = None, k_pools=None, v_pools=None, use_graphs: bool = True,
-                 split_tokens: int | None = None):
+                 split_tokens: int | None = None, ep_group=None, ep_capacity: int | None = None):
         if not torch.cuda.is_available():
             raise RuntimeError("DecodeEngine needs a CUDA device; this path has no CPU implementation")
         self.cfg = cfg
@@ -127,7 +165,17 @@ class DecodeEngine:
         self.use_graphs = use_graphs
         bf = torch.bfloat16
         gen = torch.Generator(device=self.device).manual_seed(seed)
-        self.layers = layers if layers is not None else [random_layer(cfg, self.device, gen) for _ in range(cfg.layers)]
+        # expert parallelism: this rank owns experts [rank * E / W, (rank + 1) * E / W) of every layer
+        self.ep_group = ep_group
+        self.ep_world = 1
+        if ep_group is not None:
+            import torch.distributed as dist
+            self.ep_world = dist.get_world_size(ep_group)
+            if cfg.experts % self.ep_world:
+                raise ValueError(f"{cfg.experts} experts do not divide over {self.ep_world} ranks")
+        local = cfg.experts // self.ep_world if self.ep_world > 1 else None
+        self.layers = layers if layers is not None else [random_layer(cfg, self.device, gen, local_experts=local)
+                                                         for _ in range(cfg.layers)]
         std = 0.02
         self.embed = embed if embed is not None else (
             torch.randn(cfg.vocab_size, cfg.hidden, device=self.device, generator=gen) * std).to(bf)
@@ -150,9 +198,17 @@ class DecodeEngine:
                                                 self.split_tokens, self.device)
         self.moe_ws = ops.moe_fp8_workspace(max_batch, cfg.experts, cfg.top_k, cfg.hidden, cfg.moe_inter, self.device)
         self._graphs: dict[int, torch.cuda.CUDAGraph] = {}
+        self.ep_state = None
+        if self.ep_world > 1:
+            from . import ep
+            cap = ep_capacity or ep.default_capacity(max_batch, cfg.top_k, self.ep_world)
+            self.ep_state = ep.EPState(max_batch, cfg.hidden, cfg.top_k, cfg.experts, self.ep_world, cap, self.device,
+                                       ep_group)
         # per layer: qk_norm_rope_append, attention + split reduce, add_rmsnorm, route, rank, scatter+quant, gemm x2,
         # combine+norm; + the first norm
         self.kernel_launches_per_step = cfg.layers * 10 + 1
+        if self.ep_world > 1:
+            self.kernel_launches_per_step += cfg.layers * 2  # the local re-sort of received rows (rank + scatter)
 
     # ------------------------------------------------------------------ step
     def _step_eager(self, B: int) -> None:
@@ -180,11 +236,26 @@ class DecodeEngine:
             logits = torch.matmul(h2, w.router.t())  # bf16, routed as is
             nxt = self.layers[li + 1].ln1 if li + 1 < len(self.layers) else self.final_norm
             # MoE layer; its combine also adds into the residual stream and applies the next norm
-            h = ops.moe_fp8_forward(h2, logits, w.w13, w.w13_scale, w.w2, w.w2_scale, cfg.top_k, cfg.norm_topk_prob,
-                                    self.moe_ws, residual=x, norm_weight=nxt, eps=cfg.rms_eps)
+            if self.ep_state is not None:
+                h = self._ep_moe(h2, logits, w, x, nxt, B)
+            else:
+                h = ops.moe_fp8_forward(h2, logits, w.w13, w.w13_scale, w.w2, w.w2_scale, cfg.top_k,
+                                        cfg.norm_topk_prob, self.moe_ws, residual=x, norm_weight=nxt, eps=cfg.rms_eps)
         self.last_logits = torch.matmul(h, self.lm_head.t())
         self.next_tokens[:B] = self.last_logits.argmax(dim=-1)
         self.ctx_lens[:B] += 1
+
+    def _ep_moe(self, h2, logits, w: LayerWeights, x, next_norm, B: int) -> torch.Tensor:
+        """Expert-parallel MoE layer: NCCL all-to-all dispatch and combine around the local grouped GEMMs."""
+        import torch.distributed as dist
+
+        from . import ep
+        st = self.ep_state
+        if B != st.T:
+            raise ValueError("expert-parallel decode runs at the engine's full batch (every rank the same size)")
+        return ep.ep_moe_forward(st, h2, logits, w.w13, w.w13_scale, w.w2, w.w2_scale, self.cfg.norm_topk_prob, ops,
+                                 lambda o, i: dist.all_to_all_single(o, i, group=st.group), residual=x,
+                                 norm_weight=next_norm, eps=self.cfg.rms_eps)
 
     def step(self, B: int) -> torch.Tensor:
         """Run one decode step for the first B rows of the static state; returns next tokens (device)."""

@@ -1,0 +1,76 @@
+"""CPU stand-ins for the ``ops`` kernels, built from the oracle (test infrastructure only).
+
+Same call signatures as ``inference-server_b200/ops.py`` for the functions the expert-parallel layer
+uses, on CPU tensors, so the multi-rank host logic (slot planning, exchanges, re-sort, combine) can be
+exercised with gloo ranks on a machine without a GPU."""
+from __future__ import annotations
+
+import types
+
+import torch
+
+from . import moe_ref
+
+
+def moe_route(logits, top_k, renormalize=True):
+    return moe_ref.route_ref(logits.float(), top_k, renormalize)
+
+
+def _perm(ids, num_experts):
+    r = moe_ref.permute_ref(ids, num_experts)
+    p = types.SimpleNamespace()
+    p.sorted_pair_ids = torch.from_numpy(r["sorted_pair_ids"])
+    p.row_of_pair = torch.from_numpy(r["row_of_pair"])
+    p.expert_offsets = torch.from_numpy(r["expert_offsets"])
+    tiles = torch.zeros(max(1, ids.numel() // 128 + num_experts), 4, dtype=torch.int32)
+    tiles[: len(r["tiles"])] = torch.from_numpy(r["tiles"])
+    p.tiles = tiles
+    p.num_tiles = torch.tensor([len(r["tiles"])], dtype=torch.int32)
+    return p
+
+
+def moe_permute(ids, num_experts):
+    return _perm(ids, num_experts)
+
+
+def moe_permute_quant(ids, x, num_experts):
+    p = _perm(ids, num_experts)
+    q, s = moe_ref.act_quant_ref(x)
+    tok = p.sorted_pair_ids.long() // ids.shape[1]
+    return p, q.view(torch.uint8)[tok].contiguous(), s[tok].contiguous()
+
+
+def _rows_of_tiles(perm):
+    n = int(perm.num_tiles)
+    for e, row0, rows, _ in perm.tiles[:n].tolist():
+        yield e, row0, rows
+
+
+def moe_fp8_gemm_gate_up(xq, xs, w13, w13_scale, perm, status=None):
+    inter = w13.shape[1] // 2
+    hq = torch.zeros(xq.shape[0], inter, dtype=torch.uint8)
+    hs = torch.zeros(xq.shape[0], inter // 128)
+    for e, row0, rows in _rows_of_tiles(perm):
+        a = moe_ref.dequant_act(xq[row0:row0 + rows].view(torch.float8_e4m3fn), xs[row0:row0 + rows])
+        gu = a @ moe_ref.dequant_weight(w13[e].view(torch.float8_e4m3fn), w13_scale[e]).t()
+        h = torch.nn.functional.silu(gu[:, :inter]) * gu[:, inter:]
+        q, s = moe_ref.act_quant_ref(h)
+        hq[row0:row0 + rows], hs[row0:row0 + rows] = q.view(torch.uint8), s
+    return hq, hs
+
+
+def moe_fp8_gemm_down(hq, hs, w2, w2_scale, perm, status=None):
+    y = torch.zeros(hq.shape[0], w2.shape[1], dtype=torch.bfloat16)
+    for e, row0, rows in _rows_of_tiles(perm):
+        a = moe_ref.dequant_act(hq[row0:row0 + rows].view(torch.float8_e4m3fn), hs[row0:row0 + rows])
+        y[row0:row0 + rows] = (a @ moe_ref.dequant_weight(w2[e].view(torch.float8_e4m3fn), w2_scale[e]).t()).bfloat16()
+    return y
+
+
+def moe_combine(y, row_of_pair, w):
+    T, K = w.shape
+    rop = row_of_pair.long().view(T, K)
+    out = torch.zeros(T, y.shape[1])
+    for k in range(K):
+        out = out + w[:, k:k + 1] * y[rop[:, k]].float()
+    return out.bfloat16()

@@ -100,11 +100,21 @@ def moe_fp8_ref(x, router_logits, w13_q, w13_s, w2_q, w2_s, top_k: int, renormal
     fp32 until h is quantised (there they pass through bf16), which is the more
     accurate of the two and what the CUDA kernel does.
     """
+    ids, w = route_ref(router_logits, top_k, renormalize)
+    return moe_fp8_experts_ref(x, ids, w, w13_q, w13_s, w2_q, w2_s, return_parts)
+
+
+def moe_fp8_experts_ref(x, ids, w, w13_q, w13_s, w2_q, w2_s, return_parts: bool = False):
+    """The expert part of :func:`moe_fp8_ref` for given routing (ids int [T,K], weights fp32 [T,K]);
+    this is the signature the model's experts module is called with
+    (``experts(hidden_states, top_k_index, top_k_weights)``)."""
     x = x.detach().cpu()
     T, H = x.shape
     E = w13_q.shape[0]
     inter = w13_q.shape[1] // 2
-    ids, w = route_ref(router_logits, top_k, renormalize)
+    top_k = ids.shape[1]
+    ids = ids.to(torch.int32)
+    w = w.float()
     perm = permute_ref(ids, E)
     xq, xs = act_quant_ref(x)
     xd = dequant_act(xq, xs)
