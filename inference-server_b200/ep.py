@@ -46,7 +46,7 @@ def plan_dispatch(topk_ids: torch.Tensor, row_of_pair: torch.Tensor, expert_offs
     trash = world * capacity
     expert_of_slot = torch.full((trash + 1,), e_local, dtype=torch.int32, device=topk_ids.device)
     expert_of_slot.index_copy_(0, torch.where(fits, slot, torch.full_like(slot, trash)), (flat % e_local).to(torch.int32))
-    expert_of_slot[trash] = e_local
+    expert_of_slot[trash:].fill_(e_local)  # (a fill kernel: a scalar assignment would be a host copy)
     return slot, expert_of_slot[:trash], overflow
 
 

@@ -1,0 +1,65 @@
+"""The expert-parallel MoE layer's GPU path with a world of one (all-to-all = copy) vs the fused layer (B200).
+Multi-rank slot logic is covered by tests/test_ep_gloo.py; this covers the same function on CUDA tensors with
+the real kernels, including the local re-sort with empty slots."""
+import pytest
+import torch
+
+from conftest import pkg, rel_err
+import oracle
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+@pytest.mark.parametrize("T,slack", [(64, 0), (64, 40), (256, 128)])
+def test_ep_layer_world_one_matches_fused_layer(ops, T, slack):
+    ep = pkg("ep")
+    E, K, H, I = 128, 8, 2048, 768
+    g = torch.Generator().manual_seed(T)
+    w13q, w13s = oracle.quantize_weight_ref(torch.randn(E, 2 * I, H, generator=g) * 0.02)
+    w2q, w2s = oracle.quantize_weight_ref(torch.randn(E, H, I, generator=g) * 0.02)
+    dw = [w13q.view(torch.uint8).to(DEV), w13s.to(DEV), w2q.view(torch.uint8).to(DEV), w2s.to(DEV)]
+    x = torch.randn(T, H, generator=g).bfloat16().to(DEV)
+    logits = torch.randn(T, E, generator=g).bfloat16().to(DEV)
+    ref = ops.moe_fp8_forward(x, logits, *dw, K, True)
+    st = ep.EPState(T, H, K, E, 1, T * K + slack, DEV)  # slack leaves empty slots that must sort last and be skipped
+    out = ep.ep_moe_forward(st, x, logits, *dw, True, ops, lambda o, i: o.copy_(i))
+    torch.cuda.synchronize()
+    assert not bool(st.overflow)
+    assert rel_err(out, ref) < 1e-2
+    assert torch.equal(out, ref)  # same rows, same order inside every expert: same bits
+    # fused tail: residual add + next norm
+    res1, res2 = x.clone(), x.clone()
+    nw = torch.ones(H, dtype=torch.bfloat16, device=DEV)
+    h1 = ops.moe_fp8_forward(x, logits, *dw, K, True, residual=res1, norm_weight=nw)
+    h2 = ep.ep_moe_forward(st, x, logits, *dw, True, ops, lambda o, i: o.copy_(i), residual=res2, norm_weight=nw)
+    assert torch.equal(res1, res2) and torch.equal(h1, h2)
+
+
+def test_ep_layer_can_be_captured_in_a_cuda_graph(ops):
+    """The decode step is replayed from a CUDA graph: the layer must not copy from the host or size anything
+    by device data while it is being captured."""
+    ep = pkg("ep")
+    E, K, H, I, T = 128, 8, 2048, 768, 32
+    g = torch.Generator().manual_seed(1)
+    w13q, w13s = oracle.quantize_weight_ref(torch.randn(E, 2 * I, H, generator=g) * 0.02)
+    w2q, w2s = oracle.quantize_weight_ref(torch.randn(E, H, I, generator=g) * 0.02)
+    dw = [w13q.view(torch.uint8).to(DEV), w13s.to(DEV), w2q.view(torch.uint8).to(DEV), w2s.to(DEV)]
+    x = torch.randn(T, H, generator=g).bfloat16().to(DEV)
+    logits = torch.randn(T, E, generator=g).bfloat16().to(DEV)
+    st = ep.EPState(T, H, K, E, 1, T * K + 16, DEV)
+    run = lambda: ep.ep_moe_forward(st, x, logits, *dw, True, ops, lambda o, i: o.copy_(i))
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        ref = run().clone()
+    torch.cuda.current_stream().wait_stream(side)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        out = run()
+    x.copy_(torch.randn(T, H, generator=g).bfloat16())  # new input, replay must recompute
+    graph.replay()
+    torch.cuda.synchronize()
+    assert torch.equal(out, ops.moe_fp8_forward(x, logits, *dw, K, True))
+    assert not torch.equal(out, ref)
