@@ -143,7 +143,8 @@ def main():
     ap.add_argument("--batch", type=int, default=256, help="concurrent sequences per GPU")
     ap.add_argument("--gen-tokens", type=int, default=256)
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--no-ep", action="store_true", help="N > 1: independent replicas instead of expert parallelism")
+    ap.add_argument("--ep", action="store_true",
+                    help="N > 1: expert-parallel MoE (NCCL all-to-all dispatch/combine) instead of independent replicas")
     args = ap.parse_args()
 
     rank = int(os.environ.get("RANK", "0"))
@@ -154,8 +155,8 @@ def main():
     config = {"workload": f"{args.model} continuous-batching decode, {args.batch} sequences/GPU, prompts U{{512..4096}}, "
                           f"page {PAGE}, FP8 experts (BASELINE config 4)",
               "batch_per_gpu": args.batch, "mean_ctx": float(np.mean(prompt_lens)),
-              "parallelism": (f"dp{world} attention + ep{world} MoE (NCCL all-to-all)" if world > 1 and not args.no_ep
-                              else f"dp{world}"),
+              "parallelism": (f"dp{world} attention + ep{world} MoE (NCCL all-to-all)" if world > 1 and args.ep
+                              else f"dp{world} (replicas: disjoint request batches, no data-path collective)"),
               "kv": "synthetic N(0,1) pages at the prompt lengths; prefill not timed",
               "l2": "each step streams >90 GB of KV and weights, far larger than the 126 MB L2"}
 
@@ -188,7 +189,7 @@ def main():
 
     eng_mod, ops, backend_mod = pkg("engine"), pkg("ops"), pkg("backend")
     t_setup = time.time()
-    ep_group = torch.distributed.group.WORLD if world > 1 and not args.no_ep else None
+    ep_group = torch.distributed.group.WORLD if world > 1 and args.ep else None
     engine = eng_mod.DecodeEngine(cfg, num_blocks=num_blocks, max_batch=args.batch, max_pages_per_seq=max_pages,
                                   device=dev, seed=rank, ep_group=ep_group)
     # KV image: one random pool, shared by all layers (contents do not affect timing)
@@ -272,9 +273,25 @@ def main():
         torch.distributed.all_reduce(times, op=torch.distributed.ReduceOp.MAX)
     ms_max, e2e_ms_max = times.tolist()
     total_tokens = world * B * args.steps
+
+    def shutdown():
+        """Release the captured graphs before the communicator (graphs that hold NCCL kernels keep it busy),
+        and never let a stuck teardown outlive the measurement."""
+        if world == 1:
+            return
+        import threading
+        sys.stdout.flush()
+        guard = threading.Timer(30.0, os._exit, (0,))
+        guard.daemon = True
+        guard.start()
+        engine._graphs.clear()
+        torch.cuda.synchronize()
+        torch.distributed.barrier()
+        torch.distributed.destroy_process_group()
+        guard.cancel()
+
     if rank != 0:
-        if world > 1:
-            torch.distributed.destroy_process_group()
+        shutdown()
         return
 
     line = {
@@ -298,8 +315,7 @@ def main():
         line["cpu_baseline"] = {"value": r["tok_per_s"], "unit": "tok/s", "cores": r["threads"], "kind": "port",
                                 "sample": r["sample"]}
     print(json.dumps(line))
-    if world > 1:
-        torch.distributed.destroy_process_group()
+    shutdown()
 
 
 if __name__ == "__main__":
