@@ -239,10 +239,18 @@ moe_fp8_gemm_kernel(const __grid_constant__ CUtensorMap a_map,
             __syncwarp();
             if (lane == 0) mbar_arrive(bar_tempty + 8 * buf);
           }
+          // packed fp32 FMA (two lanes per instruction) halves the issue slots of the promotion
+          const float2 sc0v = make_float2(sc0, sc0), sc1v = make_float2(sc1, sc1);
 #pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            acc[c * 32 + i] = fmaf(__uint_as_float(v0[i]), sc0, acc[c * 32 + i]);
-            acc[c * 32 + 32 + i] = fmaf(__uint_as_float(v1[i]), sc1, acc[c * 32 + 32 + i]);
+          for (int i = 0; i < 32; i += 2) {
+            const float2 r0 = __ffma2_rn(make_float2(__uint_as_float(v0[i]), __uint_as_float(v0[i + 1])), sc0v,
+                                         make_float2(acc[c * 32 + i], acc[c * 32 + i + 1]));
+            acc[c * 32 + i] = r0.x;
+            acc[c * 32 + i + 1] = r0.y;
+            const float2 r1 = __ffma2_rn(make_float2(__uint_as_float(v1[i]), __uint_as_float(v1[i + 1])), sc1v,
+                                         make_float2(acc[c * 32 + 32 + i], acc[c * 32 + 32 + i + 1]));
+            acc[c * 32 + 32 + i] = r1.x;
+            acc[c * 32 + 32 + i + 1] = r1.y;
           }
         }
         if (threadIdx.x == 128) B200_TRACE(2, 2 * it + 1);
@@ -256,7 +264,11 @@ moe_fp8_gemm_kernel(const __grid_constant__ CUtensorMap a_map,
 #pragma unroll
         for (int i = 0; i < 64; ++i) {
           const float g = acc[i];
-          const float h = __fdividef(g, 1.f + __expf(-g)) * acc[64 + i];  // no slow-path branch: the loop must pipeline
+          // silu(g) = g * sigmoid(g) = 0.5 g (1 + tanh(g / 2)): one special-function op per element instead of
+          // two (exp + reciprocal); the loop is bound by that unit.  tanh.approx is good to ~2^-11 relative.
+          float th;
+          asm("tanh.approx.f32 %0, %1;" : "=f"(th) : "f"(0.5f * g));
+          const float h = (0.5f * g) * (1.f + th) * acc[64 + i];
           acc[i] = h;
           amax = fmaxf(amax, fabsf(h));
         }
