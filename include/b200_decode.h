@@ -240,16 +240,24 @@ int b200_act_quant_fp8(const void* x, const int32_t* row_of_pair, int num_tokens
  *   w2_scale_inv [num_experts, hidden/128, inter/128] fp32
  *   y_sorted [num_rows, hidden] bf16
  * tiles/num_tiles come from b200_moe_permute; status_word may be NULL.
+ *
+ * weight_layout: B200_WEIGHTS_ROW_MAJOR - the arrays above as written (the
+ * reference checkpoint layout); B200_WEIGHTS_TILED - the same e4m3 values
+ * re-ordered at load time into contiguous 128x128 blocks,
+ * [num_experts, rows/128, cols/128, 128, 128], so that every TMA box of W is
+ * one sequential 16 KiB read.  Scales are the same in both.
  */
+#define B200_WEIGHTS_ROW_MAJOR 0
+#define B200_WEIGHTS_TILED 1
 int b200_moe_fp8_gemm_gate_up(const void* xq, const float* x_scale, const void* w13,
                               const float* w13_scale_inv, const void* tiles,
                               const int32_t* num_tiles, void* hq, float* h_scale,
                               void* status_word, int num_rows, int num_experts, int hidden,
-                              int inter, void* stream);
+                              int inter, int weight_layout, void* stream);
 int b200_moe_fp8_gemm_down(const void* hq, const float* h_scale, const void* w2,
                            const float* w2_scale_inv, const void* tiles, const int32_t* num_tiles,
                            void* y_sorted, void* status_word, int num_rows, int num_experts,
-                           int hidden, int inter, void* stream);
+                           int hidden, int inter, int weight_layout, void* stream);
 
 /*
  * Replaces: the routing-weight multiply and per-token sum over the top_k expert
@@ -287,14 +295,14 @@ int b200_moe_fp8_forward(const void* x, const void* router_logits, int logits_dt
                          const float* w13_scale_inv, const void* w2, const float* w2_scale_inv,
                          void* out, void* workspace, size_t workspace_bytes, int num_tokens,
                          int num_experts, int top_k, int hidden, int inter, int renormalize,
-                         void* stream);
+                         int weight_layout, void* stream);
 int b200_moe_fp8_forward_add_rmsnorm(const void* x, const void* router_logits, int logits_dtype,
                                      const void* w13, const float* w13_scale_inv, const void* w2,
                                      const float* w2_scale_inv, void* residual,
                                      const void* norm_weight, float eps, void* normed_out,
                                      void* workspace, size_t workspace_bytes, int num_tokens,
                                      int num_experts, int top_k, int hidden, int inter,
-                                     int renormalize, void* stream);
+                                     int renormalize, int weight_layout, void* stream);
 
 #ifdef __cplusplus
 }

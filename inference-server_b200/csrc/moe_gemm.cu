@@ -78,6 +78,7 @@ struct GemmParams {
   int n_rows;            // weight rows per expert (2 * inter, or hidden)
   int inter;             // gate/up only
   int n_tiles;           // column tiles per row tile
+  int tiled;             // weights stored as contiguous 128x128 blocks [E, n_rows/128, k_blocks, 128, 128]
 };
 
 template <int MODE>
@@ -130,14 +131,20 @@ moe_fp8_gemm_kernel(const __grid_constant__ CUtensorMap a_map,
       for (int w = blockIdx.x; w < total && alive; w += gridDim.x) {
         const MoeTile tile = p.tiles[w / p.n_tiles];
         const int j = w % p.n_tiles;
-        int b_row0, b_row1;
+        // the two 128-row blocks of W this tile multiplies with: block index inside the expert
+        int nb0, nb1;
         if (MODE == kModeGateUp) {
-          b_row0 = tile.expert * p.n_rows + j * 128;
-          b_row1 = b_row0 + p.inter;
+          nb0 = j;
+          nb1 = p.inter / 128 + j;
         } else {
-          b_row0 = tile.expert * p.n_rows + j * kTileN;
-          b_row1 = b_row0 + 128;
+          nb0 = 2 * j;
+          nb1 = 2 * j + 1;
         }
+        const int sblocks = p.n_rows / 128;
+        // row-major weights: block (nb, kb) starts at row expert*n_rows + nb*128, column kb*128;
+        // tiled weights: it is the contiguous 16 KiB block number (expert*sblocks + nb)*k_blocks + kb
+        const int b_row0 = p.tiled ? (tile.expert * sblocks + nb0) * p.k_blocks * 128 : tile.expert * p.n_rows + nb0 * 128;
+        const int b_row1 = p.tiled ? (tile.expert * sblocks + nb1) * p.k_blocks * 128 : tile.expert * p.n_rows + nb1 * 128;
         for (int kb = 0; kb < p.k_blocks; ++kb, ++it) {
           const uint32_t slot = it % kGemmStages, phase = (it / kGemmStages) & 1;
           alive = mbar_wait(bar_empty + 8 * slot, phase ^ 1, p.err);
@@ -146,8 +153,9 @@ moe_fp8_gemm_kernel(const __grid_constant__ CUtensorMap a_map,
           const uint32_t sa = ring + slot * kStageBytesG, sb = sa + kABytes;
           mbar_arrive_expect_tx(bar_full + 8 * slot, kStageBytesG);
           tma_load_2d(sa, &a_map, bar_full + 8 * slot, kb * kBlockK, tile.row0);
-          tma_load_2d(sb, &b_map, bar_full + 8 * slot, kb * kBlockK, b_row0);
-          tma_load_2d(sb + kBBytes / 2, &b_map, bar_full + 8 * slot, kb * kBlockK, b_row1);
+          const int bx = p.tiled ? 0 : kb * kBlockK, by = p.tiled ? kb * 128 : 0;
+          tma_load_2d(sb, &b_map, bar_full + 8 * slot, bx, b_row0 + by);
+          tma_load_2d(sb + kBBytes / 2, &b_map, bar_full + 8 * slot, bx, b_row1 + by);
         }
       }
     }
@@ -368,7 +376,7 @@ extern "C" int b200_moe_fp8_gemm_gate_up(const void* xq, const float* x_scale, c
                                          const float* w13_scale_inv, const void* tiles,
                                          const int32_t* num_tiles, void* hq, float* h_scale,
                                          void* status_word, int num_rows, int num_experts,
-                                         int hidden, int inter, void* stream) {
+                                         int hidden, int inter, int weight_layout, void* stream) {
   B200_REQUIRE(xq && x_scale && w13 && w13_scale_inv && tiles && num_tiles && hq && h_scale,
                "moe_fp8_gemm_gate_up: null pointer");
   B200_REQUIRE(num_rows >= 0 && num_experts > 0, "moe_fp8_gemm_gate_up: bad row/expert count");
@@ -382,7 +390,12 @@ extern "C" int b200_moe_fp8_gemm_gate_up(const void* xq, const float* x_scale, c
   CUtensorMap a_map, b_map;
   rc = get_tensor_map_2d(xq, num_rows, hidden, 1, 128, 128, &a_map);
   if (rc) return rc;
-  rc = get_tensor_map_2d(w13, static_cast<uint64_t>(num_experts) * 2 * inter, hidden, 1, 128, 128, &b_map);
+  B200_REQUIRE(weight_layout == 0 || weight_layout == 1, "moe_fp8_gemm_gate_up: weight_layout %d is neither 0 nor 1",
+               weight_layout);
+  if (weight_layout == 1)
+    rc = get_tensor_map_2d(w13, static_cast<uint64_t>(num_experts) * 2 * inter * (hidden / 128), 128, 1, 128, 128, &b_map);
+  else
+    rc = get_tensor_map_2d(w13, static_cast<uint64_t>(num_experts) * 2 * inter, hidden, 1, 128, 128, &b_map);
   if (rc) return rc;
   GemmParams p{};
   p.a_scale = x_scale;
@@ -396,6 +409,7 @@ extern "C" int b200_moe_fp8_gemm_gate_up(const void* xq, const float* x_scale, c
   p.n_rows = 2 * inter;
   p.inter = inter;
   p.n_tiles = inter / 128;
+  p.tiled = weight_layout;
   return launch_gemm<kModeGateUp>(a_map, b_map, p, as_stream(stream));
 }
 
@@ -403,7 +417,7 @@ extern "C" int b200_moe_fp8_gemm_down(const void* hq, const float* h_scale, cons
                                       const float* w2_scale_inv, const void* tiles,
                                       const int32_t* num_tiles, void* y_sorted, void* status_word,
                                       int num_rows, int num_experts, int hidden, int inter,
-                                      void* stream) {
+                                      int weight_layout, void* stream) {
   B200_REQUIRE(hq && h_scale && w2 && w2_scale_inv && tiles && num_tiles && y_sorted,
                "moe_fp8_gemm_down: null pointer");
   B200_REQUIRE(num_rows >= 0 && num_experts > 0, "moe_fp8_gemm_down: bad row/expert count");
@@ -417,7 +431,12 @@ extern "C" int b200_moe_fp8_gemm_down(const void* hq, const float* h_scale, cons
   CUtensorMap a_map, b_map;
   rc = get_tensor_map_2d(hq, num_rows, inter, 1, 128, 128, &a_map);
   if (rc) return rc;
-  rc = get_tensor_map_2d(w2, static_cast<uint64_t>(num_experts) * hidden, inter, 1, 128, 128, &b_map);
+  B200_REQUIRE(weight_layout == 0 || weight_layout == 1, "moe_fp8_gemm_down: weight_layout %d is neither 0 nor 1",
+               weight_layout);
+  if (weight_layout == 1)
+    rc = get_tensor_map_2d(w2, static_cast<uint64_t>(num_experts) * hidden * (inter / 128), 128, 1, 128, 128, &b_map);
+  else
+    rc = get_tensor_map_2d(w2, static_cast<uint64_t>(num_experts) * hidden, inter, 1, 128, 128, &b_map);
   if (rc) return rc;
   GemmParams p{};
   p.a_scale = h_scale;
@@ -430,5 +449,6 @@ extern "C" int b200_moe_fp8_gemm_down(const void* hq, const float* h_scale, cons
   p.n_rows = hidden;
   p.inter = inter;
   p.n_tiles = hidden / kTileN;
+  p.tiled = weight_layout;
   return launch_gemm<kModeDown>(a_map, b_map, p, as_stream(stream));
 }

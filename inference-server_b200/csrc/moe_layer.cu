@@ -63,7 +63,7 @@ static int moe_forward_impl(const void* x, const void* router_logits, int logits
                             const float* w13_scale_inv, const void* w2, const float* w2_scale_inv,
                             void* out, void* residual, const void* norm_weight, float eps, void* workspace,
                             size_t workspace_bytes, int num_tokens, int num_experts, int top_k, int hidden,
-                            int inter, int renormalize, void* stream) {
+                            int inter, int renormalize, int weight_layout, void* stream) {
   B200_REQUIRE(x && router_logits && w13 && w13_scale_inv && w2 && w2_scale_inv && out && workspace,
                "moe_fp8_forward: null pointer");
   B200_REQUIRE(num_tokens >= 0 && num_experts > 0 && top_k > 0 && hidden > 0 && inter > 0,
@@ -97,11 +97,11 @@ static int moe_forward_impl(const void* x, const void* router_logits, int logits
   if (rc) return rc;
   rc = b200_moe_fp8_gemm_gate_up(ws + c.xq, reinterpret_cast<float*>(ws + c.xs), w13, w13_scale_inv,
                                  tiles, num_tiles, ws + c.hq, reinterpret_cast<float*>(ws + c.hs),
-                                 status, rows, num_experts, hidden, inter, stream);
+                                 status, rows, num_experts, hidden, inter, weight_layout, stream);
   if (rc) return rc;
   rc = b200_moe_fp8_gemm_down(ws + c.hq, reinterpret_cast<float*>(ws + c.hs), w2, w2_scale_inv,
                               tiles, num_tiles, ws + c.y, status, rows, num_experts, hidden, inter,
-                              stream);
+                              weight_layout, stream);
   if (rc) return rc;
   if (residual != nullptr)
     return b200_moe_combine_add_rmsnorm(ws + c.y, row_of_pair, topk_w, residual, norm_weight, eps, num_tokens,
@@ -114,10 +114,10 @@ extern "C" int b200_moe_fp8_forward(const void* x, const void* router_logits, in
                                     const float* w2_scale_inv, void* out, void* workspace,
                                     size_t workspace_bytes, int num_tokens, int num_experts,
                                     int top_k, int hidden, int inter, int renormalize,
-                                    void* stream) {
+                                    int weight_layout, void* stream) {
   return moe_forward_impl(x, router_logits, logits_dtype, w13, w13_scale_inv, w2, w2_scale_inv, out, nullptr,
                           nullptr, 0.f, workspace, workspace_bytes, num_tokens, num_experts, top_k, hidden, inter,
-                          renormalize, stream);
+                          renormalize, weight_layout, stream);
 }
 
 extern "C" int b200_moe_fp8_forward_add_rmsnorm(const void* x, const void* router_logits, int logits_dtype,
@@ -126,9 +126,9 @@ extern "C" int b200_moe_fp8_forward_add_rmsnorm(const void* x, const void* route
                                                 const void* norm_weight, float eps, void* normed_out,
                                                 void* workspace, size_t workspace_bytes, int num_tokens,
                                                 int num_experts, int top_k, int hidden, int inter,
-                                                int renormalize, void* stream) {
+                                                int renormalize, int weight_layout, void* stream) {
   B200_REQUIRE(residual && norm_weight && normed_out, "moe_fp8_forward_add_rmsnorm: null pointer");
   return moe_forward_impl(x, router_logits, logits_dtype, w13, w13_scale_inv, w2, w2_scale_inv, normed_out,
                           residual, norm_weight, eps, workspace, workspace_bytes, num_tokens, num_experts, top_k,
-                          hidden, inter, renormalize, stream);
+                          hidden, inter, renormalize, weight_layout, stream);
 }

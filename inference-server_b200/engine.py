@@ -109,6 +109,7 @@ def random_layer(cfg: ModelConfig, device, gen: torch.Generator, std: float = 0.
     n_exp = local_experts or cfg.experts
     w.w13, w.w13_scale = quant.quantize_weight_blocks(rn(n_exp, 2 * cfg.moe_inter, H))
     w.w2, w.w2_scale = quant.quantize_weight_blocks(rn(n_exp, H, cfg.moe_inter))
+    w.w13, w.w2 = quant.tile_weight_blocks(w.w13), quant.tile_weight_blocks(w.w2)
     return w
 
 
@@ -129,6 +130,7 @@ def layer_from_hf(layer, device) -> LayerWeights:
     w.router = dev(mlp.gate.weight)
     w.w13, w.w13_scale = quant.quantize_weight_blocks(mlp.experts.gate_up_proj.detach().to(device).float())
     w.w2, w.w2_scale = quant.quantize_weight_blocks(mlp.experts.down_proj.detach().to(device).float())
+    w.w13, w.w2 = quant.tile_weight_blocks(w.w13), quant.tile_weight_blocks(w.w2)
     return w
 
 

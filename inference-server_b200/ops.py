@@ -250,6 +250,16 @@ def _as_u8(t: torch.Tensor) -> torch.Tensor:
     return t.view(torch.uint8) if t.dtype != torch.uint8 else t
 
 
+def _weight_dims(w: torch.Tensor):
+    """(num_experts, rows, cols, layout code) of an expert weight tensor: 3-D [E, rows, cols] is the
+    row-major checkpoint layout, 5-D [E, rows/128, cols/128, 128, 128] the tiled one (quant.tile_weight_blocks)."""
+    if w.dim() == 3:
+        return w.shape[0], w.shape[1], w.shape[2], 0
+    if w.dim() == 5 and w.shape[3] == 128 and w.shape[4] == 128:
+        return w.shape[0], w.shape[1] * 128, w.shape[2] * 128, 1
+    raise ValueError(f"expert weights must be [E, rows, cols] or [E, rows/128, cols/128, 128, 128], got {tuple(w.shape)}")
+
+
 def moe_fp8_gemm_gate_up(xq, x_scale, w13, w13_scale_inv, perm: Permutation, status=None):
     """h = silu(W13[:I] x) * (W13[I:] x) per sorted row, re-quantised to e4m3."""
     xq, w13 = _as_u8(xq), _as_u8(w13)
@@ -258,7 +268,7 @@ def moe_fp8_gemm_gate_up(xq, x_scale, w13, w13_scale_inv, perm: Permutation, sta
     _need(x_scale, "x_scale", torch.float32)
     _need(w13_scale_inv, "w13_scale_inv", torch.float32)
     rows, H = xq.shape
-    E, two_i, H2 = w13.shape
+    E, two_i, H2, layout = _weight_dims(w13)
     inter = two_i // 2
     if H2 != H or tuple(w13_scale_inv.shape) != (E, two_i // 128, H // 128):
         raise ValueError("w13 / scale shapes do not match")
@@ -266,7 +276,7 @@ def moe_fp8_gemm_gate_up(xq, x_scale, w13, w13_scale_inv, perm: Permutation, sta
     hs = torch.empty(rows, inter // 128, dtype=torch.float32, device=xq.device)
     rc = _lib.load().b200_moe_fp8_gemm_gate_up(
         _ptr(xq), _ptr(x_scale), _ptr(w13), _ptr(w13_scale_inv), _ptr(perm.tiles), _ptr(perm.num_tiles),
-        _ptr(hq), _ptr(hs), _ptr(status), rows, E, H, inter, _stream(),
+        _ptr(hq), _ptr(hs), _ptr(status), rows, E, H, inter, layout, _stream(),
     )
     check(rc, "b200_moe_fp8_gemm_gate_up")
     return hq, hs
@@ -280,13 +290,13 @@ def moe_fp8_gemm_down(hq, h_scale, w2, w2_scale_inv, perm: Permutation, status=N
     _need(h_scale, "h_scale", torch.float32)
     _need(w2_scale_inv, "w2_scale_inv", torch.float32)
     rows, inter = hq.shape
-    E, H, inter2 = w2.shape
+    E, H, inter2, layout = _weight_dims(w2)
     if inter2 != inter or tuple(w2_scale_inv.shape) != (E, H // 128, inter // 128):
         raise ValueError("w2 / scale shapes do not match")
     y = torch.empty(rows, H, dtype=torch.bfloat16, device=hq.device)
     rc = _lib.load().b200_moe_fp8_gemm_down(
         _ptr(hq), _ptr(h_scale), _ptr(w2), _ptr(w2_scale_inv), _ptr(perm.tiles), _ptr(perm.num_tiles),
-        _ptr(y), _ptr(status), rows, E, H, inter, _stream(),
+        _ptr(y), _ptr(status), rows, E, H, inter, layout, _stream(),
     )
     check(rc, "b200_moe_fp8_gemm_down")
     return y
@@ -342,7 +352,9 @@ def moe_fp8_forward(x, router_logits, w13, w13_scale_inv, w2, w2_scale_inv, top_
     _need(w13_scale_inv, "w13_scale_inv", torch.float32)
     _need(w2_scale_inv, "w2_scale_inv", torch.float32)
     T, H = x.shape
-    E, two_i, _ = w13.shape
+    E, two_i, _, layout = _weight_dims(w13)
+    if _weight_dims(w2)[3] != layout:
+        raise ValueError("w13 and w2 must use the same weight layout")
     inter = two_i // 2
     if workspace is None:
         workspace = moe_fp8_workspace(T, E, top_k, H, inter, x.device)
@@ -353,7 +365,7 @@ def moe_fp8_forward(x, router_logits, w13, w13_scale_inv, w2, w2_scale_inv, top_
     if residual is None:
         rc = lib.b200_moe_fp8_forward(
             _ptr(x), _ptr(router_logits), ld, _ptr(w13), _ptr(w13_scale_inv), _ptr(w2), _ptr(w2_scale_inv),
-            _ptr(out), _ptr(workspace), workspace.numel(), T, E, top_k, H, inter, int(renormalize), _stream())
+            _ptr(out), _ptr(workspace), workspace.numel(), T, E, top_k, H, inter, int(renormalize), layout, _stream())
         check(rc, "b200_moe_fp8_forward")
     else:
         _need(residual, "residual", torch.bfloat16)
@@ -361,6 +373,6 @@ def moe_fp8_forward(x, router_logits, w13, w13_scale_inv, w2, w2_scale_inv, top_
         rc = lib.b200_moe_fp8_forward_add_rmsnorm(
             _ptr(x), _ptr(router_logits), ld, _ptr(w13), _ptr(w13_scale_inv), _ptr(w2), _ptr(w2_scale_inv),
             _ptr(residual), _ptr(norm_weight), float(eps), _ptr(out), _ptr(workspace), workspace.numel(), T, E,
-            top_k, H, inter, int(renormalize), _stream())
+            top_k, H, inter, int(renormalize), layout, _stream())
         check(rc, "b200_moe_fp8_forward_add_rmsnorm")
     return out

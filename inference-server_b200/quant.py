@@ -36,3 +36,18 @@ def dequantize_weight_blocks(q: torch.Tensor, scale_inv: torch.Tensor) -> torch.
     lead = q.shape[:-2]
     t = q.to(torch.float32).reshape(*lead, rows // BLOCK, BLOCK, cols // BLOCK, BLOCK)
     return (t * scale_inv.unsqueeze(-1).unsqueeze(-3)).reshape(q.shape)
+
+
+def tile_weight_blocks(q: torch.Tensor) -> torch.Tensor:
+    """[..., rows, cols] -> [..., rows/128, cols/128, 128, 128]: every 128x128 block contiguous (16 KiB
+    of e4m3), the layout the grouped GEMM streams fastest (one sequential read per TMA box)."""
+    rows, cols = q.shape[-2], q.shape[-1]
+    lead = q.shape[:-2]
+    return q.reshape(*lead, rows // BLOCK, BLOCK, cols // BLOCK, BLOCK).transpose(-3, -2).contiguous()
+
+
+def untile_weight_blocks(t: torch.Tensor) -> torch.Tensor:
+    """Inverse of tile_weight_blocks."""
+    rb, cb = t.shape[-4], t.shape[-3]
+    lead = t.shape[:-4]
+    return t.transpose(-3, -2).reshape(*lead, rb * BLOCK, cb * BLOCK).contiguous()

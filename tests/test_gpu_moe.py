@@ -165,6 +165,24 @@ def test_gemm_stages_against_oracle(ops, T, E, K, H, I):
     assert rel_err(out, ref) < TOL
 
 
+@pytest.mark.parametrize("T,E,K,H,I", [(16, 16, 4, 512, 256), (64, 128, 8, 2048, 768), (300, 8, 2, 512, 256)])
+def test_tiled_weight_layout_gives_identical_bits(ops, T, E, K, H, I):
+    """Re-ordering the e4m3 weights into contiguous 128x128 blocks changes addresses, not arithmetic."""
+    from conftest import pkg
+    quant = pkg("quant")
+    w13q, w13s, w2q, w2s = make_layer(E, H, I, seed=E + H)
+    assert torch.equal(quant.untile_weight_blocks(quant.tile_weight_blocks(w13q.view(torch.uint8))), w13q.view(torch.uint8))
+    g = torch.Generator().manual_seed(T)
+    x = torch.randn(T, H, generator=g).bfloat16().to(DEV)
+    logits = torch.randn(T, E, generator=g).to(DEV)
+    rm = [w13q.view(torch.uint8).to(DEV), w13s.to(DEV), w2q.view(torch.uint8).to(DEV), w2s.to(DEV)]
+    tl = [quant.tile_weight_blocks(rm[0]), rm[1], quant.tile_weight_blocks(rm[2]), rm[3]]
+    assert tl[0].shape == (E, 2 * I // 128, H // 128, 128, 128)
+    out_rm = ops.moe_fp8_forward(x, logits, *rm, K, True)
+    out_tl = ops.moe_fp8_forward(x, logits, *tl, K, True)
+    assert torch.equal(out_rm, out_tl)
+
+
 @pytest.mark.parametrize("T", [1, 16, 64, 256])
 def test_full_layer_config3_shapes(ops, T):
     E, K, H, I = 128, 8, 2048, 768
