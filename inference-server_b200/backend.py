@@ -100,9 +100,10 @@ class B200Backend:
             return
         want = (eng.cfg.kv_heads, PAGE, eng.cfg.head_dim)
         ok = (len(bm.k_pools) == eng.cfg.layers and all(
-            tuple(p.shape[1:]) == want and p.dtype == torch.bfloat16 and p.device.type == "cuda" for p in bm.k_pools))
+            tuple(p.shape[1:]) == want and p.dtype == torch.bfloat16 and p.device.type == torch.device(eng.device).type
+            for p in bm.k_pools))
         if not ok:
-            raise ValueError("CacheManager pools do not match the engine (need bf16 CUDA pools "
+            raise ValueError("CacheManager pools do not match the engine (need bf16 pools on the engine's device, "
                              f"[num_blocks, {want[0]}, {want[1]}, {want[2]}] per layer, block_size 16)")
         eng.k_pools, eng.v_pools = bm.k_pools, bm.v_pools
         eng.num_blocks = bm.total_blocks

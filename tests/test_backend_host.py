@@ -140,3 +140,46 @@ def test_reference_scheduler_drives_the_backend_unchanged(chunk):
         assert out == [last + 1 + j for j in range(3 + i)]
     assert stats["total_completed"] == 6
     assert len(be._alloc.free) == be.engine.num_blocks  # every page returned after eviction
+
+
+@pytest.mark.skipif(not HAVE_REF, reason="reference checkout not present on this machine")
+def test_reference_cache_manager_pools_and_prefix_hits_are_used_in_place():
+    """With the reference's CacheManager attached (src/inference_server/kv_cache/cache_manager.py) the engine
+    adopts its pools, a later prompt with a cached prefix gets the cached FULL pages as shared, read-only
+    entries of its block table, and only the uncached suffix is run."""
+    sys.path.insert(0, os.path.join(REF, "src"))
+    from inference_server.kv_cache.cache_manager import CacheManager
+
+    be = make_backend(num_blocks=64, max_batch=8, max_pages=16)
+    cfg = be.engine.cfg
+    cache = CacheManager(64, 16, layer_shapes=[(cfg.kv_heads, cfg.head_dim)] * cfg.layers, device="cpu",
+                         dtype=torch.bfloat16)
+    be.set_cache_adapter(cache)
+    assert be.engine.k_pools is cache.block_manager.k_pools and be._alloc is None
+    for p in cache.block_manager.k_pools:  # make stored pages recognisable
+        p.copy_(torch.arange(p.numel(), dtype=torch.float32).reshape(p.shape) % 251)
+
+    prompt_a = list(range(1000, 1040))  # 40 tokens = 2 full pages + 8
+    kv_a, _, n_a = be.prefill(prompt_a, "a")
+    assert n_a == 40 and be.last_cache_hit_tokens == 0 and be.engine.prefill_calls[-1] == (40, 0)
+    stored = cache._exact_index[tuple(prompt_a)]
+    assert [b.num_tokens_stored for b in stored] == [16, 16, 8]
+    used_before = cache.block_manager.used_blocks
+
+    prompt_b = prompt_a[:36] + [7, 8, 9, 10, 11]  # shares 36 tokens -> 2 full pages usable
+    kv_b, _, n_b = be.prefill(prompt_b, "b")
+    assert be.last_cache_hit_tokens == 32 and be.engine.prefill_calls[-1] == (41, 32)
+    assert kv_b.block_ids[:2] == [stored[0].block_id, stored[1].block_id]  # shared pages, in place
+    assert kv_b.block_ids[2] not in [b.block_id for b in stored]           # the tail page is private
+    assert stored[0].ref_count >= 1                                        # protected while in use
+
+    batch = be.splice_into_batched(None, kv_a, n_a)
+    batch = be.splice_into_batched(batch, kv_b, n_b)
+    nxt, batch = be.decode_step_batched(torch.tensor([[1], [2]]), batch, None, None)
+    assert nxt.tolist() == [2, 3]
+    be.remove_row_from_cache(batch, 1)
+    be.remove_row_from_cache(batch, 0)
+    cache.release(prompt_a, "a")
+    cache.release(prompt_b, "b")
+    # private pages went back to the reference allocator; cached prompt pages stay cached
+    assert cache.block_manager.used_blocks <= used_before + 3
