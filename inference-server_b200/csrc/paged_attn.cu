@@ -32,8 +32,6 @@
 // split, fp32 arithmetic throughout.  It serves shapes the main kernel does not
 // (the tiny fp32 parity model) and is not tuned.
 
-#include <stdlib.h>
-
 #include <mutex>
 
 #include "common.cuh"
@@ -590,15 +588,14 @@ extern "C" int b200_paged_attn_decode(const void* q, const void* k_pool, const v
     }
 #define B200_ATTN_ARGS q, k_pool, v_pool, block_table, ctx_lens, out, w, batch, num_q_heads, num_blocks, \
                        max_pages_per_seq, scale, split_tokens, ms, st
-    static const int variant = getenv("B200_ATTN_VARIANT") ? atoi(getenv("B200_ATTN_VARIANT")) : 0;
     if (head_dim == 128) {
       switch (num_kv_heads) {
         case 1: return launch_main<128, 1, 8, 4>(B200_ATTN_ARGS);
         case 2: return launch_main<128, 2, 6, 2>(B200_ATTN_ARGS);
         case 4:
-          if (variant == 1) return launch_main<128, 4, 2, 3>(B200_ATTN_ARGS);
-          if (variant == 2) return launch_main<128, 4, 6, 1>(B200_ATTN_ARGS);
-          if (variant == 3) return launch_main<128, 4, 4, 1>(B200_ATTN_ARGS);
+          // measured on B200: few sequences (per-CTA fixed cost dominates) run best with three shallow CTAs per
+          // SM, a full decode batch with two deeper ones
+          if (batch <= 96) return launch_main<128, 4, 2, 3>(B200_ATTN_ARGS);
           return launch_main<128, 4, 3, 2>(B200_ATTN_ARGS);
         default: return launch_main<128, 8, 3, 1>(B200_ATTN_ARGS);
       }

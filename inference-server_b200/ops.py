@@ -45,6 +45,9 @@ def default_split_tokens(batch: int, num_kv_heads: int, max_ctx: int, num_sms: i
     """Tokens per KV split.  One CTA covers one split of one sequence (all kv
     heads): aim for a few waves of CTAs, keep a split at least 128 tokens so the
     pipeline fill is amortised, at most 1024 so ragged lengths still balance."""
+    if batch <= 96:
+        # few sequences: the per-CTA fixed cost dominates, long splits win (measured at 64 rows)
+        return int(min(1024, max(128, ((max_ctx + 63) // 64) * 64)))
     target_ctas = 6 * num_sms
     per_seq = max(1, target_ctas // max(1, batch))
     split = (max_ctx // 2 + per_seq - 1) // per_seq  # typical row is about half the table width
