@@ -42,8 +42,8 @@ if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 
 PAGE = 16
-# dram read+write bytes per algorithmic byte of the attention kernel, from the ncu capture summarised in
-# profiles/paged_attn_decode_small_case.md (same kernel, 16 rows x 4096 tokens; traffic grows with the pages read)
+# dram read+write bytes per algorithmic byte of the attention kernel, from an ncu capture of the same kernel on a
+# small case (16 rows x 4096 tokens, 134 MB of KV); traffic grows in proportion to the pages read
 ATTN_TRAFFIC_PER_ALG_BYTE = 1.047
 
 

@@ -43,8 +43,9 @@ def read_status(status: torch.Tensor, where: str = "device status") -> None:
 
 def default_split_tokens(batch: int, num_kv_heads: int, max_ctx: int, num_sms: int = 148) -> int:
     """Tokens per KV split.  One CTA covers one split of one sequence (all kv
-    heads): aim for a few waves of CTAs, keep a split at least 128 tokens so the
-    pipeline fill is amortised, at most 1024 so ragged lengths still balance."""
+    heads, so `num_kv_heads` does not enter): aim for a few waves of CTAs, keep a
+    split at least 128 tokens so the pipeline fill is amortised, at most 1024 so
+    ragged lengths still balance."""
     if batch <= 96:
         # few sequences: the per-CTA fixed cost dominates, long splits win (measured at 64 rows)
         return int(min(1024, max(128, ((max_ctx + 63) // 64) * 64)))

@@ -1,7 +1,7 @@
 """Generates the golden fixtures in this directory from the REAL reference.
 
-Run where the reference checkout exists (default /root/reference, override with
-REFERENCE_ROOT):
+Run where the reference checkout exists (default: a directory `reference` next to this
+repository; override with REFERENCE_ROOT):
 
     python tests/golden/make_golden.py
 
@@ -21,7 +21,8 @@ import numpy as np
 import torch
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-REF = os.environ.get("REFERENCE_ROOT", "/root/reference")
+REPO = os.path.dirname(os.path.dirname(HERE))
+REF = os.environ.get("REFERENCE_ROOT", os.path.join(os.path.dirname(REPO), "reference"))
 sys.path.insert(0, os.path.join(REF, "src"))
 
 from inference_server.kv_cache.block_manager import BlockManager  # noqa: E402

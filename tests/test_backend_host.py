@@ -8,9 +8,10 @@ import sys
 import pytest
 import torch
 
-from conftest import pkg
+from conftest import ROOT, pkg
 
-REF = os.environ.get("REFERENCE_ROOT", "/root/reference")
+# the reference checkout: a directory `reference` next to this repository unless REFERENCE_ROOT says otherwise
+REF = os.environ.get("REFERENCE_ROOT", os.path.join(os.path.dirname(ROOT), "reference"))
 HAVE_REF = os.path.isdir(os.path.join(REF, "src", "inference_server"))
 
 
