@@ -73,7 +73,8 @@ def test_golden_bf16_tma_kernel(ops, name, split):
     assert rel_err(out, torch.from_numpy(g["out"])) < 3e-2
 
 
-@pytest.mark.parametrize("Hq,Hkv,D", [(32, 4, 128), (8, 2, 64), (64, 4, 128), (4, 4, 128), (16, 4, 64)])
+@pytest.mark.parametrize("Hq,Hkv,D", [(32, 4, 128), (8, 2, 64), (64, 4, 128), (4, 4, 128), (16, 4, 64),
+                                       (8, 1, 128), (64, 8, 128), (16, 2, 128), (16, 1, 64), (32, 8, 64), (12, 4, 128)])
 def test_ragged_lengths_and_split_boundaries(ops, Hq, Hkv, D):
     lens = [1, 15, 16, 17, 63, 64, 65, 255, 256, 257, 300, 511, 512, 513, 1000, 0]
     q, kp, vp, table, ctx = build_case(len(lens), Hq, Hkv, D, lens, seed=7)
