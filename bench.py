@@ -143,6 +143,7 @@ def main():
     ap.add_argument("--batch", type=int, default=256, help="concurrent sequences per GPU")
     ap.add_argument("--gen-tokens", type=int, default=256)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--split-tokens", type=int, default=0, help="attention KV split size (0 = the library default)")
     ap.add_argument("--ep", action="store_true",
                     help="N > 1: expert-parallel MoE (NCCL all-to-all dispatch/combine) instead of independent replicas")
     args = ap.parse_args()
@@ -191,7 +192,7 @@ def main():
     t_setup = time.time()
     ep_group = torch.distributed.group.WORLD if world > 1 and args.ep else None
     engine = eng_mod.DecodeEngine(cfg, num_blocks=num_blocks, max_batch=args.batch, max_pages_per_seq=max_pages,
-                                  device=dev, seed=rank, ep_group=ep_group)
+                                  device=dev, seed=rank, ep_group=ep_group, split_tokens=args.split_tokens or None)
     # KV image: one random pool, shared by all layers (contents do not affect timing)
     g = torch.Generator(device=dev).manual_seed(1000 + rank)
     engine.k_pools[0].normal_(generator=g)
