@@ -199,8 +199,10 @@ size_t b200_moe_permute_workspace_bytes(int num_tokens, int num_experts, int top
 int b200_moe_max_tiles(int num_tokens, int num_experts, int top_k);
 int b200_moe_permute(const int32_t* topk_ids, int num_tokens, int num_experts, int top_k,
                      int32_t* sorted_pair_ids, int32_t* row_of_pair, int32_t* expert_offsets,
-                     void* tiles, int32_t* num_tiles, void* workspace, size_t workspace_bytes,
-                     void* stream);
+                     void* tiles, int32_t* num_tiles, int tile_experts, void* workspace,
+                     size_t workspace_bytes, void* stream);
+/* tile_experts: only experts [0, tile_experts) get row tiles (0 = all).  The expert-parallel receive side
+ * sorts its slots with one extra dummy expert for empty slots and sets tile_experts to the real count. */
 
 /*
  * b200_moe_permute and b200_act_quant_fp8 (below) in one pass: the token rows of
@@ -211,6 +213,26 @@ int b200_moe_permute_quant(const int32_t* topk_ids, const void* x, int num_token
                            int top_k, int hidden, int32_t* sorted_pair_ids, int32_t* row_of_pair,
                            int32_t* expert_offsets, void* tiles, int32_t* num_tiles, void* xq,
                            float* x_scale, void* workspace, size_t workspace_bytes, void* stream);
+
+/*
+ * Expert-parallel form of b200_moe_permute_quant (no counterpart in the reference, which is single-device):
+ * experts are owned by ep_world ranks in equal contiguous id ranges.  The quantised row of pair p goes to row
+ * slot_of_pair[p] = owner * ep_capacity + (position among this rank's rows for that owner) of the send buffers
+ * xq_send / x_scale_send [ep_world * ep_capacity rows], expert_of_slot gets the owner-local expert id of every
+ * used slot (the caller pre-fills it with the "empty" id), pairs beyond the capacity get slot -1 and set
+ * *overflow to 1.
+ */
+int b200_moe_permute_quant_ep(const int32_t* topk_ids, const void* x, int num_tokens, int num_experts,
+                              int top_k, int hidden, int ep_world, int ep_capacity,
+                              int32_t* sorted_pair_ids, int32_t* row_of_pair, int32_t* expert_offsets,
+                              void* tiles, int32_t* num_tiles, void* xq_send, float* x_scale_send,
+                              int32_t* slot_of_pair, int32_t* expert_of_slot, int32_t* overflow,
+                              void* workspace, size_t workspace_bytes, void* stream);
+
+/* dst row i = src row order[i], for e4m3 rows [rows, hidden] and their scales [rows, hidden/128]
+ * (the receive side of the expert-parallel exchange brings its slots into expert-sorted order with it). */
+int b200_gather_rows_fp8(const void* src_q, const float* src_scale, const int32_t* order, int num_rows,
+                         int hidden, void* dst_q, float* dst_scale, void* stream);
 
 /*
  * Replaces: the dynamic per-token activation quantisation of the FP8 expert
@@ -238,7 +260,8 @@ int b200_act_quant_fp8(const void* x, const int32_t* row_of_pair, int num_tokens
  * down:    y = W2[e] h per sorted row.
  *   w2 [num_experts, hidden, inter] e4m3,
  *   w2_scale_inv [num_experts, hidden/128, inter/128] fp32
- *   y_sorted [num_rows, hidden] bf16
+ *   y_sorted [num_rows, hidden] bf16; with out_row_map (int32 [num_rows], may be NULL) sorted row r is
+ *   written to row out_row_map[r] instead of row r
  * tiles/num_tiles come from b200_moe_permute; status_word may be NULL.
  *
  * weight_layout: B200_WEIGHTS_ROW_MAJOR - the arrays above as written (the
@@ -256,7 +279,8 @@ int b200_moe_fp8_gemm_gate_up(const void* xq, const float* x_scale, const void* 
                               int inter, int weight_layout, void* stream);
 int b200_moe_fp8_gemm_down(const void* hq, const float* h_scale, const void* w2,
                            const float* w2_scale_inv, const void* tiles, const int32_t* num_tiles,
-                           void* y_sorted, void* status_word, int num_rows, int num_experts,
+                           void* y_sorted, const int32_t* out_row_map, void* status_word, int num_rows,
+                           int num_experts,
                            int hidden, int inter, int weight_layout, void* stream);
 
 /*

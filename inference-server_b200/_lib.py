@@ -34,12 +34,14 @@ SIGNATURES = {
     "b200_moe_max_tiles": (c_int, [c_int] * 3),
     "b200_moe_permute": (
         c_int,
-        [c_void_p, c_int, c_int, c_int] + [c_void_p] * 6 + [c_size_t, c_void_p],
+        [c_void_p, c_int, c_int, c_int] + [c_void_p] * 5 + [c_int, c_void_p, c_size_t, c_void_p],
     ),
     "b200_moe_permute_quant": (c_int, [c_void_p, c_void_p] + [c_int] * 4 + [c_void_p] * 8 + [c_size_t, c_void_p]),
+    "b200_moe_permute_quant_ep": (c_int, [c_void_p, c_void_p] + [c_int] * 6 + [c_void_p] * 11 + [c_size_t, c_void_p]),
+    "b200_gather_rows_fp8": (c_int, [c_void_p] * 3 + [c_int, c_int] + [c_void_p] * 3),
     "b200_act_quant_fp8": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p]),
     "b200_moe_fp8_gemm_gate_up": (c_int, [c_void_p] * 9 + [c_int] * 5 + [c_void_p]),
-    "b200_moe_fp8_gemm_down": (c_int, [c_void_p] * 8 + [c_int] * 5 + [c_void_p]),
+    "b200_moe_fp8_gemm_down": (c_int, [c_void_p] * 9 + [c_int] * 5 + [c_void_p]),
     "b200_moe_combine": (c_int, [c_void_p] * 3 + [c_int] * 3 + [c_void_p, c_void_p]),
     "b200_moe_combine_add_rmsnorm": (c_int, [c_void_p] * 5 + [c_float] + [c_int] * 3 + [c_void_p, c_void_p]),
     "b200_moe_fp8_workspace_bytes": (c_size_t, [c_int] * 5),

@@ -73,6 +73,7 @@ struct GemmParams {
   uint8_t* hq;           // gate/up: [rows, inter] e4m3
   float* hs;             // gate/up: [rows, inter / 128]
   __nv_bfloat16* y;      // down:    [rows, n_rows]
+  const int* out_row_map;  // down: output row of each sorted row, or null for the identity
   int* err;
   int k_blocks;          // K / 128
   int n_rows;            // weight rows per expert (2 * inter, or hidden)
@@ -315,7 +316,8 @@ moe_fp8_gemm_kernel(const __grid_constant__ CUtensorMap a_map,
         }
       } else {
         if (row_ok) {
-          __nv_bfloat16* dst = p.y + grow * p.n_rows + j * kTileN + half * 128;
+          const size_t orow = p.out_row_map ? static_cast<size_t>(__ldg(p.out_row_map + grow)) : grow;
+          __nv_bfloat16* dst = p.y + orow * p.n_rows + j * kTileN + half * 128;
 #pragma unroll
           for (int c = 0; c < 16; ++c) {
             uint4 o;
@@ -415,7 +417,8 @@ extern "C" int b200_moe_fp8_gemm_gate_up(const void* xq, const float* x_scale, c
 
 extern "C" int b200_moe_fp8_gemm_down(const void* hq, const float* h_scale, const void* w2,
                                       const float* w2_scale_inv, const void* tiles,
-                                      const int32_t* num_tiles, void* y_sorted, void* status_word,
+                                      const int32_t* num_tiles, void* y_sorted,
+                                      const int32_t* out_row_map, void* status_word,
                                       int num_rows, int num_experts, int hidden, int inter,
                                       int weight_layout, void* stream) {
   B200_REQUIRE(hq && h_scale && w2 && w2_scale_inv && tiles && num_tiles && y_sorted,
@@ -444,6 +447,7 @@ extern "C" int b200_moe_fp8_gemm_down(const void* hq, const float* h_scale, cons
   p.tiles = static_cast<const MoeTile*>(tiles);
   p.num_tiles = num_tiles;
   p.y = static_cast<__nv_bfloat16*>(y_sorted);
+  p.out_row_map = out_row_map;
   p.err = static_cast<int*>(status_word);
   p.k_blocks = inter / 128;
   p.n_rows = hidden;

@@ -100,7 +100,7 @@ static int moe_forward_impl(const void* x, const void* router_logits, int logits
                                  status, rows, num_experts, hidden, inter, weight_layout, stream);
   if (rc) return rc;
   rc = b200_moe_fp8_gemm_down(ws + c.hq, reinterpret_cast<float*>(ws + c.hs), w2, w2_scale_inv,
-                              tiles, num_tiles, ws + c.y, status, rows, num_experts, hidden, inter,
+                              tiles, num_tiles, ws + c.y, nullptr, status, rows, num_experts, hidden, inter,
                               weight_layout, stream);
   if (rc) return rc;
   if (residual != nullptr)

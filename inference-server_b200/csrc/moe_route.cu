@@ -119,7 +119,7 @@ constexpr int kScatterThreads = 256;
 
 __global__ void __launch_bounds__(kScatterThreads)
 moe_scatter_kernel(const int* __restrict__ topk_ids, const int* __restrict__ rank,
-                   const int* __restrict__ counts, int n_pairs, int E, int tile_rows,
+                   const int* __restrict__ counts, int n_pairs, int E, int tile_experts, int tile_rows,
                    int* __restrict__ sorted_pair, int* __restrict__ row_of_pair,
                    int* __restrict__ expert_offsets, MoeTile* __restrict__ tiles,
                    int* __restrict__ num_tiles, int* __restrict__ err) {
@@ -138,7 +138,9 @@ moe_scatter_kernel(const int* __restrict__ topk_ids, const int* __restrict__ ran
   if (blockIdx.x == 0) {
     for (int e = tid; e <= E; e += kScatterThreads) expert_offsets[e] = off[e];
     if (tiles != nullptr) {
-      for (int e = tid; e < E; e += kScatterThreads) {
+      // only the first `tile_experts` experts get row tiles (a trailing dummy expert that collects empty
+      // slots is sorted but never multiplied)
+      for (int e = tid; e < tile_experts; e += kScatterThreads) {
         int tp = 0;
         for (int j = 0; j < e; ++j) tp += (cnt[j] + tile_rows - 1) / tile_rows;
         const int nt = (cnt[e] + tile_rows - 1) / tile_rows;
@@ -150,7 +152,7 @@ moe_scatter_kernel(const int* __restrict__ topk_ids, const int* __restrict__ ran
           t.pad = 0;
           tiles[tp + j] = t;
         }
-        if (e == E - 1) *num_tiles = tp + nt;
+        if (e == tile_experts - 1) *num_tiles = tp + nt;
       }
     }
   }
@@ -244,7 +246,9 @@ __global__ void moe_scatter_quant_kernel(const __nv_bfloat16* __restrict__ x, co
                                          int* __restrict__ row_of_pair, int* __restrict__ expert_offsets,
                                          MoeTile* __restrict__ tiles, int* __restrict__ num_tiles,
                                          uint8_t* __restrict__ xq, float* __restrict__ xs,
-                                         int* __restrict__ err) {
+                                         int* __restrict__ err, int ep_world, int ep_capacity,
+                                         int* __restrict__ slot_of_pair, int* __restrict__ expert_of_slot,
+                                         int* __restrict__ overflow) {
   extern __shared__ int sm[];  // cnt[E], off[E+1], ntile[E], toff[E+1], warp_tot[32], dst[K]
   int* cnt = sm;
   int* off = cnt + E;
@@ -283,6 +287,20 @@ __global__ void moe_scatter_quant_kernel(const __nv_bfloat16* __restrict__ x, co
       d = off[e] + rank[pair];
       sorted_pair[d] = pair;
       row_of_pair[pair] = d;
+      if (slot_of_pair != nullptr) {
+        // expert-parallel dispatch: the row goes to slot (position among this rank's rows for the owner of
+        // expert e) of that owner's segment of the send buffer; rows past the capacity are dropped and flagged
+        const int e_local = E / ep_world, owner = e / e_local;
+        const int pos = d - off[owner * e_local];
+        if (pos < ep_capacity) {
+          d = owner * ep_capacity + pos;
+          expert_of_slot[d] = e - owner * e_local;
+        } else {
+          d = -1;
+          *overflow = 1;
+        }
+        slot_of_pair[pair] = d;
+      }
     }
     dst[tid] = d;
   }
@@ -442,13 +460,16 @@ extern "C" int b200_moe_max_tiles(int num_tokens, int num_experts, int top_k) {
 extern "C" int b200_moe_permute(const int32_t* topk_ids, int num_tokens, int num_experts, int top_k,
                                 int32_t* sorted_pair_ids, int32_t* row_of_pair,
                                 int32_t* expert_offsets, void* tiles, int32_t* num_tiles,
-                                void* workspace, size_t workspace_bytes, void* stream) {
+                                int tile_experts, void* workspace, size_t workspace_bytes, void* stream) {
   B200_REQUIRE(topk_ids && sorted_pair_ids && row_of_pair && expert_offsets && workspace,
                "moe_permute: null pointer");
   B200_REQUIRE((tiles == nullptr) == (num_tiles == nullptr),
                "moe_permute: tiles and num_tiles must be given together");
   B200_REQUIRE(num_tokens >= 0 && num_experts > 0 && num_experts <= 1024 && top_k > 0,
                "moe_permute: bad dimensions T=%d E=%d K=%d", num_tokens, num_experts, top_k);
+  B200_REQUIRE(tile_experts >= 0 && tile_experts <= num_experts, "moe_permute: tile_experts %d outside [0, %d]",
+               tile_experts, num_experts);
+  if (tile_experts == 0) tile_experts = num_experts;
   const size_t need = b200_moe_permute_workspace_bytes(num_tokens, num_experts, top_k);
   if (workspace_bytes < need) {
     set_detail("moe_permute: workspace %zu < required %zu", workspace_bytes, need);
@@ -466,17 +487,18 @@ extern "C" int b200_moe_permute(const int32_t* topk_ids, int num_tokens, int num
   B200_CUDA(cudaGetLastError());
   const int blocks = n_pairs > 0 ? (n_pairs + kScatterThreads - 1) / kScatterThreads : 1;
   moe_scatter_kernel<<<blocks, kScatterThreads, (2 * num_experts + 1) * sizeof(int), st>>>(
-      topk_ids, rank, counts, n_pairs, num_experts, 128, sorted_pair_ids, row_of_pair,
+      topk_ids, rank, counts, n_pairs, num_experts, tile_experts, 128, sorted_pair_ids, row_of_pair,
       expert_offsets, static_cast<MoeTile*>(tiles), num_tiles, err);
   B200_CUDA(cudaGetLastError());
   return 0;
 }
 
-extern "C" int b200_moe_permute_quant(const int32_t* topk_ids, const void* x, int num_tokens,
-                                      int num_experts, int top_k, int hidden, int32_t* sorted_pair_ids,
-                                      int32_t* row_of_pair, int32_t* expert_offsets, void* tiles,
-                                      int32_t* num_tiles, void* xq, float* x_scale, void* workspace,
-                                      size_t workspace_bytes, void* stream) {
+static int permute_quant_impl(const int32_t* topk_ids, const void* x, int num_tokens, int num_experts,
+                              int top_k, int hidden, int32_t* sorted_pair_ids, int32_t* row_of_pair,
+                              int32_t* expert_offsets, void* tiles, int32_t* num_tiles, void* xq,
+                              float* x_scale, void* workspace, size_t workspace_bytes, int ep_world,
+                              int ep_capacity, int32_t* slot_of_pair, int32_t* expert_of_slot,
+                              int32_t* overflow, void* stream) {
   B200_REQUIRE(topk_ids && x && sorted_pair_ids && row_of_pair && expert_offsets && tiles && num_tiles && xq &&
                    x_scale && workspace,
                "moe_permute_quant: null pointer");
@@ -505,7 +527,60 @@ extern "C" int b200_moe_permute_quant(const int32_t* topk_ids, const void* x, in
   moe_scatter_quant_kernel<<<num_tokens, hidden / 8, smem, st>>>(
       static_cast<const __nv_bfloat16*>(x), topk_ids, rank, counts, num_experts, top_k, hidden, 128,
       sorted_pair_ids, row_of_pair, expert_offsets, static_cast<MoeTile*>(tiles), num_tiles,
-      static_cast<uint8_t*>(xq), x_scale, err);
+      static_cast<uint8_t*>(xq), x_scale, err, ep_world, ep_capacity, slot_of_pair, expert_of_slot, overflow);
+  B200_CUDA(cudaGetLastError());
+  return 0;
+}
+
+extern "C" int b200_moe_permute_quant(const int32_t* topk_ids, const void* x, int num_tokens,
+                                      int num_experts, int top_k, int hidden, int32_t* sorted_pair_ids,
+                                      int32_t* row_of_pair, int32_t* expert_offsets, void* tiles,
+                                      int32_t* num_tiles, void* xq, float* x_scale, void* workspace,
+                                      size_t workspace_bytes, void* stream) {
+  return permute_quant_impl(topk_ids, x, num_tokens, num_experts, top_k, hidden, sorted_pair_ids, row_of_pair,
+                            expert_offsets, tiles, num_tiles, xq, x_scale, workspace, workspace_bytes, 1, 0,
+                            nullptr, nullptr, nullptr, stream);
+}
+
+extern "C" int b200_moe_permute_quant_ep(const int32_t* topk_ids, const void* x, int num_tokens,
+                                         int num_experts, int top_k, int hidden, int ep_world,
+                                         int ep_capacity, int32_t* sorted_pair_ids, int32_t* row_of_pair,
+                                         int32_t* expert_offsets, void* tiles, int32_t* num_tiles,
+                                         void* xq_send, float* x_scale_send, int32_t* slot_of_pair,
+                                         int32_t* expert_of_slot, int32_t* overflow, void* workspace,
+                                         size_t workspace_bytes, void* stream) {
+  B200_REQUIRE(ep_world >= 1 && num_experts % ep_world == 0 && ep_capacity > 0,
+               "moe_permute_quant_ep: %d experts over %d ranks, capacity %d", num_experts, ep_world, ep_capacity);
+  B200_REQUIRE(slot_of_pair && expert_of_slot && overflow, "moe_permute_quant_ep: null pointer");
+  return permute_quant_impl(topk_ids, x, num_tokens, num_experts, top_k, hidden, sorted_pair_ids, row_of_pair,
+                            expert_offsets, tiles, num_tiles, xq_send, x_scale_send, workspace, workspace_bytes,
+                            ep_world, ep_capacity, slot_of_pair, expert_of_slot, overflow, stream);
+}
+
+// Copies quantised rows and their scales into a new row order: dst row i = src row order[i].
+__global__ void gather_rows_fp8_kernel(const uint8_t* __restrict__ src_q, const float* __restrict__ src_s,
+                                       const int* __restrict__ order, int H, uint8_t* __restrict__ dst_q,
+                                       float* __restrict__ dst_s) {
+  const int i = blockIdx.x, tid = threadIdx.x;
+  const int srow = order[i];
+  const uint4 v = *reinterpret_cast<const uint4*>(src_q + static_cast<size_t>(srow) * H + tid * 16);
+  *reinterpret_cast<uint4*>(dst_q + static_cast<size_t>(i) * H + tid * 16) = v;
+  const int groups = H / 128;
+  if (tid < groups) dst_s[static_cast<size_t>(i) * groups + tid] = src_s[static_cast<size_t>(srow) * groups + tid];
+}
+
+extern "C" int b200_gather_rows_fp8(const void* src_q, const float* src_scale, const int32_t* order,
+                                    int num_rows, int hidden, void* dst_q, float* dst_scale, void* stream) {
+  B200_REQUIRE(src_q && src_scale && order && dst_q && dst_scale, "gather_rows_fp8: null pointer");
+  B200_REQUIRE(num_rows >= 0 && hidden > 0 && hidden % 512 == 0 && hidden <= 16384,
+               "gather_rows_fp8: hidden %d must be a multiple of 512", hidden);
+  B200_REQUIRE(((reinterpret_cast<uintptr_t>(src_q) | reinterpret_cast<uintptr_t>(dst_q)) & 15) == 0,
+               "gather_rows_fp8: buffers must be 16-byte aligned");
+  int rc = check_device(nullptr);
+  if (rc) return rc;
+  if (num_rows == 0) return 0;
+  gather_rows_fp8_kernel<<<num_rows, hidden / 16, 0, as_stream(stream)>>>(
+      static_cast<const uint8_t*>(src_q), src_scale, order, hidden, static_cast<uint8_t*>(dst_q), dst_scale);
   B200_CUDA(cudaGetLastError());
   return 0;
 }

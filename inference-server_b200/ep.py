@@ -11,8 +11,9 @@ that no step needs a host round trip:
     expert_of_slot [W*capacity]          local expert id at the destination, or
                                          E_local for an empty slot
 
-``plan_dispatch`` computes those index arrays with torch ops on whatever device
-the inputs live on; it is shared by the GPU path and by the CPU (gloo) tests.
+On the GPU the slot placement is done inside the scatter+quantise kernel
+(``b200_moe_permute_quant_ep``); ``plan_dispatch`` is the same arithmetic in torch
+ops, used by the CPU stand-in kernels of the gloo tests and as a cross-check.
 """
 from __future__ import annotations
 
@@ -60,16 +61,17 @@ class EPState:
         self.group = group
         rows = world * capacity
         u8, f32, i32 = torch.uint8, torch.float32, torch.int32
-        # one spare row at the end of the send buffers takes the rows of pairs that overflow the capacity
-        self._xq_send = torch.zeros(rows + 1, hidden, dtype=u8, device=device)
-        self._xs_send = torch.zeros(rows + 1, hidden // 128, dtype=f32, device=device)
-        self.xq_send, self.xs_send = self._xq_send[:rows], self._xs_send[:rows]
+        self.xq_send = torch.zeros(rows, hidden, dtype=u8, device=device)
         self.xq_recv = torch.zeros(rows, hidden, dtype=u8, device=device)
+        self.xs_send = torch.zeros(rows, hidden // 128, dtype=f32, device=device)
         self.xs_recv = torch.zeros(rows, hidden // 128, dtype=f32, device=device)
+        self.id_send = torch.zeros(rows, dtype=i32, device=device)
         self.id_recv = torch.zeros(rows, dtype=i32, device=device)
+        self.xq_sorted = torch.zeros(rows, hidden, dtype=u8, device=device)
+        self.xs_sorted = torch.zeros(rows, hidden // 128, dtype=f32, device=device)
         self.y_send = torch.zeros(rows, hidden, dtype=torch.bfloat16, device=device)
         self.y_recv = torch.zeros(rows, hidden, dtype=torch.bfloat16, device=device)
-        self.overflow = torch.zeros((), dtype=torch.bool, device=device)
+        self.overflow = torch.zeros(1, dtype=i32, device=device)  # sticky: set when a destination's capacity ran out
 
 
 def ep_moe_forward(st: EPState, h, logits, w13, w13_scale, w2, w2_scale, renormalize, kernels, all_to_all,
@@ -78,36 +80,30 @@ def ep_moe_forward(st: EPState, h, logits, w13, w13_scale, w2, w2_scale, renorma
 
     `w13/w2` hold only this rank's experts.  `kernels` supplies the compute steps (the ``ops`` module on a
     GPU; a CPU stand-in in the gloo tests) and `all_to_all(out, inp)` the equal-split exchange.  Steps:
-    route -> sort by (global) expert + quantise -> place rows in fixed-capacity send slots -> all-to-all of
-    e4m3 rows, scales and local expert ids -> re-sort the received rows by local expert -> grouped GEMMs ->
-    un-sort -> all-to-all back -> weighted combine in the original (token, slot) order."""
+      1. route; sort by (global) expert id, quantise and place every row in its fixed-capacity send slot
+         (one kernel: the sort by expert is also a sort by owner rank);
+      2. all-to-all of e4m3 rows, scales and owner-local expert ids (empty slots carry the id E_local);
+      3. stable sort of the received slots by local expert (the dummy expert E_local sorts last and gets no
+         tiles), one gather into sorted order, grouped gate/up GEMM, down GEMM writing straight back into slot
+         order;
+      4. all-to-all back and weighted combine in the original (token, slot) order.
+    Everything has fixed shapes and no host round trip, so the layer can sit inside a captured CUDA graph."""
     T, K, W, C, El = st.T, st.K, st.W, st.C, st.e_local
     ids, wts = kernels.moe_route(logits, K, renormalize)
-    perm, xq, xs = kernels.moe_permute_quant(ids, h, st.E)
-    slot_of_pair, expert_of_slot, overflow = plan_dispatch(ids, perm.row_of_pair, perm.expert_offsets, st.E, W, C)
-    st.overflow |= overflow
-    slot_of_row = slot_of_pair[perm.sorted_pair_ids.long()]
-    # rows that overflowed (flagged above) land in the spare row; the rest go to their slots
-    dest = torch.where(slot_of_row >= 0, slot_of_row, torch.full_like(slot_of_row, W * C))
-    st._xq_send.index_copy_(0, dest, xq)
-    st._xs_send.index_copy_(0, dest, xs)
+    st.id_send.fill_(El)
+    _, slot_of_pair = kernels.moe_permute_quant_ep(ids, h, st.E, W, C, st.xq_send, st.xs_send, st.id_send, st.overflow)
     all_to_all(st.xq_recv, st.xq_send)
     all_to_all(st.xs_recv, st.xs_send)
-    all_to_all(st.id_recv, expert_of_slot.contiguous())
+    all_to_all(st.id_recv, st.id_send)
 
-    # local experts: stable sort of the received slots by local expert id; empty slots carry id El and sort last
-    lperm = kernels.moe_permute(st.id_recv.view(-1, 1), El + 1)
-    n_real = ((lperm.tiles[:, 0] < El) & (torch.arange(lperm.tiles.shape[0], device=h.device) < lperm.num_tiles)).sum()
-    lperm.num_tiles.copy_(n_real.to(torch.int32).view(1))
-    order = lperm.sorted_pair_ids.long()
-    xq_l = st.xq_recv.index_select(0, order)
-    xs_l = st.xs_recv.index_select(0, order)
-    hq, hs = kernels.moe_fp8_gemm_gate_up(xq_l, xs_l, w13, w13_scale, lperm)
-    y_l = kernels.moe_fp8_gemm_down(hq, hs, w2, w2_scale, lperm)
-    torch.index_select(y_l, 0, lperm.row_of_pair.long(), out=st.y_send)
+    lperm = kernels.moe_permute(st.id_recv.view(-1, 1), El + 1, El)
+    kernels.gather_rows_fp8(st.xq_recv, st.xs_recv, lperm.sorted_pair_ids, st.xq_sorted, st.xs_sorted)
+    hq, hs = kernels.moe_fp8_gemm_gate_up(st.xq_sorted, st.xs_sorted, w13, w13_scale, lperm)
+    kernels.moe_fp8_gemm_down(hq, hs, w2, w2_scale, lperm, out=st.y_send, out_row_map=lperm.sorted_pair_ids)
     all_to_all(st.y_recv, st.y_send)
 
-    rows = torch.where(slot_of_pair >= 0, slot_of_pair, torch.zeros_like(slot_of_pair)).to(torch.int32)
+    # pairs that overflowed (slot -1, flagged) contribute nothing
+    rows = torch.clamp(slot_of_pair, min=0)
     wts = torch.where((slot_of_pair >= 0).view(T, K), wts, torch.zeros_like(wts))
     if residual is not None:
         return kernels.moe_combine_add_rmsnorm(st.y_recv, rows, wts, residual, norm_weight, eps)

@@ -190,7 +190,9 @@ class Permutation:
     __slots__ = ("sorted_pair_ids", "row_of_pair", "expert_offsets", "tiles", "num_tiles", "workspace")
 
 
-def moe_permute(topk_ids: torch.Tensor, num_experts: int) -> Permutation:
+def moe_permute(topk_ids: torch.Tensor, num_experts: int, tile_experts: int = 0) -> Permutation:
+    """Stable sort of the (token, slot) pairs by expert id; only experts below `tile_experts` (0 = all) get
+    row tiles for the grouped GEMM."""
     _need(topk_ids, "topk_ids", torch.int32)
     T, K = topk_ids.shape
     lib = _lib.load()
@@ -204,7 +206,7 @@ def moe_permute(topk_ids: torch.Tensor, num_experts: int) -> Permutation:
     p.workspace = torch.zeros(lib.b200_moe_permute_workspace_bytes(T, num_experts, K), dtype=torch.uint8, device=dev)
     rc = lib.b200_moe_permute(
         _ptr(topk_ids), T, num_experts, K, _ptr(p.sorted_pair_ids), _ptr(p.row_of_pair),
-        _ptr(p.expert_offsets), _ptr(p.tiles), _ptr(p.num_tiles), _ptr(p.workspace),
+        _ptr(p.expert_offsets), _ptr(p.tiles), _ptr(p.num_tiles), int(tile_experts), _ptr(p.workspace),
         p.workspace.numel(), _stream(),
     )
     check(rc, "b200_moe_permute")
@@ -234,6 +236,55 @@ def moe_permute_quant(topk_ids: torch.Tensor, x: torch.Tensor, num_experts: int)
         p.workspace.numel(), _stream())
     check(rc, "b200_moe_permute_quant")
     return p, xq, xs
+
+
+def moe_permute_quant_ep(topk_ids, x, num_experts: int, ep_world: int, ep_capacity: int, xq_send, xs_send,
+                         expert_of_slot, overflow):
+    """Expert-parallel dispatch side: sort, quantise and place every row in its send slot.
+    `expert_of_slot` must be pre-filled with the empty id (num_experts // ep_world); `overflow` is an int32 flag.
+    Returns (Permutation, slot_of_pair int32 [T*K])."""
+    _need(topk_ids, "topk_ids", torch.int32)
+    _need(x, "x", torch.bfloat16)
+    _need(xq_send, "xq_send", torch.uint8)
+    _need(xs_send, "xs_send", torch.float32)
+    _need(expert_of_slot, "expert_of_slot", torch.int32)
+    _need(overflow, "overflow", torch.int32)
+    T, K = topk_ids.shape
+    H = x.shape[1]
+    if xq_send.shape[0] < ep_world * ep_capacity or expert_of_slot.numel() < ep_world * ep_capacity:
+        raise ValueError("send buffers are smaller than ep_world * ep_capacity rows")
+    lib = _lib.load()
+    dev = x.device
+    p = Permutation()
+    p.sorted_pair_ids = torch.empty(T * K, dtype=torch.int32, device=dev)
+    p.row_of_pair = torch.empty(T * K, dtype=torch.int32, device=dev)
+    p.expert_offsets = torch.empty(num_experts + 1, dtype=torch.int32, device=dev)
+    p.tiles = torch.empty(max(1, lib.b200_moe_max_tiles(T, num_experts, K)), 4, dtype=torch.int32, device=dev)
+    p.num_tiles = torch.empty(1, dtype=torch.int32, device=dev)
+    p.workspace = torch.zeros(lib.b200_moe_permute_workspace_bytes(T, num_experts, K), dtype=torch.uint8, device=dev)
+    slot_of_pair = torch.empty(T * K, dtype=torch.int32, device=dev)
+    rc = lib.b200_moe_permute_quant_ep(
+        _ptr(topk_ids), _ptr(x), T, num_experts, K, H, ep_world, ep_capacity, _ptr(p.sorted_pair_ids),
+        _ptr(p.row_of_pair), _ptr(p.expert_offsets), _ptr(p.tiles), _ptr(p.num_tiles), _ptr(xq_send), _ptr(xs_send),
+        _ptr(slot_of_pair), _ptr(expert_of_slot), _ptr(overflow), _ptr(p.workspace), p.workspace.numel(), _stream())
+    check(rc, "b200_moe_permute_quant_ep")
+    return p, slot_of_pair
+
+
+def gather_rows_fp8(src_q, src_scale, order, dst_q=None, dst_scale=None):
+    """dst row i = src row order[i] for e4m3 rows and their per-128 scales."""
+    _need(src_q, "src_q", torch.uint8)
+    _need(src_scale, "src_scale", torch.float32)
+    _need(order, "order", torch.int32)
+    n, H = order.numel(), src_q.shape[1]
+    if dst_q is None:
+        dst_q = torch.empty(n, H, dtype=torch.uint8, device=src_q.device)
+    if dst_scale is None:
+        dst_scale = torch.empty(n, H // 128, dtype=torch.float32, device=src_q.device)
+    rc = _lib.load().b200_gather_rows_fp8(_ptr(src_q), _ptr(src_scale), _ptr(order), n, H, _ptr(dst_q), _ptr(dst_scale),
+                                          _stream())
+    check(rc, "b200_gather_rows_fp8")
+    return dst_q, dst_scale
 
 
 def act_quant_fp8(x: torch.Tensor, row_of_pair: torch.Tensor | None = None, top_k: int = 1):
@@ -286,8 +337,9 @@ def moe_fp8_gemm_gate_up(xq, x_scale, w13, w13_scale_inv, perm: Permutation, sta
     return hq, hs
 
 
-def moe_fp8_gemm_down(hq, h_scale, w2, w2_scale_inv, perm: Permutation, status=None):
-    """y = W2 h per sorted row, bf16."""
+def moe_fp8_gemm_down(hq, h_scale, w2, w2_scale_inv, perm: Permutation, status=None, out=None, out_row_map=None):
+    """y = W2 h per sorted row, bf16.  With `out_row_map` (int32 per sorted row) row r is written to row
+    out_row_map[r] of `out` instead of row r."""
     hq, w2 = _as_u8(hq), _as_u8(w2)
     _need(hq, "hq", torch.uint8)
     _need(w2, "w2", torch.uint8)
@@ -297,10 +349,13 @@ def moe_fp8_gemm_down(hq, h_scale, w2, w2_scale_inv, perm: Permutation, status=N
     E, H, inter2, layout = _weight_dims(w2)
     if inter2 != inter or tuple(w2_scale_inv.shape) != (E, H // 128, inter // 128):
         raise ValueError("w2 / scale shapes do not match")
-    y = torch.empty(rows, H, dtype=torch.bfloat16, device=hq.device)
+    if out_row_map is not None:
+        _need(out_row_map, "out_row_map", torch.int32)
+    y = out if out is not None else torch.empty(rows, H, dtype=torch.bfloat16, device=hq.device)
+    _need(y, "out", torch.bfloat16)
     rc = _lib.load().b200_moe_fp8_gemm_down(
         _ptr(hq), _ptr(h_scale), _ptr(w2), _ptr(w2_scale_inv), _ptr(perm.tiles), _ptr(perm.num_tiles),
-        _ptr(y), _ptr(status), rows, E, H, inter, layout, _stream(),
+        _ptr(y), _ptr(out_row_map), _ptr(status), rows, E, H, inter, layout, _stream(),
     )
     check(rc, "b200_moe_fp8_gemm_down")
     return y

@@ -29,8 +29,35 @@ def _perm(ids, num_experts):
     return p
 
 
-def moe_permute(ids, num_experts):
-    return _perm(ids, num_experts)
+def moe_permute(ids, num_experts, tile_experts=0):
+    p = _perm(ids, num_experts)
+    if tile_experts:
+        n = int((p.tiles[: int(p.num_tiles), 0] < tile_experts).sum())
+        p.num_tiles = torch.tensor([n], dtype=torch.int32)
+    return p
+
+
+def moe_permute_quant_ep(ids, x, num_experts, ep_world, ep_capacity, xq_send, xs_send, expert_of_slot, overflow):
+    """Slot placement by the torch restatement in the package (ep.plan_dispatch), rows by the oracle quantiser."""
+    import importlib
+
+    ep = importlib.import_module("inference-server_b200.ep")
+    p, xq, xs = moe_permute_quant(ids, x, num_experts)
+    slot, eos, ovf = ep.plan_dispatch(ids, p.row_of_pair, p.expert_offsets, num_experts, ep_world, ep_capacity)
+    slot_of_row = slot[p.sorted_pair_ids.long()]
+    ok = slot_of_row >= 0
+    xq_send[slot_of_row[ok]] = xq[ok]
+    xs_send[slot_of_row[ok]] = xs[ok]
+    expert_of_slot.copy_(eos)
+    if bool(ovf):
+        overflow.fill_(1)
+    return p, slot.to(torch.int32)
+
+
+def gather_rows_fp8(src_q, src_s, order, dst_q, dst_s):
+    dst_q.copy_(src_q[order.long()])
+    dst_s.copy_(src_s[order.long()])
+    return dst_q, dst_s
 
 
 def moe_permute_quant(ids, x, num_experts):
@@ -59,11 +86,15 @@ def moe_fp8_gemm_gate_up(xq, xs, w13, w13_scale, perm, status=None):
     return hq, hs
 
 
-def moe_fp8_gemm_down(hq, hs, w2, w2_scale, perm, status=None):
-    y = torch.zeros(hq.shape[0], w2.shape[1], dtype=torch.bfloat16)
+def moe_fp8_gemm_down(hq, hs, w2, w2_scale, perm, status=None, out=None, out_row_map=None):
+    y = out if out is not None else torch.zeros(hq.shape[0], w2.shape[1], dtype=torch.bfloat16)
     for e, row0, rows in _rows_of_tiles(perm):
         a = moe_ref.dequant_act(hq[row0:row0 + rows].view(torch.float8_e4m3fn), hs[row0:row0 + rows])
-        y[row0:row0 + rows] = (a @ moe_ref.dequant_weight(w2[e].view(torch.float8_e4m3fn), w2_scale[e]).t()).bfloat16()
+        val = (a @ moe_ref.dequant_weight(w2[e].view(torch.float8_e4m3fn), w2_scale[e]).t()).bfloat16()
+        if out_row_map is None:
+            y[row0:row0 + rows] = val
+        else:
+            y[out_row_map[row0:row0 + rows].long()] = val
     return y
 
 

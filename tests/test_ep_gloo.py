@@ -41,7 +41,7 @@ def _worker(rank, world, port, capacity, results):
             w2s[lo:lo + el], True, cpu_kernels, lambda o, i: dist.all_to_all_single(o, i))
         ref = oracle.moe_fp8_ref(x, logits, w13q, w13s, w2q, w2s, K, True)
         err = float((out.float() - ref.float()).abs().max() / ref.float().abs().max())
-        results[rank] = (err, bool(st.overflow))
+        results[rank] = (err, bool(st.overflow.item()))
     finally:
         dist.destroy_process_group()
 

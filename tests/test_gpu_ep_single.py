@@ -25,7 +25,7 @@ def test_ep_layer_world_one_matches_fused_layer(ops, T, slack):
     st = ep.EPState(T, H, K, E, 1, T * K + slack, DEV)  # slack leaves empty slots that must sort last and be skipped
     out = ep.ep_moe_forward(st, x, logits, *dw, True, ops, lambda o, i: o.copy_(i))
     torch.cuda.synchronize()
-    assert not bool(st.overflow)
+    assert not bool(st.overflow.item())
     assert rel_err(out, ref) < 1e-2
     assert torch.equal(out, ref)  # same rows, same order inside every expert: same bits
     # fused tail: residual add + next norm
@@ -63,3 +63,32 @@ def test_ep_layer_can_be_captured_in_a_cuda_graph(ops):
     torch.cuda.synchronize()
     assert torch.equal(out, ops.moe_fp8_forward(x, logits, *dw, K, True))
     assert not torch.equal(out, ref)
+
+
+@pytest.mark.parametrize("T,W,cap", [(64, 4, 256), (256, 8, 512), (64, 2, 200), (33, 4, 40)])
+def test_dispatch_slot_kernel_matches_the_torch_plan(ops, T, W, cap):
+    """b200_moe_permute_quant_ep places rows exactly where ep.plan_dispatch (plain torch index arithmetic,
+    verified against the single-process layer by the gloo test) says, including the overflow case."""
+    ep = pkg("ep")
+    E, K, H = 128, 8, 2048
+    g = torch.Generator().manual_seed(T + W)
+    logits = torch.randn(T, E, generator=g)
+    x = torch.randn(T, H, generator=g).bfloat16()
+    ids, _ = oracle.route_ref(logits, K, True)
+    r = oracle.permute_ref(ids, E)
+    slot_ref, eos_ref, ovf_ref = ep.plan_dispatch(ids, torch.from_numpy(r["row_of_pair"]),
+                                                  torch.from_numpy(r["expert_offsets"]), E, W, cap)
+    xq_send = torch.zeros(W * cap, H, dtype=torch.uint8, device=DEV)
+    xs_send = torch.zeros(W * cap, H // 128, dtype=torch.float32, device=DEV)
+    eos = torch.full((W * cap,), E // W, dtype=torch.int32, device=DEV)
+    ovf = torch.zeros(1, dtype=torch.int32, device=DEV)
+    p, slot = ops.moe_permute_quant_ep(ids.to(DEV), x.to(DEV), E, W, cap, xq_send, xs_send, eos, ovf)
+    ops.read_status(p.workspace, "moe_permute_quant_ep")
+    assert torch.equal(slot.cpu().long(), slot_ref)
+    assert torch.equal(eos.cpu(), eos_ref)
+    assert bool(ovf.item()) == bool(ovf_ref)
+    rq, rs = oracle.act_quant_ref(x)
+    ok = slot_ref >= 0
+    tok = torch.arange(T * K) // K
+    assert torch.equal(xq_send.cpu()[slot_ref[ok]], rq.view(torch.uint8)[tok[ok]])
+    assert torch.equal(xs_send.cpu()[slot_ref[ok]], rs[tok[ok]])
