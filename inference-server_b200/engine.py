@@ -67,25 +67,11 @@ class LayerWeights:
     __slots__ = ("ln1", "wqkv", "q_norm", "k_norm", "wo", "ln2", "router", "w13", "w13_scale", "w2", "w2_scale")
 
 
-def rms_norm(x: torch.Tensor, weight: torch.Tensor, eps: float) -> torch.Tensor:
-    """weight * (x / rms(x)) with the statistics in fp32 (the model's RMSNorm)."""
-    xf = x.float()
-    xf = xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps)
-    return weight * xf.to(x.dtype)
-
-
 def rope_tables(head_dim: int, theta: float, max_pos: int, device, dtype):
     inv = 1.0 / (theta ** (torch.arange(0, head_dim, 2, dtype=torch.float32, device=device) / head_dim))
     ang = torch.arange(max_pos, dtype=torch.float32, device=device)[:, None] * inv[None, :]
     emb = torch.cat([ang, ang], dim=-1)
     return emb.cos().to(dtype), emb.sin().to(dtype)
-
-
-def apply_rope(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> torch.Tensor:
-    """x [..., heads, D]; cos/sin broadcastable [..., 1, D]; rotate-half convention."""
-    half = x.shape[-1] // 2
-    rot = torch.cat([-x[..., half:], x[..., :half]], dim=-1)
-    return x * cos + rot * sin
 
 
 def random_layer(cfg: ModelConfig, device, gen: torch.Generator, std: float = 0.02,
@@ -213,36 +199,43 @@ class DecodeEngine:
             self.kernel_launches_per_step += cfg.layers * 2  # the local re-sort of received rows (rank + scatter)
 
     # ------------------------------------------------------------------ step
-    def _step_eager(self, B: int) -> None:
-        """One decode step over rows [0, B) of the static buffers; advances ctx_lens by one.
+    def _forward(self, tokens, pos, table, attn_ws, moe_ws, split_tokens, ep: bool) -> torch.Tensor:
+        """The layer stack for R rows: row i is token `tokens[i]` at position `pos[i]` of the sequence whose
+        pages are `table[i]`; it attends to positions 0..pos[i].  Decode passes one row per sequence; a prompt
+        chunk passes one row per prompt token with the sequence's table repeated - the same kernels, reading
+        the pages in place either way.  Returns the final normed hidden states [R, hidden].
 
         Per layer: qkv GEMM, fused q/k norm + RoPE + page write, paged attention, o GEMM, fused
         residual+RMSNorm, router GEMM, FP8 MoE whose combine adds into the residual stream `x`
         (in place) and applies the next layer's input norm."""
         cfg = self.cfg
         D, Hq, Hkv = cfg.head_dim, cfg.q_heads, cfg.kv_heads
-        tokens = self.tokens[:B]
-        pos = self.ctx_lens[:B]
-        table = self.block_table[:B]
+        R = tokens.shape[0]
         new_len = pos + 1
         x = self.embed[tokens]
         h = ops.add_rmsnorm(x, None, self.layers[0].ln1, cfg.rms_eps)
         for li, w in enumerate(self.layers):
-            qkv = torch.matmul(h, w.wqkv.t()).view(B, Hq + 2 * Hkv, D)
+            qkv = torch.matmul(h, w.wqkv.t()).view(R, Hq + 2 * Hkv, D)
             q = ops.qk_norm_rope_append(qkv, w.q_norm, w.k_norm, self.cos, self.sin, pos, table, self.k_pools[li],
-                                        self.v_pools[li], Hq, cfg.rms_eps, self.attn_ws)
+                                        self.v_pools[li], Hq, cfg.rms_eps, attn_ws)
             attn = ops.paged_attn_decode(q, self.k_pools[li], self.v_pools[li], table, new_len, self.scale,
-                                         self.split_tokens, self.attn_ws)
-            o = torch.matmul(attn.view(B, Hq * D), w.wo.t())
+                                         split_tokens, attn_ws)
+            o = torch.matmul(attn.view(R, Hq * D), w.wo.t())
             h2 = ops.add_rmsnorm(x, o, w.ln2, cfg.rms_eps)
             logits = torch.matmul(h2, w.router.t())  # bf16, routed as is
             nxt = self.layers[li + 1].ln1 if li + 1 < len(self.layers) else self.final_norm
             # MoE layer; its combine also adds into the residual stream and applies the next norm
-            if self.ep_state is not None:
-                h = self._ep_moe(h2, logits, w, x, nxt, B)
+            if ep:
+                h = self._ep_moe(h2, logits, w, x, nxt, R)
             else:
                 h = ops.moe_fp8_forward(h2, logits, w.w13, w.w13_scale, w.w2, w.w2_scale, cfg.top_k,
-                                        cfg.norm_topk_prob, self.moe_ws, residual=x, norm_weight=nxt, eps=cfg.rms_eps)
+                                        cfg.norm_topk_prob, moe_ws, residual=x, norm_weight=nxt, eps=cfg.rms_eps)
+        return h
+
+    def _step_eager(self, B: int) -> None:
+        """One decode step over rows [0, B) of the static buffers; advances ctx_lens by one."""
+        h = self._forward(self.tokens[:B], self.ctx_lens[:B], self.block_table[:B], self.attn_ws, self.moe_ws,
+                          self.split_tokens, self.ep_state is not None)
         self.last_logits = torch.matmul(h, self.lm_head.t())
         self.next_tokens[:B] = self.last_logits.argmax(dim=-1)
         self.ctx_lens[:B] += 1
@@ -287,50 +280,49 @@ class DecodeEngine:
 
     # --------------------------------------------------------------- prefill
     @torch.no_grad()
-    def prefill(self, token_ids: list[int], block_ids: list[int], cached_tokens: int = 0) -> tuple[int, torch.Tensor]:
+    def prefill(self, token_ids: list[int], block_ids: list[int], cached_tokens: int = 0,
+                chunk: int = 256) -> tuple[int, torch.Tensor]:
         """Prompt pass for one sequence; writes K/V of tokens [cached_tokens, n) into `block_ids` pages.
 
-        Outside the per-step hot path: attention over the prompt is torch SDPA on
-        the gathered pages; the MoE layers run the same FP8 kernels as decode.
+        Runs the same paged kernels as decode, in chunks of `chunk` prompt tokens: every token of a chunk is a
+        row with its own position, all rows share the sequence's block table, and attention reads the pages in
+        place (cached prefix pages included) - there is no dense gather of the KV.  This replaces the
+        reference's page gather for cache hits (src/inference_server/kv_cache/hf_format.py:21-45).  The K/V
+        of a whole chunk are written to their page slots before the chunk's attention runs, and row i only
+        looks at positions <= its own, which is the causal mask.
+        Under expert parallelism the MoE layers of a prompt pass need the same exchange on every rank, so
+        prefill is available on single-GPU engines only.
         Returns (first generated token, last-position logits)."""
-        cfg = self.cfg
         n = len(token_ids)
         if n == 0 or cached_tokens >= n:
             raise ValueError("prefill needs at least one uncached token")
         if len(block_ids) * PAGE < n:
             raise ValueError("not enough pages for the prompt")
-        D, Hq, Hkv = cfg.head_dim, cfg.q_heads, cfg.kv_heads
-        new = n - cached_tokens
-        ids = torch.tensor(token_ids[cached_tokens:], device=self.device)
-        pos = torch.arange(cached_tokens, n, device=self.device)
-        bt = torch.tensor(block_ids, device=self.device, dtype=torch.long)
-        page_of = bt[pos // PAGE]
-        slot_of = pos % PAGE
-        x = self.embed[ids]
-        cos, sin = self.cos[pos].unsqueeze(1), self.sin[pos].unsqueeze(1)
-        n_pages = (n + PAGE - 1) // PAGE
-        for li, w in enumerate(self.layers):
-            h = rms_norm(x, w.ln1, cfg.rms_eps)
-            qkv = torch.matmul(h, w.wqkv.t()).view(new, Hq + 2 * Hkv, D)
-            q = apply_rope(rms_norm(qkv[:, :Hq], w.q_norm, cfg.rms_eps), cos, sin)
-            k = apply_rope(rms_norm(qkv[:, Hq:Hq + Hkv], w.k_norm, cfg.rms_eps), cos, sin)
-            v = qkv[:, Hq + Hkv:]
-            self.k_pools[li][page_of, :, slot_of, :] = k
-            self.v_pools[li][page_of, :, slot_of, :] = v
-            kd = self.k_pools[li][bt[:n_pages]].permute(1, 0, 2, 3).reshape(Hkv, n_pages * PAGE, D)[:, :n]
-            vd = self.v_pools[li][bt[:n_pages]].permute(1, 0, 2, 3).reshape(Hkv, n_pages * PAGE, D)[:, :n]
-            rep = Hq // Hkv
-            mask = pos[:, None] >= torch.arange(n, device=self.device)[None, :]
-            o = torch.nn.functional.scaled_dot_product_attention(
-                q.transpose(0, 1).unsqueeze(0), kd.repeat_interleave(rep, 0).unsqueeze(0),
-                vd.repeat_interleave(rep, 0).unsqueeze(0), attn_mask=mask, scale=self.scale)
-            x = x + torch.matmul(o[0].transpose(0, 1).reshape(new, Hq * D), w.wo.t())
-            h = rms_norm(x, w.ln2, cfg.rms_eps)
-            logits = torch.matmul(h, w.router.t()).float()
-            x = x + ops.moe_fp8_forward(h.contiguous(), logits, w.w13, w.w13_scale, w.w2, w.w2_scale, cfg.top_k,
-                                        cfg.norm_topk_prob)
-        x = rms_norm(x[-1:], self.final_norm, cfg.rms_eps)
-        logits = torch.matmul(x, self.lm_head.t())[0]
+        if len(block_ids) > self.max_pages:
+            raise ValueError("sequence needs more pages than the block table is wide")
+        if self.ep_state is not None:
+            raise NotImplementedError("prefill on an expert-parallel engine")
+        cfg = self.cfg
+        if getattr(self, "_prefill_chunk", 0) != chunk:
+            self._prefill_chunk = chunk
+            self._prefill_split = ops.default_split_tokens(chunk, cfg.kv_heads, self.max_pages * PAGE)
+            self._prefill_attn_ws = ops.paged_attn_workspace(chunk, cfg.q_heads, cfg.head_dim, self.max_pages, PAGE,
+                                                             self._prefill_split, self.device)
+            self._prefill_moe_ws = ops.moe_fp8_workspace(chunk, cfg.experts, cfg.top_k, cfg.hidden, cfg.moe_inter,
+                                                         self.device)
+        row = torch.zeros(self.max_pages, dtype=torch.int32)
+        row[: len(block_ids)] = torch.tensor(block_ids, dtype=torch.int32)
+        row = row.to(self.device)
+        h_last = None
+        for lo in range(cached_tokens, n, chunk):
+            hi = min(n, lo + chunk)
+            tokens = torch.tensor(token_ids[lo:hi], device=self.device)
+            pos = torch.arange(lo, hi, device=self.device, dtype=torch.int32)
+            table = row.unsqueeze(0).expand(hi - lo, -1).contiguous()
+            h = self._forward(tokens, pos, table, self._prefill_attn_ws, self._prefill_moe_ws, self._prefill_split,
+                              False)
+            h_last = h[-1:]
+        logits = torch.matmul(h_last, self.lm_head.t())[0]
         return int(logits.argmax()), logits
 
     # ------------------------------------------------------------- accounting
