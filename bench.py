@@ -110,9 +110,9 @@ class ClockSampler:
         return out
 
 
-def build_workload(cfg, batch: int, gen_tokens: int, seed: int):
+def build_workload(cfg, batch: int, gen_tokens: int, seed: int, ctx_min: int = 512, ctx_max: int = 4096):
     rng = np.random.default_rng(seed)
-    prompt_lens = rng.integers(512, 4097, size=batch).tolist()
+    prompt_lens = rng.integers(ctx_min, ctx_max + 1, size=batch).tolist()
     pages = [(L + gen_tokens + PAGE - 1) // PAGE for L in prompt_lens]
     max_pages = max(pages)
     total = sum(pages) + 64
@@ -142,6 +142,8 @@ def main():
     ap.add_argument("--model", default="qwen3-30b-a3b")
     ap.add_argument("--batch", type=int, default=256, help="concurrent sequences per GPU")
     ap.add_argument("--gen-tokens", type=int, default=256)
+    ap.add_argument("--ctx-min", type=int, default=512, help="shortest prompt (tokens)")
+    ap.add_argument("--ctx-max", type=int, default=4096, help="longest prompt (tokens)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--split-tokens", type=int, default=0, help="attention KV split size (0 = the library default)")
     ap.add_argument("--ep", action="store_true",
@@ -152,14 +154,16 @@ def main():
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     cfg = pkg("engine").CONFIGS[args.model]
-    prompt_lens, table, num_blocks, max_pages = build_workload(cfg, args.batch, args.gen_tokens, seed=rank)
-    config = {"workload": f"{args.model} continuous-batching decode, {args.batch} sequences/GPU, prompts U{{512..4096}}, "
-                          f"page {PAGE}, FP8 experts (BASELINE config 4)",
+    prompt_lens, table, num_blocks, max_pages = build_workload(cfg, args.batch, args.gen_tokens, seed=rank,
+                                                               ctx_min=args.ctx_min, ctx_max=args.ctx_max)
+    which = {"qwen3-30b-a3b": "BASELINE config 4", "qwen3-235b-a22b": "BASELINE config 5 shape"}.get(args.model, "parity shape")
+    config = {"workload": f"{args.model} continuous-batching decode, {args.batch} sequences/GPU, prompts "
+                          f"U{{{args.ctx_min}..{args.ctx_max}}}, page {PAGE}, FP8 experts ({which})",
               "batch_per_gpu": args.batch, "mean_ctx": float(np.mean(prompt_lens)),
               "parallelism": (f"dp{world} attention + ep{world} MoE (NCCL all-to-all)" if world > 1 and args.ep
                               else f"dp{world} (replicas: disjoint request batches, no data-path collective)"),
               "kv": "synthetic N(0,1) pages at the prompt lengths; prefill not timed",
-              "l2": "each step streams >90 GB of KV and weights, far larger than the 126 MB L2"}
+              "l2": "each step streams tens of GB of KV pages and expert weights, far more than the 126 MB L2"}
 
     if args.impl == "reference":
         if rank != 0:
