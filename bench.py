@@ -146,6 +146,8 @@ def main():
     ap.add_argument("--ctx-max", type=int, default=4096, help="longest prompt (tokens)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--split-tokens", type=int, default=0, help="attention KV split size (0 = the library default)")
+    ap.add_argument("--ep-transport", default="nccl", choices=["nccl", "p2p"],
+                    help="with --ep: NCCL all-to-all, or stores into the peers' mapped receive buffers")
     ap.add_argument("--ep", action="store_true",
                     help="N > 1: expert-parallel MoE (NCCL all-to-all dispatch/combine) instead of independent replicas")
     args = ap.parse_args()
@@ -160,7 +162,8 @@ def main():
     config = {"workload": f"{args.model} continuous-batching decode, {args.batch} sequences/GPU, prompts "
                           f"U{{{args.ctx_min}..{args.ctx_max}}}, page {PAGE}, FP8 experts ({which})",
               "batch_per_gpu": args.batch, "mean_ctx": float(np.mean(prompt_lens)),
-              "parallelism": (f"dp{world} attention + ep{world} MoE (NCCL all-to-all)" if world > 1 and args.ep
+              "parallelism": (f"dp{world} attention + ep{world} MoE ({'NCCL all-to-all' if args.ep_transport == 'nccl' else 'peer-memory stores + flag exchange'})"
+                               if world > 1 and args.ep
                               else f"dp{world} (replicas: disjoint request batches, no data-path collective)"),
               "kv": "synthetic N(0,1) pages at the prompt lengths; prefill not timed",
               "l2": "each step streams tens of GB of KV pages and expert weights, far more than the 126 MB L2"}
@@ -196,7 +199,8 @@ def main():
     t_setup = time.time()
     ep_group = torch.distributed.group.WORLD if world > 1 and args.ep else None
     engine = eng_mod.DecodeEngine(cfg, num_blocks=num_blocks, max_batch=args.batch, max_pages_per_seq=max_pages,
-                                  device=dev, seed=rank, ep_group=ep_group, split_tokens=args.split_tokens or None)
+                                  device=dev, seed=rank, ep_group=ep_group, split_tokens=args.split_tokens or None,
+                                  ep_transport=args.ep_transport)
     # KV image: one random pool, shared by all layers (contents do not affect timing)
     g = torch.Generator(device=dev).manual_seed(1000 + rank)
     engine.k_pools[0].normal_(generator=g)

@@ -219,8 +219,8 @@ int b200_moe_permute_quant(const int32_t* topk_ids, const void* x, int num_token
  * experts are owned by ep_world ranks in equal contiguous id ranges.  The quantised row of pair p goes to row
  * slot_of_pair[p] = owner * ep_capacity + (position among this rank's rows for that owner) of the send buffers
  * xq_send / x_scale_send [ep_world * ep_capacity rows], expert_of_slot gets the owner-local expert id of every
- * used slot (the caller pre-fills it with the "empty" id), pairs beyond the capacity get slot -1 and set
- * *overflow to 1.
+ * used slot and the "empty" id num_experts / ep_world of every unused one, pairs beyond the capacity get
+ * slot -1 and set *overflow to 1.
  */
 int b200_moe_permute_quant_ep(const int32_t* topk_ids, const void* x, int num_tokens, int num_experts,
                               int top_k, int hidden, int ep_world, int ep_capacity,
@@ -327,6 +327,71 @@ int b200_moe_fp8_forward_add_rmsnorm(const void* x, const void* router_logits, i
                                      void* workspace, size_t workspace_bytes, int num_tokens,
                                      int num_experts, int top_k, int hidden, int inter,
                                      int renormalize, int weight_layout, void* stream);
+
+/*
+ * ---------------------------------------------------------------------------
+ * Expert parallelism over peer memory.  None of this has a counterpart in the
+ * reference, which is single-device; it serves the multi-GPU partition of the
+ * MoE layer (experts owned by ep_world <= 8 ranks in equal contiguous id ranges).
+ *
+ * Every rank keeps its receive buffers in one device allocation that the other
+ * ranks of the node map (b200_ipc_*), so that the dispatch and the return path
+ * store rows straight into the owner's memory over NVLink:
+ *
+ *   xq_recv  [ep_world * ep_capacity, hidden] e4m3     row s * ep_capacity + i =
+ *   xs_recv  [ep_world * ep_capacity, hidden/128] f32  the i-th row rank s sent here
+ *   id_recv  [ep_world * ep_capacity] int32            its local expert id, or
+ *                                                      num_experts / ep_world if empty
+ *   y_recv   [ep_world * ep_capacity, hidden] bf16     row d * ep_capacity + i = the
+ *                                                      expert output of the i-th row this
+ *                                                      rank sent to rank d
+ *   flags    [8] int32 per exchange phase, zero before first use
+ *
+ * The *_peers arguments are host arrays of ep_world device pointers, entry r =
+ * that buffer of rank r as mapped in this process (entry ep_rank = this rank's own).
+ * ---------------------------------------------------------------------------
+ */
+
+/* b200_moe_permute_quant_ep with the rows, scales and expert ids written into the owners' xq_recv / xs_recv /
+ * id_recv (row ep_rank * ep_capacity + position) instead of local send buffers.  slot_of_pair as above. */
+int b200_moe_permute_quant_ep_p2p(const int32_t* topk_ids, const void* x, int num_tokens, int num_experts,
+                                  int top_k, int hidden, int ep_world, int ep_capacity, int ep_rank,
+                                  int32_t* sorted_pair_ids, int32_t* row_of_pair, int32_t* expert_offsets,
+                                  void* tiles, int32_t* num_tiles, void* const* xq_peers,
+                                  void* const* xs_peers, void* const* id_peers, int32_t* slot_of_pair,
+                                  int32_t* overflow, void* workspace, size_t workspace_bytes, void* stream);
+
+/* b200_moe_fp8_gemm_down whose epilogue returns every row to the rank it came from: with
+ * o = out_row_map[r] (the receive slot of sorted row r), the row is written to row
+ * ep_rank * ep_capacity + o % ep_capacity of y_recv of rank o / ep_capacity. */
+int b200_moe_fp8_gemm_down_p2p(const void* hq, const float* h_scale, const void* w2,
+                               const float* w2_scale_inv, const void* tiles, const int32_t* num_tiles,
+                               void* const* y_peers, const int32_t* out_row_map, void* status_word,
+                               int num_rows, int num_experts, int hidden, int inter, int weight_layout,
+                               int ep_world, int ep_capacity, int ep_rank, void* stream);
+
+/*
+ * Flag exchange that orders one rank's peer stores before another rank's reads.  epoch is a device int32
+ * owned by this rank (one per phase, zero before first use); flag_peers[r] is the flags array of that phase
+ * on rank r.  signal: epoch += 1 and flags[ep_rank] of every rank = epoch (after all earlier work of the
+ * stream).  wait: returns when every entry of this rank's flags has reached its epoch; the wait is bounded
+ * (about a second), after which the status word gets a peer-timeout code and the stream carries on.
+ * barrier = signal + wait in one launch.  All ranks must issue the same sequence of phases.
+ */
+int b200_ep_signal(void* const* flag_peers, int32_t* epoch, int ep_rank, int ep_world, void* stream);
+int b200_ep_wait(const int32_t* local_flags, const int32_t* epoch, int ep_world, void* status_word,
+                 void* stream);
+int b200_ep_barrier(void* const* flag_peers, int32_t* epoch, int ep_rank, int ep_world, void* status_word,
+                    void* stream);
+
+/*
+ * CUDA IPC for the buffers above.  export: the 64-byte handle of the allocation that contains ptr, and ptr's
+ * offset inside it.  import (in another process of the node, once per handle): maps the allocation with
+ * peer access and returns its base (for b200_ipc_close) and base + offset.
+ */
+int b200_ipc_export(const void* ptr, void* handle_out_64_bytes, uint64_t* offset_out);
+int b200_ipc_import(const void* handle_64_bytes, uint64_t offset, void** base_out, void** ptr_out);
+int b200_ipc_close(void* base);
 
 #ifdef __cplusplus
 }

@@ -48,6 +48,15 @@ SIGNATURES = {
     "b200_moe_fp8_forward": (c_int, [c_void_p, c_void_p, c_int] + [c_void_p] * 6 + [c_size_t] + [c_int] * 7 + [c_void_p]),
     "b200_moe_fp8_forward_add_rmsnorm": (
         c_int, [c_void_p, c_void_p, c_int] + [c_void_p] * 6 + [c_float] + [c_void_p] * 2 + [c_size_t] + [c_int] * 7 + [c_void_p]),
+    # expert parallelism over peer memory (no counterpart in the reference)
+    "b200_moe_permute_quant_ep_p2p": (c_int, [c_void_p, c_void_p] + [c_int] * 7 + [c_void_p] * 11 + [c_size_t, c_void_p]),
+    "b200_moe_fp8_gemm_down_p2p": (c_int, [c_void_p] * 9 + [c_int] * 8 + [c_void_p]),
+    "b200_ep_signal": (c_int, [c_void_p, c_void_p, c_int, c_int, c_void_p]),
+    "b200_ep_wait": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_void_p]),
+    "b200_ep_barrier": (c_int, [c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p]),
+    "b200_ipc_export": (c_int, [c_void_p, c_void_p, c_void_p]),
+    "b200_ipc_import": (c_int, [c_void_p, ctypes.c_uint64, c_void_p, c_void_p]),
+    "b200_ipc_close": (c_int, [c_void_p]),
 }
 
 _lib = None

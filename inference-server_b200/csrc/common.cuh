@@ -32,6 +32,18 @@ enum : int {
   kErrDevBadCtxLen = 17,    // ctx_len outside [0, max_pages * page]
   kErrDevWaitTimeout = 18,  // a bounded mbarrier wait ran out
   kErrDevBadExpert = 19,    // expert id outside [0, E)
+  kErrDevPeerTimeout = 20,  // a bounded wait for another rank's flag ran out
+};
+
+// Peer receive buffers of the expert-parallel dispatch, one entry per rank (this rank included); all null
+// when rows are exchanged by a library all-to-all instead.  Row (src_rank * capacity + pos) of rank d's
+// buffers holds the pos-th row that src_rank sends to d.
+constexpr int kMaxEpWorld = 8;
+struct EpPeers {
+  uint8_t* xq[kMaxEpWorld];
+  float* xs[kMaxEpWorld];
+  int* id[kMaxEpWorld];
+  int my_rank;
 };
 
 // Row tile consumed by the grouped GEMM: up to 128 consecutive sorted rows of

@@ -149,6 +149,7 @@ extern "C" const char* b200_strerror(int code) {
     case kErrDevBadCtxLen: return "device: context length or position outside the block table";
     case kErrDevWaitTimeout: return "device: a bounded barrier wait ran out";
     case kErrDevBadExpert: return "device: expert id outside [0, num_experts)";
+    case kErrDevPeerTimeout: return "device: a bounded wait for another rank's flag ran out";
     default: return "unknown error";
   }
 }

@@ -80,6 +80,12 @@ struct GemmParams {
   int inter;             // gate/up only
   int n_tiles;           // column tiles per row tile
   int tiled;             // weights stored as contiguous 128x128 blocks [E, n_rows/128, k_blocks, 128, 128]
+  // down, expert-parallel return path: output row o = r * peer_capacity + i (slot i received from rank r) is
+  // written to row my_rank * peer_capacity + i of rank r's buffer y_peers[r] instead of to y.  Off when
+  // peer_capacity is 0.
+  __nv_bfloat16* y_peers[kMaxEpWorld];
+  int peer_capacity;
+  int my_rank;
 };
 
 template <int MODE>
@@ -316,8 +322,14 @@ moe_fp8_gemm_kernel(const __grid_constant__ CUtensorMap a_map,
         }
       } else {
         if (row_ok) {
-          const size_t orow = p.out_row_map ? static_cast<size_t>(__ldg(p.out_row_map + grow)) : grow;
-          __nv_bfloat16* dst = p.y + orow * p.n_rows + j * kTileN + half * 128;
+          size_t orow = p.out_row_map ? static_cast<size_t>(__ldg(p.out_row_map + grow)) : grow;
+          __nv_bfloat16* ybase = p.y;
+          if (p.peer_capacity > 0) {
+            const int src = static_cast<int>(orow) / p.peer_capacity;
+            orow = static_cast<size_t>(p.my_rank) * p.peer_capacity + (orow - static_cast<size_t>(src) * p.peer_capacity);
+            ybase = p.y_peers[src];
+          }
+          __nv_bfloat16* dst = ybase + orow * p.n_rows + j * kTileN + half * 128;
 #pragma unroll
           for (int c = 0; c < 16; ++c) {
             uint4 o;
@@ -415,18 +427,17 @@ extern "C" int b200_moe_fp8_gemm_gate_up(const void* xq, const float* x_scale, c
   return launch_gemm<kModeGateUp>(a_map, b_map, p, as_stream(stream));
 }
 
-extern "C" int b200_moe_fp8_gemm_down(const void* hq, const float* h_scale, const void* w2,
-                                      const float* w2_scale_inv, const void* tiles,
-                                      const int32_t* num_tiles, void* y_sorted,
-                                      const int32_t* out_row_map, void* status_word,
-                                      int num_rows, int num_experts, int hidden, int inter,
-                                      int weight_layout, void* stream) {
-  B200_REQUIRE(hq && h_scale && w2 && w2_scale_inv && tiles && num_tiles && y_sorted,
+static int gemm_down_impl(const void* hq, const float* h_scale, const void* w2, const float* w2_scale_inv,
+                          const void* tiles, const int32_t* num_tiles, void* y_sorted,
+                          const int32_t* out_row_map, void* status_word, int num_rows, int num_experts,
+                          int hidden, int inter, int weight_layout, void* const* y_peers, int ep_world,
+                          int ep_capacity, int ep_rank, void* stream) {
+  B200_REQUIRE(hq && h_scale && w2 && w2_scale_inv && tiles && num_tiles && (y_sorted || y_peers),
                "moe_fp8_gemm_down: null pointer");
   B200_REQUIRE(num_rows >= 0 && num_experts > 0, "moe_fp8_gemm_down: bad row/expert count");
   B200_REQUIRE(hidden > 0 && hidden % 256 == 0 && inter > 0 && inter % 128 == 0,
                "moe_fp8_gemm_down: hidden %d must be a multiple of 256 and inter %d of 128", hidden, inter);
-  B200_REQUIRE(aligned16(hq) && aligned16(w2) && aligned16(y_sorted),
+  B200_REQUIRE(aligned16(hq) && aligned16(w2) && (y_sorted == nullptr || aligned16(y_sorted)),
                "moe_fp8_gemm_down: buffers must be 16-byte aligned");
   int rc = check_device(nullptr);
   if (rc) return rc;
@@ -454,5 +465,40 @@ extern "C" int b200_moe_fp8_gemm_down(const void* hq, const float* h_scale, cons
   p.inter = inter;
   p.n_tiles = hidden / kTileN;
   p.tiled = weight_layout;
+  if (y_peers != nullptr) {
+    B200_REQUIRE(ep_world >= 1 && ep_world <= kMaxEpWorld && ep_capacity > 0 && ep_rank >= 0 && ep_rank < ep_world &&
+                     out_row_map != nullptr,
+                 "moe_fp8_gemm_down_p2p: world %d (at most %d), capacity %d, rank %d, row map %p", ep_world,
+                 kMaxEpWorld, ep_capacity, ep_rank, static_cast<const void*>(out_row_map));
+    for (int r = 0; r < ep_world; ++r) {
+      B200_REQUIRE(y_peers[r] && aligned16(y_peers[r]), "moe_fp8_gemm_down_p2p: buffer of rank %d null or unaligned", r);
+      p.y_peers[r] = static_cast<__nv_bfloat16*>(y_peers[r]);
+    }
+    p.peer_capacity = ep_capacity;
+    p.my_rank = ep_rank;
+  }
   return launch_gemm<kModeDown>(a_map, b_map, p, as_stream(stream));
+}
+
+extern "C" int b200_moe_fp8_gemm_down(const void* hq, const float* h_scale, const void* w2,
+                                      const float* w2_scale_inv, const void* tiles,
+                                      const int32_t* num_tiles, void* y_sorted,
+                                      const int32_t* out_row_map, void* status_word,
+                                      int num_rows, int num_experts, int hidden, int inter,
+                                      int weight_layout, void* stream) {
+  B200_REQUIRE(y_sorted, "moe_fp8_gemm_down: null pointer");
+  return gemm_down_impl(hq, h_scale, w2, w2_scale_inv, tiles, num_tiles, y_sorted, out_row_map, status_word,
+                        num_rows, num_experts, hidden, inter, weight_layout, nullptr, 0, 0, 0, stream);
+}
+
+extern "C" int b200_moe_fp8_gemm_down_p2p(const void* hq, const float* h_scale, const void* w2,
+                                          const float* w2_scale_inv, const void* tiles,
+                                          const int32_t* num_tiles, void* const* y_peers,
+                                          const int32_t* out_row_map, void* status_word, int num_rows,
+                                          int num_experts, int hidden, int inter, int weight_layout,
+                                          int ep_world, int ep_capacity, int ep_rank, void* stream) {
+  B200_REQUIRE(y_peers, "moe_fp8_gemm_down_p2p: null pointer");
+  return gemm_down_impl(hq, h_scale, w2, w2_scale_inv, tiles, num_tiles, nullptr, out_row_map, status_word,
+                        num_rows, num_experts, hidden, inter, weight_layout, y_peers, ep_world, ep_capacity,
+                        ep_rank, stream);
 }

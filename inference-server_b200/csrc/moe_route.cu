@@ -248,8 +248,9 @@ __global__ void moe_scatter_quant_kernel(const __nv_bfloat16* __restrict__ x, co
                                          uint8_t* __restrict__ xq, float* __restrict__ xs,
                                          int* __restrict__ err, int ep_world, int ep_capacity,
                                          int* __restrict__ slot_of_pair, int* __restrict__ expert_of_slot,
-                                         int* __restrict__ overflow) {
+                                         int* __restrict__ overflow, const EpPeers peers) {
   extern __shared__ int sm[];  // cnt[E], off[E+1], ntile[E], toff[E+1], warp_tot[32], dst[K]
+  const bool p2p = peers.xq[0] != nullptr;
   int* cnt = sm;
   int* off = cnt + E;
   int* ntile = off + E + 1;
@@ -294,7 +295,8 @@ __global__ void moe_scatter_quant_kernel(const __nv_bfloat16* __restrict__ x, co
         const int pos = d - off[owner * e_local];
         if (pos < ep_capacity) {
           d = owner * ep_capacity + pos;
-          expert_of_slot[d] = e - owner * e_local;
+          if (p2p) peers.id[owner][peers.my_rank * ep_capacity + pos] = e - owner * e_local;
+          else expert_of_slot[d] = e - owner * e_local;
         } else {
           d = -1;
           *overflow = 1;
@@ -303,6 +305,17 @@ __global__ void moe_scatter_quant_kernel(const __nv_bfloat16* __restrict__ x, co
       }
     }
     dst[tid] = d;
+  }
+  if (slot_of_pair != nullptr) {
+    // slots past the rows a destination gets carry the dummy expert id E/W, which gets no tiles there
+    const int e_local = E / ep_world, total = ep_world * ep_capacity;
+    for (int i = t * blockDim.x + tid; i < total; i += gridDim.x * blockDim.x) {
+      const int owner = i / ep_capacity, pos = i - owner * ep_capacity;
+      if (pos >= off[(owner + 1) * e_local] - off[owner * e_local]) {
+        if (p2p) peers.id[owner][peers.my_rank * ep_capacity + pos] = e_local;
+        else expert_of_slot[i] = e_local;
+      }
+    }
   }
   __syncthreads();
 
@@ -328,10 +341,18 @@ __global__ void moe_scatter_quant_kernel(const __nv_bfloat16* __restrict__ x, co
   }
   const int groups = H / 128;
   for (int k = 0; k < K; ++k) {
-    const int row = dst[k];
+    int row = dst[k];
     if (row < 0) continue;
-    *reinterpret_cast<uint2*>(xq + static_cast<size_t>(row) * H + tid * 8) = make_uint2(lo, hi);
-    if ((tid & 15) == 0) xs[static_cast<size_t>(row) * groups + (tid >> 4)] = s;
+    uint8_t* q = xq;
+    float* sc = xs;
+    if (p2p) {  // straight into the owner's receive buffers over NVLink (or this GPU's own, for its experts)
+      const int owner = row / ep_capacity;
+      row = peers.my_rank * ep_capacity + (row - owner * ep_capacity);
+      q = peers.xq[owner];
+      sc = peers.xs[owner];
+    }
+    *reinterpret_cast<uint2*>(q + static_cast<size_t>(row) * H + tid * 8) = make_uint2(lo, hi);
+    if ((tid & 15) == 0) sc[static_cast<size_t>(row) * groups + (tid >> 4)] = s;
   }
 }
 
@@ -498,7 +519,7 @@ static int permute_quant_impl(const int32_t* topk_ids, const void* x, int num_to
                               int32_t* expert_offsets, void* tiles, int32_t* num_tiles, void* xq,
                               float* x_scale, void* workspace, size_t workspace_bytes, int ep_world,
                               int ep_capacity, int32_t* slot_of_pair, int32_t* expert_of_slot,
-                              int32_t* overflow, void* stream) {
+                              int32_t* overflow, const EpPeers& peers, void* stream) {
   B200_REQUIRE(topk_ids && x && sorted_pair_ids && row_of_pair && expert_offsets && tiles && num_tiles && xq &&
                    x_scale && workspace,
                "moe_permute_quant: null pointer");
@@ -527,7 +548,8 @@ static int permute_quant_impl(const int32_t* topk_ids, const void* x, int num_to
   moe_scatter_quant_kernel<<<num_tokens, hidden / 8, smem, st>>>(
       static_cast<const __nv_bfloat16*>(x), topk_ids, rank, counts, num_experts, top_k, hidden, 128,
       sorted_pair_ids, row_of_pair, expert_offsets, static_cast<MoeTile*>(tiles), num_tiles,
-      static_cast<uint8_t*>(xq), x_scale, err, ep_world, ep_capacity, slot_of_pair, expert_of_slot, overflow);
+      static_cast<uint8_t*>(xq), x_scale, err, ep_world, ep_capacity, slot_of_pair, expert_of_slot, overflow,
+      peers);
   B200_CUDA(cudaGetLastError());
   return 0;
 }
@@ -539,7 +561,7 @@ extern "C" int b200_moe_permute_quant(const int32_t* topk_ids, const void* x, in
                                       size_t workspace_bytes, void* stream) {
   return permute_quant_impl(topk_ids, x, num_tokens, num_experts, top_k, hidden, sorted_pair_ids, row_of_pair,
                             expert_offsets, tiles, num_tiles, xq, x_scale, workspace, workspace_bytes, 1, 0,
-                            nullptr, nullptr, nullptr, stream);
+                            nullptr, nullptr, nullptr, EpPeers{}, stream);
 }
 
 extern "C" int b200_moe_permute_quant_ep(const int32_t* topk_ids, const void* x, int num_tokens,
@@ -554,7 +576,34 @@ extern "C" int b200_moe_permute_quant_ep(const int32_t* topk_ids, const void* x,
   B200_REQUIRE(slot_of_pair && expert_of_slot && overflow, "moe_permute_quant_ep: null pointer");
   return permute_quant_impl(topk_ids, x, num_tokens, num_experts, top_k, hidden, sorted_pair_ids, row_of_pair,
                             expert_offsets, tiles, num_tiles, xq_send, x_scale_send, workspace, workspace_bytes,
-                            ep_world, ep_capacity, slot_of_pair, expert_of_slot, overflow, stream);
+                            ep_world, ep_capacity, slot_of_pair, expert_of_slot, overflow, EpPeers{}, stream);
+}
+
+extern "C" int b200_moe_permute_quant_ep_p2p(const int32_t* topk_ids, const void* x, int num_tokens,
+                                             int num_experts, int top_k, int hidden, int ep_world,
+                                             int ep_capacity, int ep_rank, int32_t* sorted_pair_ids,
+                                             int32_t* row_of_pair, int32_t* expert_offsets, void* tiles,
+                                             int32_t* num_tiles, void* const* xq_peers, void* const* xs_peers,
+                                             void* const* id_peers, int32_t* slot_of_pair, int32_t* overflow,
+                                             void* workspace, size_t workspace_bytes, void* stream) {
+  B200_REQUIRE(ep_world >= 1 && ep_world <= kMaxEpWorld && num_experts % ep_world == 0 && ep_capacity > 0 &&
+                   ep_rank >= 0 && ep_rank < ep_world,
+               "moe_permute_quant_ep_p2p: %d experts over %d ranks (at most %d), capacity %d, rank %d", num_experts,
+               ep_world, kMaxEpWorld, ep_capacity, ep_rank);
+  B200_REQUIRE(slot_of_pair && overflow && xq_peers && xs_peers && id_peers, "moe_permute_quant_ep_p2p: null pointer");
+  EpPeers peers{};
+  for (int r = 0; r < ep_world; ++r) {
+    B200_REQUIRE(xq_peers[r] && xs_peers[r] && id_peers[r], "moe_permute_quant_ep_p2p: null buffer of rank %d", r);
+    B200_REQUIRE((reinterpret_cast<uintptr_t>(xq_peers[r]) & 7) == 0,
+                 "moe_permute_quant_ep_p2p: xq of rank %d is not 8-byte aligned", r);
+    peers.xq[r] = static_cast<uint8_t*>(xq_peers[r]);
+    peers.xs[r] = static_cast<float*>(xs_peers[r]);
+    peers.id[r] = static_cast<int*>(id_peers[r]);
+  }
+  peers.my_rank = ep_rank;
+  return permute_quant_impl(topk_ids, x, num_tokens, num_experts, top_k, hidden, sorted_pair_ids, row_of_pair,
+                            expert_offsets, tiles, num_tiles, peers.xq[ep_rank], peers.xs[ep_rank], workspace,
+                            workspace_bytes, ep_world, ep_capacity, slot_of_pair, nullptr, overflow, peers, stream);
 }
 
 // Copies quantised rows and their scales into a new row order: dst row i = src row order[i].

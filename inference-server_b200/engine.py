@@ -142,7 +142,8 @@ class DecodeEngine:
                  device: str | torch.device = "cuda", seed: int = 0, layers: list[LayerWeights] | None = None,
                  embed: torch.Tensor | None = None, lm_head: torch.Tensor | None = None,
                  final_norm: torch.Tensor | None = None, k_pools=None, v_pools=None, use_graphs: bool = True,
-                 split_tokens: int | None = None, ep_group=None, ep_capacity: int | None = None):
+                 split_tokens: int | None = None, ep_group=None, ep_capacity: int | None = None,
+                 ep_transport: str = "nccl"):
         if not torch.cuda.is_available():
             raise RuntimeError("DecodeEngine needs a CUDA device; this path has no CPU implementation")
         self.cfg = cfg
@@ -190,13 +191,24 @@ class DecodeEngine:
         if self.ep_world > 1:
             from . import ep
             cap = ep_capacity or ep.default_capacity(max_batch, cfg.top_k, self.ep_world)
+            if ep_transport not in ("nccl", "p2p"):
+                raise ValueError(f"ep_transport must be 'nccl' or 'p2p', got {ep_transport!r}")
+            arena = None
+            if ep_transport == "p2p":
+                # receive buffers of every rank mapped into every process of the node (CUDA IPC): rows then
+                # move by stores from the dispatch kernel and the down-GEMM epilogue, not by a collective
+                arena = ep.PeerArena(cfg.hidden, self.ep_world, cap, self.device)
+                arena.connect(ops, ep_group)
+            self.ep_arena = arena
             self.ep_state = ep.EPState(max_batch, cfg.hidden, cfg.top_k, cfg.experts, self.ep_world, cap, self.device,
-                                       ep_group)
+                                       ep_group, arena=arena)
         # per layer: qk_norm_rope_append, attention + split reduce, add_rmsnorm, route, rank, scatter+quant, gemm x2,
         # combine+norm; + the first norm
         self.kernel_launches_per_step = cfg.layers * 10 + 1
         if self.ep_world > 1:
-            self.kernel_launches_per_step += cfg.layers * 2  # the local re-sort of received rows (rank + scatter)
+            # the local re-sort of received rows (rank + scatter + row gather), and with the peer-memory
+            # transport the two flag exchanges
+            self.kernel_launches_per_step += cfg.layers * (3 + (2 if ep_transport == "p2p" else 0))
 
     # ------------------------------------------------------------------ step
     def _forward(self, tokens, pos, table, attn_ws, moe_ws, split_tokens, ep: bool) -> torch.Tensor:
@@ -241,7 +253,8 @@ class DecodeEngine:
         self.ctx_lens[:B] += 1
 
     def _ep_moe(self, h2, logits, w: LayerWeights, x, next_norm, B: int) -> torch.Tensor:
-        """Expert-parallel MoE layer: NCCL all-to-all dispatch and combine around the local grouped GEMMs."""
+        """Expert-parallel MoE layer: dispatch and combine around the local grouped GEMMs, by NCCL all-to-all
+        or, with a peer arena, by stores into the other ranks' memory."""
         import torch.distributed as dist
 
         from . import ep

@@ -14,6 +14,13 @@ that no step needs a host round trip:
 On the GPU the slot placement is done inside the scatter+quantise kernel
 (``b200_moe_permute_quant_ep``); ``plan_dispatch`` is the same arithmetic in torch
 ops, used by the CPU stand-in kernels of the gloo tests and as a cross-check.
+
+Two transports move the rows.  "a2a": local send buffers and a library all-to-all
+(NCCL on GPUs, gloo in the CPU tests).  "p2p": every rank keeps its receive buffers in
+one allocation that the other ranks of the node map (``PeerArena``), the dispatch
+kernel and the down-GEMM epilogue store rows straight into the owner's memory over
+NVLink, and a flag exchange (``ep_barrier``) orders those stores before the reads - no
+library collective and no staging copy on the data path.
 """
 from __future__ import annotations
 
@@ -51,27 +58,107 @@ def plan_dispatch(topk_ids: torch.Tensor, row_of_pair: torch.Tensor, expert_offs
     return slot, expert_of_slot[:trash], overflow
 
 
+def _align(n: int, a: int = 256) -> int:
+    return (n + a - 1) // a * a
+
+
+class PeerArena:
+    """One device allocation per rank holding the receive side of the peer-memory exchange, with the same
+    layout on every rank, plus the addresses of the other ranks' arenas as mapped into this process.
+
+    Layout (each section 256-byte aligned): xq_recv [W*C, H] u8 | xs_recv [W*C, H/128] f32 | id_recv [W*C] i32 |
+    y_recv [W*C, H] bf16 | flags [2 phases][8] i32."""
+
+    def __init__(self, hidden: int, world: int, capacity: int, device):
+        rows = world * capacity
+        self.rows, self.hidden, self.world = rows, hidden, world
+        self.off_xq = 0
+        self.off_xs = _align(self.off_xq + rows * hidden)
+        self.off_id = _align(self.off_xs + rows * (hidden // 128) * 4)
+        self.off_y = _align(self.off_id + rows * 4)
+        self.off_flags = _align(self.off_y + rows * hidden * 2)
+        self.nbytes = self.off_flags + 256
+        self.buf = torch.zeros(self.nbytes, dtype=torch.uint8, device=device)
+        self.rank = 0
+        self.bases = [self.buf.data_ptr()]  # arena address of every rank, as seen from this process
+        self._opened: list[int] = []
+
+    def view(self, off: int, nbytes: int, dtype, shape):
+        return self.buf[off:off + nbytes].view(dtype).view(shape)
+
+    def connect(self, ops, group) -> None:
+        """Exchange CUDA IPC handles over `group` and map every other rank's arena (ranks of one node)."""
+        import torch.distributed as dist
+
+        world = dist.get_world_size(group)
+        if world != self.world:
+            raise ValueError(f"arena laid out for {self.world} ranks, group has {world}")
+        self.rank = dist.get_rank(group)
+        mine = ops.ipc_export(self.buf)
+        everyone = [None] * world
+        dist.all_gather_object(everyone, mine, group=group)
+        self.bases = []
+        for r, (handle, offset) in enumerate(everyone):
+            if r == self.rank:
+                self.bases.append(self.buf.data_ptr())
+            else:
+                base, ptr = ops.ipc_import(handle, offset)
+                self._opened.append(base)
+                self.bases.append(ptr)
+        dist.barrier(group=group)  # nobody proceeds (or frees) before every mapping exists
+
+    def connect_in_process(self, arenas: list["PeerArena"], rank: int) -> None:
+        """Several ranks emulated in one process (tests on one GPU): peers are plain device pointers."""
+        self.rank = rank
+        self.bases = [a.buf.data_ptr() for a in arenas]
+
+    def close(self, ops) -> None:
+        for base in self._opened:
+            ops.ipc_close(base)
+        self._opened = []
+
+
 class EPState:
-    """Per-rank buffers of the expert-parallel exchange, allocated once (graph-capturable)."""
+    """Per-rank buffers of the expert-parallel exchange, allocated once (graph-capturable).
+    With `arena` (a connected PeerArena) the exchange runs over peer memory, else over `all_to_all`."""
 
     def __init__(self, num_tokens: int, hidden: int, top_k: int, num_experts: int, world: int, capacity: int,
-                 device, group=None):
+                 device, group=None, arena: PeerArena | None = None):
         self.T, self.H, self.K, self.E, self.W, self.C = num_tokens, hidden, top_k, num_experts, world, capacity
         self.e_local = num_experts // world
         self.group = group
+        self.arena = arena
         rows = world * capacity
         u8, f32, i32 = torch.uint8, torch.float32, torch.int32
+        self.overflow = torch.zeros(1, dtype=i32, device=device)  # sticky: set when a destination's capacity ran out
+        self.xq_sorted = torch.zeros(rows, hidden, dtype=u8, device=device)
+        self.xs_sorted = torch.zeros(rows, hidden // 128, dtype=f32, device=device)
+        if arena is not None:
+            if arena.rows != rows or arena.hidden != hidden:
+                raise ValueError("arena was laid out for other sizes")
+            a = arena
+            self.rank = a.rank
+            self.xq_recv = a.view(a.off_xq, rows * hidden, u8, (rows, hidden))
+            self.xs_recv = a.view(a.off_xs, rows * (hidden // 128) * 4, f32, (rows, hidden // 128))
+            self.id_recv = a.view(a.off_id, rows * 4, i32, (rows,))
+            self.y_recv = a.view(a.off_y, rows * hidden * 2, torch.bfloat16, (rows, hidden))
+            self.flags = [a.view(a.off_flags + 32 * ph, 32, i32, (8,)) for ph in range(2)]
+            self.peer_xq = [b + a.off_xq for b in a.bases]
+            self.peer_xs = [b + a.off_xs for b in a.bases]
+            self.peer_id = [b + a.off_id for b in a.bases]
+            self.peer_y = [b + a.off_y for b in a.bases]
+            self.peer_flags = [[b + a.off_flags + 32 * ph for b in a.bases] for ph in range(2)]
+            self.epochs = torch.zeros(2, dtype=i32, device=device)  # local: exchanges done so far, per phase
+            self.status = torch.zeros(64, dtype=i32, device=device)
+            return
         self.xq_send = torch.zeros(rows, hidden, dtype=u8, device=device)
         self.xq_recv = torch.zeros(rows, hidden, dtype=u8, device=device)
         self.xs_send = torch.zeros(rows, hidden // 128, dtype=f32, device=device)
         self.xs_recv = torch.zeros(rows, hidden // 128, dtype=f32, device=device)
         self.id_send = torch.zeros(rows, dtype=i32, device=device)
         self.id_recv = torch.zeros(rows, dtype=i32, device=device)
-        self.xq_sorted = torch.zeros(rows, hidden, dtype=u8, device=device)
-        self.xs_sorted = torch.zeros(rows, hidden // 128, dtype=f32, device=device)
         self.y_send = torch.zeros(rows, hidden, dtype=torch.bfloat16, device=device)
         self.y_recv = torch.zeros(rows, hidden, dtype=torch.bfloat16, device=device)
-        self.overflow = torch.zeros(1, dtype=i32, device=device)  # sticky: set when a destination's capacity ran out
 
 
 def ep_moe_forward(st: EPState, h, logits, w13, w13_scale, w2, w2_scale, renormalize, kernels, all_to_all,
@@ -87,10 +174,17 @@ def ep_moe_forward(st: EPState, h, logits, w13, w13_scale, w2, w2_scale, renorma
          tiles), one gather into sorted order, grouped gate/up GEMM, down GEMM writing straight back into slot
          order;
       4. all-to-all back and weighted combine in the original (token, slot) order.
-    Everything has fixed shapes and no host round trip, so the layer can sit inside a captured CUDA graph."""
+    Everything has fixed shapes and no host round trip, so the layer can sit inside a captured CUDA graph.
+    With a peer arena (`st.arena`) steps 2 and 4 are stores into the other ranks' memory from inside the
+    dispatch kernel and the down GEMM, separated by flag exchanges; `all_to_all` is then unused."""
+    if st.arena is not None:
+        wts, slot_of_pair = p2p_dispatch(st, h, logits, renormalize, kernels)
+        kernels.ep_barrier(st.peer_flags[0], st.epochs[0:1], st.rank, st.W, st.status)
+        p2p_experts(st, w13, w13_scale, w2, w2_scale, kernels)
+        kernels.ep_barrier(st.peer_flags[1], st.epochs[1:2], st.rank, st.W, st.status)
+        return _combine(st, wts, slot_of_pair, kernels, residual, norm_weight, eps)
     T, K, W, C, El = st.T, st.K, st.W, st.C, st.e_local
     ids, wts = kernels.moe_route(logits, K, renormalize)
-    st.id_send.fill_(El)
     _, slot_of_pair = kernels.moe_permute_quant_ep(ids, h, st.E, W, C, st.xq_send, st.xs_send, st.id_send, st.overflow)
     all_to_all(st.xq_recv, st.xq_send)
     all_to_all(st.xs_recv, st.xs_send)
@@ -101,10 +195,40 @@ def ep_moe_forward(st: EPState, h, logits, w13, w13_scale, w2, w2_scale, renorma
     hq, hs = kernels.moe_fp8_gemm_gate_up(st.xq_sorted, st.xs_sorted, w13, w13_scale, lperm)
     kernels.moe_fp8_gemm_down(hq, hs, w2, w2_scale, lperm, out=st.y_send, out_row_map=lperm.sorted_pair_ids)
     all_to_all(st.y_recv, st.y_send)
+    return _combine(st, wts, slot_of_pair, kernels, residual, norm_weight, eps)
 
-    # pairs that overflowed (slot -1, flagged) contribute nothing
+
+def _combine(st: EPState, wts, slot_of_pair, kernels, residual, norm_weight, eps):
+    """Weighted sum of the returned expert rows in (token, slot) order; pairs that overflowed (slot -1,
+    flagged) contribute nothing."""
     rows = torch.clamp(slot_of_pair, min=0)
-    wts = torch.where((slot_of_pair >= 0).view(T, K), wts, torch.zeros_like(wts))
+    wts = torch.where((slot_of_pair >= 0).view(st.T, st.K), wts, torch.zeros_like(wts))
     if residual is not None:
         return kernels.moe_combine_add_rmsnorm(st.y_recv, rows, wts, residual, norm_weight, eps)
     return kernels.moe_combine(st.y_recv, rows, wts)
+
+
+# ------------------------------------------------------------ peer-memory transport --
+# The three stages of one layer.  Between them stands a flag exchange: ep_barrier in production (every rank
+# is its own process and GPU); the single-GPU tests emulate several ranks in one process and therefore run
+# stage by stage over all ranks with ep_signal / ep_wait apart (kernels that wait for each other must not
+# sit in one stream).
+
+def p2p_dispatch(st: EPState, h, logits, renormalize, kernels):
+    """Route, then sort + quantise + store every row, its scales and its expert id into the owner's
+    receive buffers (one kernel).  Returns (routing weights, slot_of_pair)."""
+    ids, wts = kernels.moe_route(logits, st.K, renormalize)
+    _, slot_of_pair = kernels.moe_permute_quant_ep_p2p(ids, h, st.E, st.W, st.C, st.rank, st.peer_xq, st.peer_xs,
+                                                       st.peer_id, st.overflow)
+    return wts, slot_of_pair
+
+
+def p2p_experts(st: EPState, w13, w13_scale, w2, w2_scale, kernels) -> None:
+    """Local experts on the received rows; the down GEMM's epilogue stores each result row into y_recv of the
+    rank the row came from."""
+    El = st.e_local
+    lperm = kernels.moe_permute(st.id_recv.view(-1, 1), El + 1, El)
+    kernels.gather_rows_fp8(st.xq_recv, st.xs_recv, lperm.sorted_pair_ids, st.xq_sorted, st.xs_sorted)
+    hq, hs = kernels.moe_fp8_gemm_gate_up(st.xq_sorted, st.xs_sorted, w13, w13_scale, lperm)
+    kernels.moe_fp8_gemm_down_p2p(hq, hs, w2, w2_scale, lperm, st.peer_y, lperm.sorted_pair_ids, st.W, st.C, st.rank,
+                                  st.status)

@@ -241,7 +241,8 @@ def moe_permute_quant(topk_ids: torch.Tensor, x: torch.Tensor, num_experts: int)
 def moe_permute_quant_ep(topk_ids, x, num_experts: int, ep_world: int, ep_capacity: int, xq_send, xs_send,
                          expert_of_slot, overflow):
     """Expert-parallel dispatch side: sort, quantise and place every row in its send slot.
-    `expert_of_slot` must be pre-filled with the empty id (num_experts // ep_world); `overflow` is an int32 flag.
+    `expert_of_slot` gets the owner-local expert id of every used slot and the empty id (num_experts //
+    ep_world) of every other; `overflow` is an int32 flag.
     Returns (Permutation, slot_of_pair int32 [T*K])."""
     _need(topk_ids, "topk_ids", torch.int32)
     _need(x, "x", torch.bfloat16)
@@ -269,6 +270,83 @@ def moe_permute_quant_ep(topk_ids, x, num_experts: int, ep_world: int, ep_capaci
         _ptr(slot_of_pair), _ptr(expert_of_slot), _ptr(overflow), _ptr(p.workspace), p.workspace.numel(), _stream())
     check(rc, "b200_moe_permute_quant_ep")
     return p, slot_of_pair
+
+
+def _ptr_array(ptrs):
+    """Host array of device pointers (ints) for the *_peers arguments."""
+    import ctypes
+    return (ctypes.c_void_p * len(ptrs))(*[int(p) for p in ptrs])
+
+
+def moe_permute_quant_ep_p2p(topk_ids, x, num_experts: int, ep_world: int, ep_capacity: int, ep_rank: int,
+                             xq_peers, xs_peers, id_peers, overflow):
+    """moe_permute_quant_ep writing rows, scales and ids straight into the owners' receive buffers.
+    `*_peers` are lists of ep_world device addresses (entry r = that buffer of rank r as mapped here).
+    Returns (Permutation, slot_of_pair int32 [T*K])."""
+    _need(topk_ids, "topk_ids", torch.int32)
+    _need(x, "x", torch.bfloat16)
+    _need(overflow, "overflow", torch.int32)
+    if not (len(xq_peers) == len(xs_peers) == len(id_peers) == ep_world):
+        raise ValueError("need one peer address per rank")
+    T, K = topk_ids.shape
+    H = x.shape[1]
+    lib = _lib.load()
+    dev = x.device
+    p = Permutation()
+    p.sorted_pair_ids = torch.empty(T * K, dtype=torch.int32, device=dev)
+    p.row_of_pair = torch.empty(T * K, dtype=torch.int32, device=dev)
+    p.expert_offsets = torch.empty(num_experts + 1, dtype=torch.int32, device=dev)
+    p.tiles = torch.empty(max(1, lib.b200_moe_max_tiles(T, num_experts, K)), 4, dtype=torch.int32, device=dev)
+    p.num_tiles = torch.empty(1, dtype=torch.int32, device=dev)
+    p.workspace = torch.zeros(lib.b200_moe_permute_workspace_bytes(T, num_experts, K), dtype=torch.uint8, device=dev)
+    slot_of_pair = torch.empty(T * K, dtype=torch.int32, device=dev)
+    rc = lib.b200_moe_permute_quant_ep_p2p(
+        _ptr(topk_ids), _ptr(x), T, num_experts, K, H, ep_world, ep_capacity, ep_rank, _ptr(p.sorted_pair_ids),
+        _ptr(p.row_of_pair), _ptr(p.expert_offsets), _ptr(p.tiles), _ptr(p.num_tiles), _ptr_array(xq_peers),
+        _ptr_array(xs_peers), _ptr_array(id_peers), _ptr(slot_of_pair), _ptr(overflow), _ptr(p.workspace),
+        p.workspace.numel(), _stream())
+    check(rc, "b200_moe_permute_quant_ep_p2p")
+    return p, slot_of_pair
+
+
+def ep_signal(flag_peers, epoch: torch.Tensor, ep_rank: int, ep_world: int):
+    _need(epoch, "epoch", torch.int32)
+    check(_lib.load().b200_ep_signal(_ptr_array(flag_peers), _ptr(epoch), ep_rank, ep_world, _stream()), "b200_ep_signal")
+
+
+def ep_wait(local_flags: torch.Tensor, epoch: torch.Tensor, ep_world: int, status: torch.Tensor | None = None):
+    _need(local_flags, "local_flags", torch.int32)
+    _need(epoch, "epoch", torch.int32)
+    check(_lib.load().b200_ep_wait(_ptr(local_flags), _ptr(epoch), ep_world, _ptr(status), _stream()), "b200_ep_wait")
+
+
+def ep_barrier(flag_peers, epoch: torch.Tensor, ep_rank: int, ep_world: int, status: torch.Tensor | None = None):
+    _need(epoch, "epoch", torch.int32)
+    check(_lib.load().b200_ep_barrier(_ptr_array(flag_peers), _ptr(epoch), ep_rank, ep_world, _ptr(status), _stream()),
+          "b200_ep_barrier")
+
+
+def ipc_export(t: torch.Tensor):
+    """(64-byte handle, offset) that another process of the node can map with ipc_import."""
+    import ctypes
+    _need(t, "tensor")
+    handle = ctypes.create_string_buffer(64)
+    off = ctypes.c_uint64(0)
+    check(_lib.load().b200_ipc_export(_ptr(t), handle, ctypes.byref(off)), "b200_ipc_export")
+    return bytes(handle.raw), int(off.value)
+
+
+def ipc_import(handle: bytes, offset: int):
+    """Maps an exported allocation; returns (base address for ipc_close, address of the exported tensor)."""
+    import ctypes
+    base, ptr = ctypes.c_void_p(0), ctypes.c_void_p(0)
+    buf = ctypes.create_string_buffer(handle, 64)
+    check(_lib.load().b200_ipc_import(buf, offset, ctypes.byref(base), ctypes.byref(ptr)), "b200_ipc_import")
+    return int(base.value), int(ptr.value)
+
+
+def ipc_close(base: int):
+    check(_lib.load().b200_ipc_close(base), "b200_ipc_close")
 
 
 def gather_rows_fp8(src_q, src_scale, order, dst_q=None, dst_scale=None):
@@ -359,6 +437,29 @@ def moe_fp8_gemm_down(hq, h_scale, w2, w2_scale_inv, perm: Permutation, status=N
     )
     check(rc, "b200_moe_fp8_gemm_down")
     return y
+
+
+def moe_fp8_gemm_down_p2p(hq, h_scale, w2, w2_scale_inv, perm: Permutation, y_peers, out_row_map, ep_world: int,
+                          ep_capacity: int, ep_rank: int, status=None):
+    """Down GEMM whose epilogue writes every row into y_recv of the rank the row came from (`y_peers`:
+    ep_world device addresses); `out_row_map` gives the receive slot of each sorted row."""
+    hq, w2 = _as_u8(hq), _as_u8(w2)
+    _need(hq, "hq", torch.uint8)
+    _need(w2, "w2", torch.uint8)
+    _need(h_scale, "h_scale", torch.float32)
+    _need(w2_scale_inv, "w2_scale_inv", torch.float32)
+    _need(out_row_map, "out_row_map", torch.int32)
+    rows, inter = hq.shape
+    E, H, inter2, layout = _weight_dims(w2)
+    if inter2 != inter or tuple(w2_scale_inv.shape) != (E, H // 128, inter // 128):
+        raise ValueError("w2 / scale shapes do not match")
+    if len(y_peers) != ep_world:
+        raise ValueError("need one peer address per rank")
+    rc = _lib.load().b200_moe_fp8_gemm_down_p2p(
+        _ptr(hq), _ptr(h_scale), _ptr(w2), _ptr(w2_scale_inv), _ptr(perm.tiles), _ptr(perm.num_tiles),
+        _ptr_array(y_peers), _ptr(out_row_map), _ptr(status), rows, E, H, inter, layout, ep_world, ep_capacity,
+        ep_rank, _stream())
+    check(rc, "b200_moe_fp8_gemm_down_p2p")
 
 
 def moe_combine(y_sorted, row_of_pair, topk_weights):

@@ -80,7 +80,7 @@ def test_dispatch_slot_kernel_matches_the_torch_plan(ops, T, W, cap):
                                                   torch.from_numpy(r["expert_offsets"]), E, W, cap)
     xq_send = torch.zeros(W * cap, H, dtype=torch.uint8, device=DEV)
     xs_send = torch.zeros(W * cap, H // 128, dtype=torch.float32, device=DEV)
-    eos = torch.full((W * cap,), E // W, dtype=torch.int32, device=DEV)
+    eos = torch.full((W * cap,), -7, dtype=torch.int32, device=DEV)  # the kernel fills used AND empty slots
     ovf = torch.zeros(1, dtype=torch.int32, device=DEV)
     p, slot = ops.moe_permute_quant_ep(ids.to(DEV), x.to(DEV), E, W, cap, xq_send, xs_send, eos, ovf)
     ops.read_status(p.workspace, "moe_permute_quant_ep")
