@@ -286,7 +286,8 @@ int b200_moe_fp8_gemm_down(const void* hq, const float* h_scale, const void* w2,
 /*
  * Replaces: the routing-weight multiply and per-token sum over the top_k expert
  * outputs.  out[t] = sum_k topk_weights[t,k] * y_sorted[row_of_pair[t,k]] in
- * fp32, k ascending, rounded to bf16.
+ * fp32, k ascending, rounded to bf16.  A negative row_of_pair entry (a pair
+ * the expert-parallel dispatch had to drop) contributes nothing.
  */
 int b200_moe_combine(const void* y_sorted, const int32_t* row_of_pair, const float* topk_weights,
                      int num_tokens, int hidden, int top_k, void* out, void* stream);
@@ -369,6 +370,16 @@ int b200_moe_fp8_gemm_down_p2p(const void* hq, const float* h_scale, const void*
                                void* const* y_peers, const int32_t* out_row_map, void* status_word,
                                int num_rows, int num_experts, int hidden, int inter, int weight_layout,
                                int ep_world, int ep_capacity, int ep_rank, void* stream);
+
+/* Receive side of the exchange in one call: b200_moe_permute over the received expert ids (one per row, experts
+ * [tile_experts, num_experts) are ranked but get no tiles and no copy - the dummy expert of empty slots) fused
+ * with b200_gather_rows_fp8 of the rows into that order.  num_experts <= 256.  Workspace:
+ * b200_moe_permute_workspace_bytes(num_rows, num_experts, 1). */
+int b200_moe_permute_gather_fp8(const int32_t* ids, int num_rows, int num_experts, int tile_experts,
+                                const void* src_q, const float* src_scale, int hidden, int32_t* sorted_ids,
+                                int32_t* row_of_id, int32_t* expert_offsets, void* tiles, int32_t* num_tiles,
+                                void* dst_q, float* dst_scale, void* workspace, size_t workspace_bytes,
+                                void* stream);
 
 /*
  * Flag exchange that orders one rank's peer stores before another rank's reads.  epoch is a device int32

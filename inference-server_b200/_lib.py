@@ -51,6 +51,8 @@ SIGNATURES = {
     # expert parallelism over peer memory (no counterpart in the reference)
     "b200_moe_permute_quant_ep_p2p": (c_int, [c_void_p, c_void_p] + [c_int] * 7 + [c_void_p] * 11 + [c_size_t, c_void_p]),
     "b200_moe_fp8_gemm_down_p2p": (c_int, [c_void_p] * 9 + [c_int] * 8 + [c_void_p]),
+    "b200_moe_permute_gather_fp8": (c_int, [c_void_p] + [c_int] * 3 + [c_void_p, c_void_p, c_int] + [c_void_p] * 8
+                                    + [c_size_t, c_void_p]),
     "b200_ep_signal": (c_int, [c_void_p, c_void_p, c_int, c_int, c_void_p]),
     "b200_ep_wait": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_void_p]),
     "b200_ep_barrier": (c_int, [c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p]),

@@ -169,6 +169,66 @@ moe_scatter_kernel(const int* __restrict__ topk_ids, const int* __restrict__ ran
   }
 }
 
+// moe_scatter_kernel fused with the row copy that follows it on the receive side of the expert-parallel
+// exchange: one CTA per received slot computes the slot's sorted position and copies its e4m3 row and scales
+// there.  Slots of experts >= tile_experts (the dummy expert that collects empty slots) are ranked, not copied.
+__global__ void __launch_bounds__(256)
+moe_scatter_rows_kernel(const int* __restrict__ ids, const int* __restrict__ rank,
+                        const int* __restrict__ counts, int E, int tile_experts, int H, int tile_rows,
+                        int* __restrict__ sorted_pair, int* __restrict__ row_of_pair,
+                        int* __restrict__ expert_offsets, MoeTile* __restrict__ tiles,
+                        int* __restrict__ num_tiles, const uint8_t* __restrict__ src_q,
+                        const float* __restrict__ src_s, uint8_t* __restrict__ dst_q,
+                        float* __restrict__ dst_s, int* __restrict__ err) {
+  extern __shared__ int sm[];  // counts[E], offsets[E + 1]
+  int* cnt = sm;
+  int* off = sm + E;
+  const int tid = threadIdx.x, nthr = blockDim.x;
+  for (int e = tid; e < E; e += nthr) cnt[e] = counts[e];
+  __syncthreads();
+  for (int e = tid; e <= E; e += nthr) {
+    int s = 0;
+    for (int j = 0; j < e; ++j) s += cnt[j];
+    off[e] = s;
+  }
+  __syncthreads();
+  if (blockIdx.x == 0) {
+    for (int e = tid; e <= E; e += nthr) expert_offsets[e] = off[e];
+    for (int e = tid; e < tile_experts; e += nthr) {
+      int tp = 0;
+      for (int j = 0; j < e; ++j) tp += (cnt[j] + tile_rows - 1) / tile_rows;
+      const int nt = (cnt[e] + tile_rows - 1) / tile_rows;
+      for (int j = 0; j < nt; ++j) {
+        MoeTile t;
+        t.expert = e;
+        t.row0 = off[e] + j * tile_rows;
+        t.rows = min(tile_rows, cnt[e] - j * tile_rows);
+        t.pad = 0;
+        tiles[tp + j] = t;
+      }
+      if (e == tile_experts - 1) *num_tiles = tp + nt;
+    }
+  }
+  const int i = blockIdx.x;
+  const int e = ids[i];
+  if (e < 0 || e >= E) {
+    if (tid == 0) set_error(err, kErrDevBadExpert);
+    return;
+  }
+  const int dst = off[e] + rank[i];
+  if (tid == 0) {
+    sorted_pair[dst] = i;
+    row_of_pair[i] = dst;
+  }
+  if (e >= tile_experts) return;
+  const uint4* s4 = reinterpret_cast<const uint4*>(src_q + static_cast<size_t>(i) * H);
+  uint4* d4 = reinterpret_cast<uint4*>(dst_q + static_cast<size_t>(dst) * H);
+  for (int c = tid; c < H / 16; c += nthr) d4[c] = s4[c];
+  const int groups = H / 128;
+  for (int gidx = tid; gidx < groups; gidx += nthr)
+    dst_s[static_cast<size_t>(dst) * groups + gidx] = src_s[static_cast<size_t>(i) * groups + gidx];
+}
+
 // ------------------------------------------------------ activation quant ----
 // One CTA per token, 8 columns per thread.  When row_of_pair is given the
 // quantised row is written to each of the token's K sorted rows; otherwise to
@@ -365,6 +425,7 @@ __global__ void moe_combine_kernel(const __nv_bfloat16* __restrict__ y,
   float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
   for (int k = 0; k < K; ++k) {
     const int row = row_of_pair[static_cast<size_t>(t) * K + k];
+    if (row < 0) continue;  // a pair without a result row (dropped by the expert-parallel capacity) adds nothing
     const float w = topk_w[static_cast<size_t>(t) * K + k];
     const uint4 raw = *reinterpret_cast<const uint4*>(y + static_cast<size_t>(row) * H + tid * 8);
     const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
@@ -395,6 +456,7 @@ __global__ void moe_combine_add_rmsnorm_kernel(const __nv_bfloat16* __restrict__
   float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
   for (int k = 0; k < K; ++k) {
     const int row = row_of_pair[static_cast<size_t>(t) * K + k];
+    if (row < 0) continue;  // a pair without a result row (dropped by the expert-parallel capacity) adds nothing
     const float w = topk_w[static_cast<size_t>(t) * K + k];
     const uint4 raw = *reinterpret_cast<const uint4*>(y + static_cast<size_t>(row) * H + tid * 8);
     const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
@@ -688,6 +750,46 @@ extern "C" int b200_moe_combine(const void* y_sorted, const int32_t* row_of_pair
   moe_combine_kernel<<<num_tokens, hidden / 8, 0, as_stream(stream)>>>(
       static_cast<const __nv_bfloat16*>(y_sorted), row_of_pair, topk_weights, hidden, top_k,
       static_cast<__nv_bfloat16*>(out));
+  B200_CUDA(cudaGetLastError());
+  return 0;
+}
+
+extern "C" int b200_moe_permute_gather_fp8(const int32_t* ids, int num_rows, int num_experts, int tile_experts,
+                                           const void* src_q, const float* src_scale, int hidden,
+                                           int32_t* sorted_ids, int32_t* row_of_id, int32_t* expert_offsets,
+                                           void* tiles, int32_t* num_tiles, void* dst_q, float* dst_scale,
+                                           void* workspace, size_t workspace_bytes, void* stream) {
+  B200_REQUIRE(ids && src_q && src_scale && sorted_ids && row_of_id && expert_offsets && tiles && num_tiles &&
+                   dst_q && dst_scale && workspace,
+               "moe_permute_gather_fp8: null pointer");
+  B200_REQUIRE(num_rows >= 0 && num_experts > 0 && num_experts <= 256 && tile_experts > 0 &&
+                   tile_experts <= num_experts,
+               "moe_permute_gather_fp8: rows %d, experts %d (at most 256), tile_experts %d", num_rows, num_experts,
+               tile_experts);
+  B200_REQUIRE(hidden > 0 && hidden % 128 == 0, "moe_permute_gather_fp8: hidden %d must be a multiple of 128", hidden);
+  B200_REQUIRE((reinterpret_cast<uintptr_t>(src_q) & 15) == 0 && (reinterpret_cast<uintptr_t>(dst_q) & 15) == 0,
+               "moe_permute_gather_fp8: row buffers must be 16-byte aligned");
+  const size_t need = b200_moe_permute_workspace_bytes(num_rows, num_experts, 1);
+  if (workspace_bytes < need) {
+    set_detail("moe_permute_gather_fp8: workspace %zu < required %zu", workspace_bytes, need);
+    return -kErrWorkspace;
+  }
+  int rc = check_device(nullptr);
+  if (rc) return rc;
+  if (num_rows == 0) return 0;
+  cudaStream_t st = as_stream(stream);
+  uint8_t* p = static_cast<uint8_t*>(workspace);
+  int* err = reinterpret_cast<int*>(p);
+  int* counts = reinterpret_cast<int*>(p + 256);
+  int* rank = reinterpret_cast<int*>(p + 256 + ((static_cast<size_t>(num_experts) * 4 + 255) & ~size_t(255)));
+  moe_rank_kernel<<<num_experts, kRankThreads, 0, st>>>(ids, num_rows, rank, counts);
+  B200_CUDA(cudaGetLastError());
+  const int threads = hidden / 16 < 256 ? (hidden / 16 < 32 ? 32 : hidden / 16) : 256;
+  const size_t smem = (2 * static_cast<size_t>(num_experts) + 1) * sizeof(int);
+  moe_scatter_rows_kernel<<<num_rows, threads, smem, st>>>(
+      ids, rank, counts, num_experts, tile_experts, hidden, 128, sorted_ids, row_of_id, expert_offsets,
+      static_cast<MoeTile*>(tiles), num_tiles, static_cast<const uint8_t*>(src_q), src_scale,
+      static_cast<uint8_t*>(dst_q), dst_scale, err);
   B200_CUDA(cudaGetLastError());
   return 0;
 }

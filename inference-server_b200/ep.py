@@ -131,6 +131,14 @@ class EPState:
         rows = world * capacity
         u8, f32, i32 = torch.uint8, torch.float32, torch.int32
         self.overflow = torch.zeros(1, dtype=i32, device=device)  # sticky: set when a destination's capacity ran out
+        # permutation buffers, allocated once when the kernels are the real ones (a hot path must not allocate
+        # or clear anything per layer); None lets a stand-in allocate per call
+        self.perm_send = self.perm_local = self.slot_of_pair = None
+        if torch.device(device).type == "cuda":
+            from . import ops
+            self.perm_send = ops.new_permutation(num_tokens, top_k, num_experts, device)
+            self.perm_local = ops.new_permutation(rows, 1, self.e_local + 1, device)
+            self.slot_of_pair = torch.empty(num_tokens * top_k, dtype=i32, device=device)
         self.xq_sorted = torch.zeros(rows, hidden, dtype=u8, device=device)
         self.xs_sorted = torch.zeros(rows, hidden // 128, dtype=f32, device=device)
         if arena is not None:
@@ -170,9 +178,9 @@ def ep_moe_forward(st: EPState, h, logits, w13, w13_scale, w2, w2_scale, renorma
       1. route; sort by (global) expert id, quantise and place every row in its fixed-capacity send slot
          (one kernel: the sort by expert is also a sort by owner rank);
       2. all-to-all of e4m3 rows, scales and owner-local expert ids (empty slots carry the id E_local);
-      3. stable sort of the received slots by local expert (the dummy expert E_local sorts last and gets no
-         tiles), one gather into sorted order, grouped gate/up GEMM, down GEMM writing straight back into slot
-         order;
+      3. stable sort of the received slots by local expert fused with the row copy into that order (the dummy
+         expert E_local sorts last, gets no tiles and is not copied), grouped gate/up GEMM, down GEMM writing
+         straight back into slot order;
       4. all-to-all back and weighted combine in the original (token, slot) order.
     Everything has fixed shapes and no host round trip, so the layer can sit inside a captured CUDA graph.
     With a peer arena (`st.arena`) steps 2 and 4 are stores into the other ranks' memory from inside the
@@ -185,13 +193,14 @@ def ep_moe_forward(st: EPState, h, logits, w13, w13_scale, w2, w2_scale, renorma
         return _combine(st, wts, slot_of_pair, kernels, residual, norm_weight, eps)
     T, K, W, C, El = st.T, st.K, st.W, st.C, st.e_local
     ids, wts = kernels.moe_route(logits, K, renormalize)
-    _, slot_of_pair = kernels.moe_permute_quant_ep(ids, h, st.E, W, C, st.xq_send, st.xs_send, st.id_send, st.overflow)
+    _, slot_of_pair = kernels.moe_permute_quant_ep(ids, h, st.E, W, C, st.xq_send, st.xs_send, st.id_send, st.overflow,
+                                                   perm=st.perm_send, slot_of_pair=st.slot_of_pair)
     all_to_all(st.xq_recv, st.xq_send)
     all_to_all(st.xs_recv, st.xs_send)
     all_to_all(st.id_recv, st.id_send)
 
-    lperm = kernels.moe_permute(st.id_recv.view(-1, 1), El + 1, El)
-    kernels.gather_rows_fp8(st.xq_recv, st.xs_recv, lperm.sorted_pair_ids, st.xq_sorted, st.xs_sorted)
+    lperm = kernels.moe_permute_gather_fp8(st.id_recv, El + 1, El, st.xq_recv, st.xs_recv, st.xq_sorted, st.xs_sorted,
+                                           perm=st.perm_local)
     hq, hs = kernels.moe_fp8_gemm_gate_up(st.xq_sorted, st.xs_sorted, w13, w13_scale, lperm)
     kernels.moe_fp8_gemm_down(hq, hs, w2, w2_scale, lperm, out=st.y_send, out_row_map=lperm.sorted_pair_ids)
     all_to_all(st.y_recv, st.y_send)
@@ -200,12 +209,10 @@ def ep_moe_forward(st: EPState, h, logits, w13, w13_scale, w2, w2_scale, renorma
 
 def _combine(st: EPState, wts, slot_of_pair, kernels, residual, norm_weight, eps):
     """Weighted sum of the returned expert rows in (token, slot) order; pairs that overflowed (slot -1,
-    flagged) contribute nothing."""
-    rows = torch.clamp(slot_of_pair, min=0)
-    wts = torch.where((slot_of_pair >= 0).view(st.T, st.K), wts, torch.zeros_like(wts))
+    flagged) contribute nothing (the combine kernels skip negative rows)."""
     if residual is not None:
-        return kernels.moe_combine_add_rmsnorm(st.y_recv, rows, wts, residual, norm_weight, eps)
-    return kernels.moe_combine(st.y_recv, rows, wts)
+        return kernels.moe_combine_add_rmsnorm(st.y_recv, slot_of_pair, wts, residual, norm_weight, eps)
+    return kernels.moe_combine(st.y_recv, slot_of_pair, wts)
 
 
 # ------------------------------------------------------------ peer-memory transport --
@@ -219,7 +226,8 @@ def p2p_dispatch(st: EPState, h, logits, renormalize, kernels):
     receive buffers (one kernel).  Returns (routing weights, slot_of_pair)."""
     ids, wts = kernels.moe_route(logits, st.K, renormalize)
     _, slot_of_pair = kernels.moe_permute_quant_ep_p2p(ids, h, st.E, st.W, st.C, st.rank, st.peer_xq, st.peer_xs,
-                                                       st.peer_id, st.overflow)
+                                                       st.peer_id, st.overflow, perm=st.perm_send,
+                                                       slot_of_pair=st.slot_of_pair)
     return wts, slot_of_pair
 
 
@@ -227,8 +235,8 @@ def p2p_experts(st: EPState, w13, w13_scale, w2, w2_scale, kernels) -> None:
     """Local experts on the received rows; the down GEMM's epilogue stores each result row into y_recv of the
     rank the row came from."""
     El = st.e_local
-    lperm = kernels.moe_permute(st.id_recv.view(-1, 1), El + 1, El)
-    kernels.gather_rows_fp8(st.xq_recv, st.xs_recv, lperm.sorted_pair_ids, st.xq_sorted, st.xs_sorted)
+    lperm = kernels.moe_permute_gather_fp8(st.id_recv, El + 1, El, st.xq_recv, st.xs_recv, st.xq_sorted, st.xs_sorted,
+                                           perm=st.perm_local)
     hq, hs = kernels.moe_fp8_gemm_gate_up(st.xq_sorted, st.xs_sorted, w13, w13_scale, lperm)
     kernels.moe_fp8_gemm_down_p2p(hq, hs, w2, w2_scale, lperm, st.peer_y, lperm.sorted_pair_ids, st.W, st.C, st.rank,
                                   st.status)

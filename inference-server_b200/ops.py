@@ -190,20 +190,29 @@ class Permutation:
     __slots__ = ("sorted_pair_ids", "row_of_pair", "expert_offsets", "tiles", "num_tiles", "workspace")
 
 
-def moe_permute(topk_ids: torch.Tensor, num_experts: int, tile_experts: int = 0) -> Permutation:
+def new_permutation(num_tokens: int, top_k: int, num_experts: int, device) -> Permutation:
+    """Buffers of one permutation.  Callers on a hot path allocate them once and pass them as `perm=`; the
+    workspace starts zeroed (its first word is the sticky device status)."""
+    lib = _lib.load()
+    n = num_tokens * top_k
+    p = Permutation()
+    p.sorted_pair_ids = torch.empty(n, dtype=torch.int32, device=device)
+    p.row_of_pair = torch.empty(n, dtype=torch.int32, device=device)
+    p.expert_offsets = torch.empty(num_experts + 1, dtype=torch.int32, device=device)
+    p.tiles = torch.zeros(max(1, lib.b200_moe_max_tiles(num_tokens, num_experts, top_k)), 4, dtype=torch.int32, device=device)
+    p.num_tiles = torch.zeros(1, dtype=torch.int32, device=device)
+    p.workspace = torch.zeros(lib.b200_moe_permute_workspace_bytes(num_tokens, num_experts, top_k), dtype=torch.uint8,
+                              device=device)
+    return p
+
+
+def moe_permute(topk_ids: torch.Tensor, num_experts: int, tile_experts: int = 0, perm: Permutation | None = None) -> Permutation:
     """Stable sort of the (token, slot) pairs by expert id; only experts below `tile_experts` (0 = all) get
     row tiles for the grouped GEMM."""
     _need(topk_ids, "topk_ids", torch.int32)
     T, K = topk_ids.shape
     lib = _lib.load()
-    dev = topk_ids.device
-    p = Permutation()
-    p.sorted_pair_ids = torch.empty(T * K, dtype=torch.int32, device=dev)
-    p.row_of_pair = torch.empty(T * K, dtype=torch.int32, device=dev)
-    p.expert_offsets = torch.empty(num_experts + 1, dtype=torch.int32, device=dev)
-    p.tiles = torch.zeros(max(1, lib.b200_moe_max_tiles(T, num_experts, K)), 4, dtype=torch.int32, device=dev)
-    p.num_tiles = torch.zeros(1, dtype=torch.int32, device=dev)
-    p.workspace = torch.zeros(lib.b200_moe_permute_workspace_bytes(T, num_experts, K), dtype=torch.uint8, device=dev)
+    p = perm if perm is not None else new_permutation(T, K, num_experts, topk_ids.device)
     rc = lib.b200_moe_permute(
         _ptr(topk_ids), T, num_experts, K, _ptr(p.sorted_pair_ids), _ptr(p.row_of_pair),
         _ptr(p.expert_offsets), _ptr(p.tiles), _ptr(p.num_tiles), int(tile_experts), _ptr(p.workspace),
@@ -239,7 +248,7 @@ def moe_permute_quant(topk_ids: torch.Tensor, x: torch.Tensor, num_experts: int)
 
 
 def moe_permute_quant_ep(topk_ids, x, num_experts: int, ep_world: int, ep_capacity: int, xq_send, xs_send,
-                         expert_of_slot, overflow):
+                         expert_of_slot, overflow, perm: Permutation | None = None, slot_of_pair=None):
     """Expert-parallel dispatch side: sort, quantise and place every row in its send slot.
     `expert_of_slot` gets the owner-local expert id of every used slot and the empty id (num_experts //
     ep_world) of every other; `overflow` is an int32 flag.
@@ -256,14 +265,9 @@ def moe_permute_quant_ep(topk_ids, x, num_experts: int, ep_world: int, ep_capaci
         raise ValueError("send buffers are smaller than ep_world * ep_capacity rows")
     lib = _lib.load()
     dev = x.device
-    p = Permutation()
-    p.sorted_pair_ids = torch.empty(T * K, dtype=torch.int32, device=dev)
-    p.row_of_pair = torch.empty(T * K, dtype=torch.int32, device=dev)
-    p.expert_offsets = torch.empty(num_experts + 1, dtype=torch.int32, device=dev)
-    p.tiles = torch.empty(max(1, lib.b200_moe_max_tiles(T, num_experts, K)), 4, dtype=torch.int32, device=dev)
-    p.num_tiles = torch.empty(1, dtype=torch.int32, device=dev)
-    p.workspace = torch.zeros(lib.b200_moe_permute_workspace_bytes(T, num_experts, K), dtype=torch.uint8, device=dev)
-    slot_of_pair = torch.empty(T * K, dtype=torch.int32, device=dev)
+    p = perm if perm is not None else new_permutation(T, K, num_experts, dev)
+    if slot_of_pair is None:
+        slot_of_pair = torch.empty(T * K, dtype=torch.int32, device=dev)
     rc = lib.b200_moe_permute_quant_ep(
         _ptr(topk_ids), _ptr(x), T, num_experts, K, H, ep_world, ep_capacity, _ptr(p.sorted_pair_ids),
         _ptr(p.row_of_pair), _ptr(p.expert_offsets), _ptr(p.tiles), _ptr(p.num_tiles), _ptr(xq_send), _ptr(xs_send),
@@ -279,7 +283,8 @@ def _ptr_array(ptrs):
 
 
 def moe_permute_quant_ep_p2p(topk_ids, x, num_experts: int, ep_world: int, ep_capacity: int, ep_rank: int,
-                             xq_peers, xs_peers, id_peers, overflow):
+                             xq_peers, xs_peers, id_peers, overflow, perm: Permutation | None = None,
+                             slot_of_pair=None):
     """moe_permute_quant_ep writing rows, scales and ids straight into the owners' receive buffers.
     `*_peers` are lists of ep_world device addresses (entry r = that buffer of rank r as mapped here).
     Returns (Permutation, slot_of_pair int32 [T*K])."""
@@ -292,14 +297,9 @@ def moe_permute_quant_ep_p2p(topk_ids, x, num_experts: int, ep_world: int, ep_ca
     H = x.shape[1]
     lib = _lib.load()
     dev = x.device
-    p = Permutation()
-    p.sorted_pair_ids = torch.empty(T * K, dtype=torch.int32, device=dev)
-    p.row_of_pair = torch.empty(T * K, dtype=torch.int32, device=dev)
-    p.expert_offsets = torch.empty(num_experts + 1, dtype=torch.int32, device=dev)
-    p.tiles = torch.empty(max(1, lib.b200_moe_max_tiles(T, num_experts, K)), 4, dtype=torch.int32, device=dev)
-    p.num_tiles = torch.empty(1, dtype=torch.int32, device=dev)
-    p.workspace = torch.zeros(lib.b200_moe_permute_workspace_bytes(T, num_experts, K), dtype=torch.uint8, device=dev)
-    slot_of_pair = torch.empty(T * K, dtype=torch.int32, device=dev)
+    p = perm if perm is not None else new_permutation(T, K, num_experts, dev)
+    if slot_of_pair is None:
+        slot_of_pair = torch.empty(T * K, dtype=torch.int32, device=dev)
     rc = lib.b200_moe_permute_quant_ep_p2p(
         _ptr(topk_ids), _ptr(x), T, num_experts, K, H, ep_world, ep_capacity, ep_rank, _ptr(p.sorted_pair_ids),
         _ptr(p.row_of_pair), _ptr(p.expert_offsets), _ptr(p.tiles), _ptr(p.num_tiles), _ptr_array(xq_peers),
@@ -347,6 +347,25 @@ def ipc_import(handle: bytes, offset: int):
 
 def ipc_close(base: int):
     check(_lib.load().b200_ipc_close(base), "b200_ipc_close")
+
+
+def moe_permute_gather_fp8(ids, num_experts: int, tile_experts: int, src_q, src_scale, dst_q, dst_scale,
+                           perm: Permutation | None = None) -> Permutation:
+    """Receive side of the expert-parallel exchange: sort the received rows by their (local) expert id and
+    copy them into that order, in one pass.  Experts >= tile_experts are ranked but neither tiled nor copied."""
+    _need(ids, "ids", torch.int32)
+    _need(src_q, "src_q", torch.uint8)
+    _need(src_scale, "src_scale", torch.float32)
+    _need(dst_q, "dst_q", torch.uint8)
+    _need(dst_scale, "dst_scale", torch.float32)
+    n, H = ids.numel(), src_q.shape[1]
+    p = perm if perm is not None else new_permutation(n, 1, num_experts, ids.device)
+    rc = _lib.load().b200_moe_permute_gather_fp8(
+        _ptr(ids), n, num_experts, tile_experts, _ptr(src_q), _ptr(src_scale), H, _ptr(p.sorted_pair_ids),
+        _ptr(p.row_of_pair), _ptr(p.expert_offsets), _ptr(p.tiles), _ptr(p.num_tiles), _ptr(dst_q), _ptr(dst_scale),
+        _ptr(p.workspace), p.workspace.numel(), _stream())
+    check(rc, "b200_moe_permute_gather_fp8")
+    return p
 
 
 def gather_rows_fp8(src_q, src_scale, order, dst_q=None, dst_scale=None):

@@ -29,7 +29,7 @@ def _perm(ids, num_experts):
     return p
 
 
-def moe_permute(ids, num_experts, tile_experts=0):
+def moe_permute(ids, num_experts, tile_experts=0, perm=None):
     p = _perm(ids, num_experts)
     if tile_experts:
         n = int((p.tiles[: int(p.num_tiles), 0] < tile_experts).sum())
@@ -37,7 +37,8 @@ def moe_permute(ids, num_experts, tile_experts=0):
     return p
 
 
-def moe_permute_quant_ep(ids, x, num_experts, ep_world, ep_capacity, xq_send, xs_send, expert_of_slot, overflow):
+def moe_permute_quant_ep(ids, x, num_experts, ep_world, ep_capacity, xq_send, xs_send, expert_of_slot, overflow,
+                         perm=None, slot_of_pair=None):
     """Slot placement by the torch restatement in the package (ep.plan_dispatch), rows by the oracle quantiser."""
     import importlib
 
@@ -52,6 +53,17 @@ def moe_permute_quant_ep(ids, x, num_experts, ep_world, ep_capacity, xq_send, xs
     if bool(ovf):
         overflow.fill_(1)
     return p, slot.to(torch.int32)
+
+
+def moe_permute_gather_fp8(ids, num_experts, tile_experts, src_q, src_s, dst_q, dst_s, perm=None):
+    """Sort the received rows by local expert and copy them into that order (rows of experts >= tile_experts,
+    the dummy expert of empty slots, are ranked but not copied)."""
+    p = moe_permute(ids.view(-1, 1), num_experts, tile_experts)
+    order = p.sorted_pair_ids.long()
+    real = ids.view(-1)[order] < tile_experts
+    dst_q[real] = src_q[order[real]]
+    dst_s[real] = src_s[order[real]]
+    return p
 
 
 def gather_rows_fp8(src_q, src_s, order, dst_q, dst_s):
@@ -103,5 +115,6 @@ def moe_combine(y, row_of_pair, w):
     rop = row_of_pair.long().view(T, K)
     out = torch.zeros(T, y.shape[1])
     for k in range(K):
-        out = out + w[:, k:k + 1] * y[rop[:, k]].float()
+        ok = (rop[:, k] >= 0).view(T, 1)  # a negative row (dropped pair) adds nothing
+        out = out + torch.where(ok, w[:, k:k + 1] * y[rop[:, k].clamp(min=0)].float(), torch.zeros(1))
     return out.bfloat16()

@@ -4,7 +4,7 @@ rows into "peer" receive buffers, flag exchanges order the stages.
 Several ranks are emulated in one process: every rank has its own tokens, arena and expert slice, the peers'
 arenas are plain device pointers, and the layer runs stage by stage over all ranks with ep_signal / ep_wait
 apart (kernels that wait for each other must not be queued behind one another).  What this cannot cover -
-CUDA IPC mapping and visibility across GPUs - is exercised by the multi-GPU bench (`bench.py --ep`).
+CUDA IPC mapping and visibility across GPUs - is covered by tests/test_gpu_ep_multi.py on a box with two GPUs.
 """
 import pytest
 import torch
@@ -94,3 +94,45 @@ def test_a_wait_nobody_answers_runs_out_and_reports(ops):
     assert after.sum().item() == 8
     with pytest.raises(Exception, match="rank's flag"):
         ops.read_status(status, "ep_wait")
+
+
+@pytest.mark.parametrize("n,El,H_", [(4096, 16, 2048), (512, 32, 2048), (300, 4, 512)])
+def test_fused_receive_side_sort_and_copy(ops, n, El, H_):
+    """b200_moe_permute_gather_fp8 = b200_moe_permute (with the dummy expert El for empty slots) followed by
+    b200_gather_rows_fp8, except that rows of the dummy expert are not copied."""
+    g = torch.Generator().manual_seed(n)
+    ids = torch.randint(0, El + 1, (n,), generator=g, dtype=torch.int32).to(DEV)
+    src_q = torch.randint(0, 256, (n, H_), generator=g, dtype=torch.uint8).to(DEV)
+    src_s = torch.rand(n, H_ // 128, generator=g).to(DEV)
+    ref = ops.moe_permute(ids.view(-1, 1), El + 1, El)
+    rq, rs = ops.gather_rows_fp8(src_q, src_s, ref.sorted_pair_ids)
+    dq = torch.full((n, H_), 0xAB, dtype=torch.uint8, device=DEV)
+    ds = torch.full((n, H_ // 128), -1.0, device=DEV)
+    p = ops.moe_permute_gather_fp8(ids, El + 1, El, src_q, src_s, dq, ds)
+    torch.cuda.synchronize()
+    ops.read_status(p.workspace, "moe_permute_gather_fp8")
+    assert torch.equal(p.sorted_pair_ids, ref.sorted_pair_ids) and torch.equal(p.row_of_pair, ref.row_of_pair)
+    assert torch.equal(p.expert_offsets, ref.expert_offsets) and int(p.num_tiles) == int(ref.num_tiles)
+    nt = int(ref.num_tiles)
+    assert torch.equal(p.tiles[:nt], ref.tiles[:nt])
+    real = int(ref.expert_offsets[El])  # rows of real experts come first
+    assert torch.equal(dq[:real], rq[:real]) and torch.equal(ds[:real], rs[:real])
+    assert bool((dq[real:] == 0xAB).all()) and bool((ds[real:] == -1.0).all())
+
+
+def test_combine_skips_negative_rows(ops):
+    T, K_, H_ = 16, 4, 512
+    g = torch.Generator().manual_seed(3)
+    y = torch.randn(T * K_, H_, generator=g).bfloat16().to(DEV)
+    w = torch.rand(T, K_, generator=g).to(DEV)
+    rows = torch.randperm(T * K_, generator=g).to(torch.int32).to(DEV)
+    drop = torch.rand(T * K_, generator=g).to(DEV) < 0.3
+    ref = ops.moe_combine(y, rows, torch.where(drop.view(T, K_), torch.zeros_like(w), w))
+    out = ops.moe_combine(y, torch.where(drop, torch.full_like(rows, -1), rows), w)
+    assert torch.equal(out, ref)
+    x1 = torch.randn(T, H_, generator=g).bfloat16().to(DEV)
+    x2 = x1.clone()
+    nw = torch.rand(H_, generator=g).bfloat16().to(DEV)
+    h1 = ops.moe_combine_add_rmsnorm(y, rows, torch.where(drop.view(T, K_), torch.zeros_like(w), w), x1, nw, 1e-6)
+    h2 = ops.moe_combine_add_rmsnorm(y, torch.where(drop, torch.full_like(rows, -1), rows), w, x2, nw, 1e-6)
+    assert torch.equal(h1, h2) and torch.equal(x1, x2)
