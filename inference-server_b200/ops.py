@@ -47,8 +47,12 @@ def default_split_tokens(batch: int, num_kv_heads: int, max_ctx: int, num_sms: i
     split at least 128 tokens so the pipeline fill is amortised, at most 1024 so
     ragged lengths still balance."""
     if batch <= 96:
-        # few sequences: the per-CTA fixed cost dominates, long splits win (measured at 64 rows)
-        return int(min(1024, max(128, ((max_ctx + 63) // 64) * 64)))
+        # few sequences: the per-CTA fixed cost dominates, so splits are as long as still fills the GPU -
+        # about 1.75 CTAs per SM over the batch's expected tokens (1 024 at 64 rows of up to 8 192 tokens, the
+        # measured optimum; 128 for 16 rows of 4 096, where 1 024 would leave half the SMs idle)
+        tokens = batch * max(1, max_ctx // 2)
+        split = (tokens * 4 + 7 * num_sms - 1) // (7 * num_sms)
+        return int(min(1024, max(128, ((split + 63) // 64) * 64)))
     target_ctas = 6 * num_sms
     per_seq = max(1, target_ctas // max(1, batch))
     split = (max_ctx // 2 + per_seq - 1) // per_seq  # typical row is about half the table width
