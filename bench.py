@@ -44,7 +44,7 @@ if ROOT not in sys.path:
 PAGE = 16
 # dram read+write bytes per algorithmic byte of the attention kernel, from an ncu capture of the same kernel on a
 # small case (16 rows x 4096 tokens, 134 MB of KV); traffic grows in proportion to the pages read
-ATTN_TRAFFIC_PER_ALG_BYTE = 1.047
+ATTN_TRAFFIC_PER_ALG_BYTE = 1.04
 
 
 def pkg(sub):
