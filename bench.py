@@ -146,7 +146,7 @@ def main():
     ap.add_argument("--ctx-max", type=int, default=4096, help="longest prompt (tokens)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--split-tokens", type=int, default=0, help="attention KV split size (0 = the library default)")
-    ap.add_argument("--ep-transport", default="nccl", choices=["nccl", "p2p"],
+    ap.add_argument("--ep-transport", default="p2p", choices=["nccl", "p2p"],
                     help="with --ep: NCCL all-to-all, or stores into the peers' mapped receive buffers")
     ap.add_argument("--ep", action="store_true",
                     help="N > 1: expert-parallel MoE (NCCL all-to-all dispatch/combine) instead of independent replicas")
@@ -201,6 +201,8 @@ def main():
     engine = eng_mod.DecodeEngine(cfg, num_blocks=num_blocks, max_batch=args.batch, max_pages_per_seq=max_pages,
                                   device=dev, seed=rank, ep_group=ep_group, split_tokens=args.split_tokens or None,
                                   ep_transport=args.ep_transport)
+    if world > 1 and args.ep and engine.ep_transport != args.ep_transport:  # the mapping could not be made
+        config["parallelism"] = f"dp{world} attention + ep{world} MoE (NCCL all-to-all; peer memory unavailable)"
     # KV image: one random pool, shared by all layers (contents do not affect timing)
     g = torch.Generator(device=dev).manual_seed(1000 + rank)
     engine.k_pools[0].normal_(generator=g)

@@ -143,7 +143,7 @@ class DecodeEngine:
                  embed: torch.Tensor | None = None, lm_head: torch.Tensor | None = None,
                  final_norm: torch.Tensor | None = None, k_pools=None, v_pools=None, use_graphs: bool = True,
                  split_tokens: int | None = None, ep_group=None, ep_capacity: int | None = None,
-                 ep_transport: str = "nccl"):
+                 ep_transport: str = "p2p"):
         if not torch.cuda.is_available():
             raise RuntimeError("DecodeEngine needs a CUDA device; this path has no CPU implementation")
         self.cfg = cfg
@@ -196,10 +196,16 @@ class DecodeEngine:
             arena = None
             if ep_transport == "p2p":
                 # receive buffers of every rank mapped into every process of the node (CUDA IPC): rows then
-                # move by stores from the dispatch kernel and the down-GEMM epilogue, not by a collective
+                # move by stores from the dispatch kernel and the down-GEMM epilogue, not by a collective.
+                # Where the mapping cannot be made, every rank alike takes the NCCL transport and says so.
                 arena = ep.PeerArena(cfg.hidden, self.ep_world, cap, self.device)
-                arena.connect(ops, ep_group)
+                if not arena.connect(ops, ep_group):
+                    import warnings
+                    warnings.warn("peer-memory expert parallelism unavailable, using NCCL all-to-all: "
+                                  + "; ".join(arena.failures))
+                    arena, ep_transport = None, "nccl"
             self.ep_arena = arena
+            self.ep_transport = ep_transport
             self.ep_state = ep.EPState(max_batch, cfg.hidden, cfg.top_k, cfg.experts, self.ep_world, cap, self.device,
                                        ep_group, arena=arena)
         # per layer: qk_norm_rope_append, attention + split reduce, add_rmsnorm, route, rank, scatter+quant, gemm x2,

@@ -82,30 +82,51 @@ class PeerArena:
         self.rank = 0
         self.bases = [self.buf.data_ptr()]  # arena address of every rank, as seen from this process
         self._opened: list[int] = []
+        self.failures: list[str] = []
 
     def view(self, off: int, nbytes: int, dtype, shape):
         return self.buf[off:off + nbytes].view(dtype).view(shape)
 
-    def connect(self, ops, group) -> None:
-        """Exchange CUDA IPC handles over `group` and map every other rank's arena (ranks of one node)."""
+    def connect(self, ops, group) -> bool:
+        """Exchange CUDA IPC handles over `group` and map every other rank's arena (ranks of one node).
+        Collective.  Returns True when EVERY rank mapped every peer; if any rank could not export or map
+        (no peer access, IPC closed in this container), all ranks unmap what they have and return False
+        together, so the caller can fall back to the all-to-all transport on every rank alike."""
         import torch.distributed as dist
 
         world = dist.get_world_size(group)
         if world != self.world:
             raise ValueError(f"arena laid out for {self.world} ranks, group has {world}")
         self.rank = dist.get_rank(group)
-        mine = ops.ipc_export(self.buf)
+        try:
+            mine = ops.ipc_export(self.buf)
+        except Exception as exc:  # reported below, after every rank has joined the exchange
+            mine = ("error", repr(exc))
         everyone = [None] * world
         dist.all_gather_object(everyone, mine, group=group)
+        ok = all(e[0] != "error" for e in everyone)
         self.bases = []
-        for r, (handle, offset) in enumerate(everyone):
-            if r == self.rank:
-                self.bases.append(self.buf.data_ptr())
-            else:
-                base, ptr = ops.ipc_import(handle, offset)
-                self._opened.append(base)
-                self.bases.append(ptr)
+        if ok:
+            try:
+                for r, (handle, offset) in enumerate(everyone):
+                    if r == self.rank:
+                        self.bases.append(self.buf.data_ptr())
+                    else:
+                        base, ptr = ops.ipc_import(handle, offset)
+                        self._opened.append(base)
+                        self.bases.append(ptr)
+            except Exception as exc:
+                ok = False
+                mine = ("error", repr(exc))
+        verdicts = [None] * world
+        dist.all_gather_object(verdicts, mine if not ok else ("ok", ""), group=group)
+        self.failures = [f"rank {r}: {v[1]}" for r, v in enumerate(verdicts) if v[0] == "error"]
+        if self.failures:
+            self.close(ops)
+            self.bases = [self.buf.data_ptr()]
+            return False
         dist.barrier(group=group)  # nobody proceeds (or frees) before every mapping exists
+        return True
 
     def connect_in_process(self, arenas: list["PeerArena"], rank: int) -> None:
         """Several ranks emulated in one process (tests on one GPU): peers are plain device pointers."""
