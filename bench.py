@@ -12,6 +12,12 @@ argmax.  Prefill is not part of the metric: the KV pages are filled with N(0,1)
 values at the prompt lengths (all layers share one random pool image) and only
 decode steps are timed.  Inputs are synthetic and seeded.
 
+N > 1 (one process per GPU under torchrun, weak scaling: 256 sequences per GPU):
+data-parallel attention over disjoint request batches + expert-parallel MoE, the
+experts split N ways and the rows exchanged by stores into the peers' mapped
+receive buffers (--ep-transport nccl: by NCCL all-to-all); --replicas runs N
+independent engines instead.
+
 One JSON line is printed by rank 0:
   value     decode tokens/s with the step's inputs already on the device (CUDA
             graph replays, timed with CUDA events, max over ranks)
@@ -149,8 +155,11 @@ def main():
     ap.add_argument("--ep-transport", default="p2p", choices=["nccl", "p2p"],
                     help="with --ep: NCCL all-to-all, or stores into the peers' mapped receive buffers")
     ap.add_argument("--ep", action="store_true",
-                    help="N > 1: expert-parallel MoE (NCCL all-to-all dispatch/combine) instead of independent replicas")
+                    help="N > 1: data-parallel attention + expert-parallel MoE (the default for N > 1)")
+    ap.add_argument("--replicas", action="store_true",
+                    help="N > 1: N independent data-parallel engines with all experts each, no data-path exchange")
     args = ap.parse_args()
+    args.ep = not args.replicas  # only matters for N > 1
 
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
