@@ -235,6 +235,9 @@ def main():
     for _ in range(max(3, args.warmup)):
         engine.tokens[:B].copy_(engine.step(B))
     barrier()
+    p2p = engine.ep_state is not None and engine.ep_state.arena is not None
+    if p2p:
+        engine.ep_state.status[16:24].zero_()  # per-peer wait nanoseconds, counted over the timed region only
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     with ClockSampler(local_rank) as clocks:
         ev0.record()
@@ -248,6 +251,13 @@ def main():
     ops.read_status(engine.moe_ws, "MoE workspace status after the timed region")
     if engine.ep_state is not None and bool(engine.ep_state.overflow):
         raise SystemExit("expert-parallel dispatch overflowed its per-destination capacity; results are invalid")
+    if p2p:
+        ops.read_status(engine.ep_state.status, "peer-memory exchange status after the timed region")
+        # time inside the flag exchanges waiting for the slowest peer (the threads of a barrier wait side by side)
+        wait_ns = engine.ep_state.status[16:16 + world].to(torch.int64) & 0xffffffff
+        wait_ms = torch.tensor([float(wait_ns.max()) / 1e6 / args.steps], device=dev, dtype=torch.float64)
+        torch.distributed.all_reduce(wait_ms, op=torch.distributed.ReduceOp.MAX)
+        config["ep_wait_ms_per_step_max_rank"] = round(float(wait_ms), 3)
 
     # ---- end to end through the backend API with host buffers
     backend = backend_mod.B200Backend(engine)

@@ -388,6 +388,9 @@ int b200_moe_permute_gather_fp8(const int32_t* ids, int num_rows, int num_expert
  * stream).  wait: returns when every entry of this rank's flags has reached its epoch; the wait is bounded
  * (about a second), after which the status word gets a peer-timeout code and the stream carries on.
  * barrier = signal + wait in one launch.  All ranks must issue the same sequence of phases.
+ * status_word (may be NULL) must head an int32 array of at least 64 words: word 0 is the sticky status, words
+ * 16..23 accumulate (modulo 2^32) the nanoseconds this rank has spent waiting for rank 0..7 - a diagnostic
+ * for load imbalance between the ranks.
  */
 int b200_ep_signal(void* const* flag_peers, int32_t* epoch, int ep_rank, int ep_world, void* stream);
 int b200_ep_wait(const int32_t* local_flags, const int32_t* epoch, int ep_world, void* status_word,

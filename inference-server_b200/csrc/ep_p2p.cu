@@ -48,8 +48,17 @@ __device__ __forceinline__ int ep_bump_epoch(int* epoch) {
   return e_sm;
 }
 
-__device__ __forceinline__ void ep_wait_flag(const int* flag, int want, int* err) {
+__device__ __forceinline__ unsigned long long global_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+
+// Spins (bounded) until *flag reaches `want`.  The status block doubles as a small diagnostic: word 16 + r of
+// a status array of at least 64 words accumulates the nanoseconds this rank spent waiting for rank r.
+__device__ __forceinline__ void ep_wait_flag(const int* flag, int want, int* err, int peer) {
   bool ok = false;
+  const unsigned long long t0 = global_ns();
   for (uint32_t i = 0; i < kEpWaitPolls; ++i) {
     if (ld_acquire_sys(flag) - want >= 0) {
       ok = true;
@@ -58,6 +67,8 @@ __device__ __forceinline__ void ep_wait_flag(const int* flag, int want, int* err
     if (i > 64) __nanosleep(200);
   }
   if (!ok) set_error(err, kErrDevPeerTimeout);
+  if (err != nullptr) atomicAdd(reinterpret_cast<unsigned int*>(err) + 16 + peer,
+                                static_cast<unsigned int>((global_ns() - t0) & 0xffffffffu));
   __threadfence_system();
 }
 
@@ -70,7 +81,7 @@ __global__ void ep_signal_kernel(const EpFlagPeers fp, int* epoch, int my_rank, 
 }
 
 __global__ void ep_wait_kernel(const int* local_flags, const int* epoch, int world, int* err) {
-  if (threadIdx.x < world) ep_wait_flag(local_flags + threadIdx.x, *epoch, err);
+  if (threadIdx.x < world) ep_wait_flag(local_flags + threadIdx.x, *epoch, err, threadIdx.x);
 }
 
 // signal + wait in one launch: thread r tells rank r, then waits for rank r.
@@ -80,7 +91,7 @@ __global__ void ep_barrier_kernel(const EpFlagPeers fp, const int* local_flags, 
   if (threadIdx.x < world) {
     __threadfence_system();
     st_release_sys(fp.flags[threadIdx.x] + my_rank, e);
-    ep_wait_flag(local_flags + threadIdx.x, e, err);
+    ep_wait_flag(local_flags + threadIdx.x, e, err, threadIdx.x);
   }
 }
 
