@@ -4,6 +4,8 @@
                                                                # contexts U{512..8192}, groups of 8 share 1024 tokens
     python inference-server_b200/microbench.py moe             # FP8 MoE layer, T in {1,16,64,256,1024,4096}
     python inference-server_b200/microbench.py ep --world 8    # expert-parallel layer, ranks emulated in-process
+    python inference-server_b200/microbench.py fp8peak         # dense e4m3 GEMM rate of the library (cuBLASLt),
+                                                               # the denominator for the MoE GEMM's tensor fraction
     ... attn --small / moe --small                             # few launches on a few hundred MB: sized for a profiler
 
 Every case prints one JSON line per measured point: CUDA-event time (median of --iters launches after 3 warm-ups,
@@ -226,6 +228,25 @@ def run_ep(args) -> None:
                       "note": "all ranks on one GPU: no NVLink time and no waiting for other ranks"}))
 
 
+# ------------------------------------------------------------ dense FP8 peak --
+def run_fp8peak(args) -> None:
+    """What the library's dense e4m3 x e4m3 -> bf16 GEMM reaches on this GPU (per-tensor scales, no block
+    scales): the practical tensor-core ceiling that the block-scaled MoE GEMM is compared with."""
+    n = args.size
+    g = torch.Generator(device=DEV).manual_seed(0)
+    a = torch.randn(n, n, generator=g, device=DEV).to(torch.float8_e4m3fn)
+    b = torch.randn(n, n, generator=g, device=DEV).to(torch.float8_e4m3fn)
+    one = torch.ones((), device=DEV)
+    fn = lambda: torch._scaled_mm(a, b.t(), scale_a=one, scale_b=one, out_dtype=torch.bfloat16)
+    med, mn = Timer(args.iters, flush=False)(fn, warm=5)
+    x = torch.randn(n, n, generator=g, device=DEV).bfloat16()
+    y = torch.randn(n, n, generator=g, device=DEV).bfloat16()
+    med16, _ = Timer(args.iters, flush=False)(lambda: torch.matmul(x, y.t()), warm=5)
+    print(json.dumps({"case": "fp8peak", "size": n, "fp8_us_median": med, "fp8_TFLOPs": 2 * n ** 3 / med / 1e6,
+                      "fp8_TFLOPs_best": 2 * n ** 3 / mn / 1e6, "bf16_TFLOPs": 2 * n ** 3 / med16 / 1e6,
+                      "note": "library GEMMs (cuBLASLt through torch), timed in isolation"}))
+
+
 def main() -> None:
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     sub = ap.add_subparsers(dest="case", required=True)
@@ -249,13 +270,17 @@ def main() -> None:
         p.add_argument("--top-k", type=int, default=8)
         p.add_argument("--hidden", type=int, default=2048)
         p.add_argument("--inter", type=int, default=768)
+    f = sub.add_parser("fp8peak")
+    f.add_argument("--size", type=int, default=8192)
+    f.add_argument("--iters", type=int, default=20)
+    f.add_argument("--small", action="store_true", help=argparse.SUPPRESS)
     for p in (a, m, e):
         p.add_argument("--iters", type=int, default=20)
         p.add_argument("--small", action="store_true", help="a few launches on a small case (for a profiler)")
     args = ap.parse_args()
     if not torch.cuda.is_available():
         raise SystemExit("microbench.py needs a CUDA device")
-    {"attn": run_attn, "moe": run_moe, "ep": run_ep}[args.case](args)
+    {"attn": run_attn, "moe": run_moe, "ep": run_ep, "fp8peak": run_fp8peak}[args.case](args)
 
 
 if __name__ == "__main__":

@@ -77,3 +77,87 @@ def test_plan_dispatch_slots():
     assert slot.tolist() == [0, 6 + 1, 6 + 0, 2, 6 + 4, 1, 6 + 3, 6 + 2]
     assert expert_of_slot.tolist() == [0, 0, 1, 4, 4, 4, 0, 1, 1, 2, 3, 4]
     assert ep.default_capacity(256, 8, 8) == 512
+
+
+# ------------------------------------------------------------ peer arena ----
+class _FakeIpc:
+    """Stand-in for the ops IPC calls: handles are (rank, address) pairs, importing one "maps" it to a fake
+    address; optionally one rank fails to export or to import."""
+
+    def __init__(self, rank, fail_export_on=None, fail_import_on=None):
+        self.rank, self.fail_export_on, self.fail_import_on = rank, fail_export_on, fail_import_on
+        self.closed = []
+
+    def ipc_export(self, t):
+        if self.rank == self.fail_export_on:
+            raise RuntimeError("export refused")
+        return (b"H%03d" % self.rank).ljust(64, b"\0"), 128
+
+    def ipc_import(self, handle, offset):
+        if self.rank == self.fail_import_on:
+            raise RuntimeError("import refused")
+        peer = int(handle[1:4])
+        return 1_000_000 * (peer + 1), 1_000_000 * (peer + 1) + offset
+
+    def ipc_close(self, base):
+        self.closed.append(base)
+
+
+def _arena_worker(rank, world, port, fail_export_on, fail_import_on, results):
+    sys.path.insert(0, ROOT)
+    import importlib
+
+    ep = importlib.import_module("inference-server_b200.ep")
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        arena = ep.PeerArena(256, world, 32, "cpu")
+        fake = _FakeIpc(rank, fail_export_on, fail_import_on)
+        ok = arena.connect(fake, dist.group.WORLD)
+        results[rank] = (ok, list(arena.bases), list(fake.closed), list(arena.failures), arena.buf.data_ptr())
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("fail_export_on,fail_import_on", [(None, None), (1, None), (None, 0)])
+def test_peer_arena_connect_agrees_on_every_rank(fail_export_on, fail_import_on):
+    """The mapping either succeeds on every rank or every rank alike falls back (and unmaps what it had):
+    a rank must never be left waiting in a collective for one that gave up."""
+    world = 2
+    mgr = mp.Manager()
+    results = mgr.dict()
+    port = 29900 + (os.getpid() * 3 + (fail_export_on or 0) * 2 + (fail_import_on is not None)) % 90
+    mp.spawn(_arena_worker, args=(world, port, fail_export_on, fail_import_on, results), nprocs=world, join=True)
+    assert len(results) == world
+    oks = [results[r][0] for r in range(world)]
+    assert oks == [fail_export_on is None and fail_import_on is None] * world
+    for rank in range(world):
+        ok, bases, closed, failures, own = results[rank]
+        if ok:
+            other = 1 - rank
+            assert bases[rank] == own and bases[other] == 1_000_000 * (other + 1) + 128
+            assert closed == [] and failures == []
+        else:
+            assert bases == [own]
+            assert failures and "refused" in failures[0]
+            # a rank that had mapped its peer before the other one failed has unmapped it again
+            assert len(closed) <= 1
+
+
+def test_peer_arena_layout_is_aligned_and_disjoint():
+    sys.path.insert(0, ROOT)
+    import importlib
+
+    ep = importlib.import_module("inference-server_b200.ep")
+    for hidden, world, cap in [(2048, 8, 512), (4096, 4, 48), (512, 2, 16)]:
+        a = ep.PeerArena(hidden, world, cap, "cpu")
+        rows = world * cap
+        offs = [a.off_xq, a.off_xs, a.off_id, a.off_y, a.off_flags, a.nbytes]
+        sizes = [rows * hidden, rows * (hidden // 128) * 4, rows * 4, rows * hidden * 2, 64]
+        assert all(o % 256 == 0 for o in offs[:-1])
+        for o, n, nxt in zip(offs, sizes, offs[1:]):
+            assert o + n <= nxt
+        st = ep.EPState(4, hidden, 2, 8 * world, world, cap, "cpu", arena=a)
+        assert st.xq_recv.shape == (rows, hidden) and st.y_recv.dtype == torch.bfloat16
+        assert st.flags[0].numel() == 8 and st.flags[1].data_ptr() - st.flags[0].data_ptr() == 32
+        assert st.peer_flags[1][0] == a.buf.data_ptr() + a.off_flags + 32
