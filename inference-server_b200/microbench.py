@@ -29,6 +29,7 @@ quant = importlib.import_module("inference-server_b200.quant")
 ep = importlib.import_module("inference-server_b200.ep")
 DEV = "cuda"
 PAGE = 16
+MOE_TOKENS_DEFAULT = "1,16,64,256,1024,4096"
 
 
 def measured_hbm_gbs() -> tuple[float, str]:
@@ -132,8 +133,13 @@ def moe_weights(E, H, I, seed=0):
 def run_moe(args) -> None:
     E, K, H, I = args.experts, args.top_k, args.hidden, args.inter
     w13q, w13s, w2q, w2s = moe_weights(E, H, I)
+    if args.tiled:  # the same values re-ordered into contiguous 128x128 blocks (bit-identical results)
+        w13q = quant.tile_weight_blocks(w13q.view(torch.uint8))
+        w2q = quant.tile_weight_blocks(w2q.view(torch.uint8))
     g = torch.Generator(device=DEV).manual_seed(1)
-    tokens = [64] if args.small else [int(t) for t in args.tokens.split(",")]
+    tokens = [int(t) for t in args.tokens.split(",")]
+    if args.small:
+        tokens = tokens[:1] if args.tokens != MOE_TOKENS_DEFAULT else [64]
     timer = Timer(args.iters)
     peak, src = measured_hbm_gbs()
     for T in tokens:
@@ -164,7 +170,7 @@ def run_moe(args) -> None:
         wbytes = hit * (3 * H * I + scale_bytes)
         alg = wbytes + T * H * 4 + T * E * 4
         flops = T * K * 6 * H * I
-        print(json.dumps({"case": "moe", "tokens": T, "experts_hit": hit, "layer_us_median": med, "layer_us_min": mn,
+        print(json.dumps({"case": "moe", "tokens": T, "tiled_weights": bool(args.tiled), "experts_hit": hit, "layer_us_median": med, "layer_us_min": mn,
                           "gate_up_us": gu, "down_us": dn, "alg_MB": alg / 1e6, "layer_GBs": alg / med / 1e3,
                           "gate_up_GBs": hit * 2 * H * I / gu / 1e3, "down_GBs": hit * H * I / dn / 1e3,
                           "frac_of_hbm_peak_gemms": wbytes / (gu + dn) / 1e3 / peak, "layer_TFLOPs": flops / med / 1e6,
@@ -261,7 +267,8 @@ def main() -> None:
     a.add_argument("--share-tokens", type=int, default=1024)
     a.add_argument("--split-tokens", type=int, default=0)
     m = sub.add_parser("moe")
-    m.add_argument("--tokens", default="1,16,64,256,1024,4096")
+    m.add_argument("--tokens", default=MOE_TOKENS_DEFAULT, help="token counts; with --small only the first (default 64)")
+    m.add_argument("--tiled", action="store_true", help="weights stored as contiguous 128x128 blocks")
     e = sub.add_parser("ep")
     e.add_argument("--world", type=int, default=8)
     e.add_argument("--tokens-per-rank", type=int, default=256)
