@@ -272,14 +272,6 @@ int b200_act_quant_fp8(const void* x, const int32_t* row_of_pair, int num_tokens
  */
 #define B200_WEIGHTS_ROW_MAJOR 0
 #define B200_WEIGHTS_TILED 1
-/*
- * Two kernel forms compute the same thing, bit for bit.  One CTA per 128-row x 256-column tile; or, from a mean
- * of 192 rows per expert on (num_rows >= 192 * num_experts), a CTA pair on two row tiles of one expert and one
- * column tile of its weights (tcgen05 cta_group::2: each CTA loads half of the weight tile), which moves a
- * third less operand data when the kernel is bound by that.  OR one of these into weight_layout to force a form.
- */
-#define B200_GEMM_FORCE_CTA_PAIRS 0x100
-#define B200_GEMM_FORCE_SINGLE_CTA 0x200
 int b200_moe_fp8_gemm_gate_up(const void* xq, const float* x_scale, const void* w13,
                               const float* w13_scale_inv, const void* tiles,
                               const int32_t* num_tiles, void* hq, float* h_scale,

@@ -49,7 +49,7 @@ struct EpPeers {
 // Row tile consumed by the grouped GEMM: up to 128 consecutive sorted rows of
 // one expert (the last tile of an expert may be short).
 struct __align__(16) MoeTile {
-  int expert, row0, rows, pad;  // pad: ordinal of the tile inside its expert (0 for the first 128 rows, ...)
+  int expert, row0, rows, pad;
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
@@ -198,64 +198,6 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
 }
 __device__ __forceinline__ void tmem_ld_wait() {
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-}
-
-// ------------------------------------------------- CTA pairs (cta_group::2) --
-// Two CTAs of a cluster (ranks 2i and 2i+1) on the two SMs of a pair run one MMA of M = 256: each CTA holds
-// 128 rows of A, half of the N rows of B and the 128 x N accumulator of its own rows; one thread of the even
-// CTA issues the instruction for both.
-__device__ __forceinline__ uint32_t cluster_ctarank() {
-  uint32_t r;
-  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
-  return r;
-}
-__device__ __forceinline__ void cluster_sync_all() {
-  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
-}
-// shared::cluster address of the same shared-memory offset in CTA `rank` of the cluster
-__device__ __forceinline__ uint32_t mapa_u32(uint32_t addr, uint32_t rank) {
-  uint32_t r;
-  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
-  return r;
-}
-__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
-  asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
-}
-// One warp of EACH CTA of the pair (the same warp index in both) allocates / frees together.
-__device__ __forceinline__ void tmem_alloc_pair(uint32_t smem_dst, uint32_t ncols) {
-  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_dst), "r"(ncols)
-               : "memory");
-  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
-}
-__device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t ncols) {
-  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
-}
-// Arrives once on the barrier at `cluster_addr` (in either CTA of the pair) when every pair MMA issued so far
-// by this thread has finished.
-__device__ __forceinline__ void tc_commit_pair(uint32_t cluster_addr) {
-  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(cluster_addr)
-               : "memory");
-}
-// D[tmem of both CTAs] (+)= A[smem of both] * B[smem of both], e4m3, M = 256, one K = 32 slice.
-__device__ __forceinline__ void tc_mma_f8_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
-                                               uint32_t accumulate) {
-  const uint32_t z = 0;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::2.kind::f8f6f4 [%0], %1, %2, %3, {%5, %5, %5, %5, %5, %5, %5, %5}, p;\n\t}"
-      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(z)
-      : "memory");
-}
-// 2-D tiled load into THIS CTA's shared memory whose completion bytes are counted on the barrier at the same
-// offset in the EVEN CTA of the pair (clearing the rank bit of the shared-window address selects it).
-__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y) {
-  const uint32_t bar_even = bar & 0xFEFFFFFFu;
-  asm volatile(
-      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes "
-      "[%0], [%1, {%3, %4}], [%2];"
-      ::"r"(dst), "l"(map), "r"(bar_even), "r"(x), "r"(y)
-      : "memory");
 }
 
 // Shared-memory matrix descriptor for a K-major operand tile whose rows are

@@ -149,7 +149,7 @@ moe_scatter_kernel(const int* __restrict__ topk_ids, const int* __restrict__ ran
           t.expert = e;
           t.row0 = off[e] + j * tile_rows;
           t.rows = min(tile_rows, cnt[e] - j * tile_rows);
-          t.pad = j;  // ordinal of the tile inside its expert
+          t.pad = 0;
           tiles[tp + j] = t;
         }
         if (e == tile_experts - 1) *num_tiles = tp + nt;
@@ -203,7 +203,7 @@ moe_scatter_rows_kernel(const int* __restrict__ ids, const int* __restrict__ ran
         t.expert = e;
         t.row0 = off[e] + j * tile_rows;
         t.rows = min(tile_rows, cnt[e] - j * tile_rows);
-        t.pad = j;  // ordinal of the tile inside its expert
+        t.pad = 0;
         tiles[tp + j] = t;
       }
       if (e == tile_experts - 1) *num_tiles = tp + nt;
@@ -333,7 +333,7 @@ __global__ void moe_scatter_quant_kernel(const __nv_bfloat16* __restrict__ x, co
         tl.expert = e;
         tl.row0 = off[e] + j * tile_rows;
         tl.rows = min(tile_rows, cnt[e] - j * tile_rows);
-        tl.pad = j;  // ordinal of the tile inside its expert
+        tl.pad = 0;
         tiles[toff[e] + j] = tl;
       }
     if (tid == 0) *num_tiles = toff[E];

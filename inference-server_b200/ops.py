@@ -416,12 +416,8 @@ def _weight_dims(w: torch.Tensor):
     raise ValueError(f"expert weights must be [E, rows, cols] or [E, rows/128, cols/128, 128, 128], got {tuple(w.shape)}")
 
 
-GEMM_FORM = {"auto": 0, "cta_pairs": 0x100, "single_cta": 0x200}  # B200_GEMM_FORCE_* of the header
-
-
-def moe_fp8_gemm_gate_up(xq, x_scale, w13, w13_scale_inv, perm: Permutation, status=None, form: str = "auto"):
-    """h = silu(W13[:I] x) * (W13[I:] x) per sorted row, re-quantised to e4m3.  `form` forces one of the two
-    kernel forms (see the header); "auto" chooses by the mean rows per expert."""
+def moe_fp8_gemm_gate_up(xq, x_scale, w13, w13_scale_inv, perm: Permutation, status=None):
+    """h = silu(W13[:I] x) * (W13[I:] x) per sorted row, re-quantised to e4m3."""
     xq, w13 = _as_u8(xq), _as_u8(w13)
     _need(xq, "xq", torch.uint8)
     _need(w13, "w13", torch.uint8)
@@ -436,14 +432,13 @@ def moe_fp8_gemm_gate_up(xq, x_scale, w13, w13_scale_inv, perm: Permutation, sta
     hs = torch.empty(rows, inter // 128, dtype=torch.float32, device=xq.device)
     rc = _lib.load().b200_moe_fp8_gemm_gate_up(
         _ptr(xq), _ptr(x_scale), _ptr(w13), _ptr(w13_scale_inv), _ptr(perm.tiles), _ptr(perm.num_tiles),
-        _ptr(hq), _ptr(hs), _ptr(status), rows, E, H, inter, layout | GEMM_FORM[form], _stream(),
+        _ptr(hq), _ptr(hs), _ptr(status), rows, E, H, inter, layout, _stream(),
     )
     check(rc, "b200_moe_fp8_gemm_gate_up")
     return hq, hs
 
 
-def moe_fp8_gemm_down(hq, h_scale, w2, w2_scale_inv, perm: Permutation, status=None, out=None, out_row_map=None,
-                      form: str = "auto"):
+def moe_fp8_gemm_down(hq, h_scale, w2, w2_scale_inv, perm: Permutation, status=None, out=None, out_row_map=None):
     """y = W2 h per sorted row, bf16.  With `out_row_map` (int32 per sorted row) row r is written to row
     out_row_map[r] of `out` instead of row r."""
     hq, w2 = _as_u8(hq), _as_u8(w2)
@@ -461,7 +456,7 @@ def moe_fp8_gemm_down(hq, h_scale, w2, w2_scale_inv, perm: Permutation, status=N
     _need(y, "out", torch.bfloat16)
     rc = _lib.load().b200_moe_fp8_gemm_down(
         _ptr(hq), _ptr(h_scale), _ptr(w2), _ptr(w2_scale_inv), _ptr(perm.tiles), _ptr(perm.num_tiles),
-        _ptr(y), _ptr(out_row_map), _ptr(status), rows, E, H, inter, layout | GEMM_FORM[form], _stream(),
+        _ptr(y), _ptr(out_row_map), _ptr(status), rows, E, H, inter, layout, _stream(),
     )
     check(rc, "b200_moe_fp8_gemm_down")
     return y
@@ -525,8 +520,7 @@ def moe_fp8_workspace(num_tokens, num_experts, top_k, hidden, inter, device):
 
 
 def moe_fp8_forward(x, router_logits, w13, w13_scale_inv, w2, w2_scale_inv, top_k, renormalize=True,
-                    workspace=None, out=None, residual=None, norm_weight=None, eps: float = 1e-6,
-                    form: str = "auto"):
+                    workspace=None, out=None, residual=None, norm_weight=None, eps: float = 1e-6):
     """The whole FP8 MoE layer on one stream: route, permute+quantise, two grouped GEMMs, combine.
 
     With `residual` and `norm_weight` the combine is fused with the next residual add and RMSNorm:
@@ -545,7 +539,6 @@ def moe_fp8_forward(x, router_logits, w13, w13_scale_inv, w2, w2_scale_inv, top_
     if _weight_dims(w2)[3] != layout:
         raise ValueError("w13 and w2 must use the same weight layout")
     inter = two_i // 2
-    layout |= GEMM_FORM[form]
     if workspace is None:
         workspace = moe_fp8_workspace(T, E, top_k, H, inter, x.device)
     if out is None:

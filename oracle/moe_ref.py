@@ -37,7 +37,7 @@ def permute_ref(topk_ids: torch.Tensor, num_experts: int):
     tiles = []
     for e in range(num_experts):
         for j in range(0, int(counts[e]), 128):
-            tiles.append((e, int(offsets[e]) + j, min(128, int(counts[e]) - j), j // 128))  # last: ordinal in the expert
+            tiles.append((e, int(offsets[e]) + j, min(128, int(counts[e]) - j), 0))
     return dict(sorted_pair_ids=sorted_pair, row_of_pair=row_of_pair, expert_offsets=offsets,
                 tiles=np.array(tiles, dtype=np.int32).reshape(-1, 4))
 

@@ -183,38 +183,6 @@ def test_tiled_weight_layout_gives_identical_bits(ops, T, E, K, H, I):
     assert torch.equal(out_rm, out_tl)
 
 
-@pytest.mark.parametrize("T,E,K,H,I", [(300, 8, 2, 512, 256), (700, 8, 2, 512, 256), (64, 16, 4, 512, 256),
-                                       (4096, 128, 8, 2048, 768), (1500, 16, 4, 2048, 768)])
-def test_cta_pair_form_gives_the_same_bits_as_the_single_cta_form(ops, T, E, K, H, I):
-    """The CTA-pair form (two row tiles of an expert share one pass over its weights) is the same sums in the
-    same order: h bytes, scales and outputs must be identical, for experts with one, two (a full pair), three
-    (a pair and an odd tile) and more row tiles, and for experts without rows."""
-    w13q, w13s, w2q, w2s = [t.to(DEV) for t in make_layer(E, H, I, seed=E + H)]
-    g = torch.Generator().manual_seed(T)
-    x = torch.randn(T, H, generator=g).bfloat16().to(DEV)
-    logits = torch.randn(T, E, generator=g)
-    logits[:, E - 1] = -30.0  # one expert gets no rows at all
-    logits = logits.to(DEV)
-    ids, _ = ops.moe_route(logits, K)
-    p = ops.moe_permute(ids, E)
-    xq, xs = ops.act_quant_fp8(x, p.row_of_pair, K)
-    status = torch.zeros(64, dtype=torch.int32, device=DEV)
-    res = {}
-    for form in ("single_cta", "cta_pairs"):
-        hq, hs = ops.moe_fp8_gemm_gate_up(xq, xs, w13q, w13s, p, status, form=form)
-        y = ops.moe_fp8_gemm_down(hq, hs, w2q, w2s, p, status, form=form)
-        ops.read_status(status, form)
-        res[form] = (hq, hs, y)
-    a, b = res["single_cta"], res["cta_pairs"]
-    assert torch.equal(a[0], b[0]), f"h bytes differ: {(a[0] != b[0]).float().mean().item():.6f}"
-    assert torch.equal(a[1], b[1]) and torch.equal(a[2], b[2])
-    # and through the fused layer entry point, twice in a row (barrier phases, TMEM hand-over between launches)
-    out1 = ops.moe_fp8_forward(x, logits, w13q, w13s, w2q, w2s, K, True, form="single_cta")
-    for _ in range(2):
-        out2 = ops.moe_fp8_forward(x, logits, w13q, w13s, w2q, w2s, K, True, form="cta_pairs")
-        assert torch.equal(out1, out2)
-
-
 @pytest.mark.parametrize("T", [1, 16, 64, 256])
 def test_full_layer_config3_shapes(ops, T):
     E, K, H, I = 128, 8, 2048, 768
