@@ -171,6 +171,7 @@ def main():
     ap.add_argument("--replicas", action="store_true",
                     help="N > 1: N independent data-parallel engines with all experts each, no data-path exchange")
     args = ap.parse_args()
+    ep_asked = args.ep
     args.ep = not args.replicas  # only matters for N > 1
 
     rank = int(os.environ.get("RANK", "0"))
@@ -217,6 +218,19 @@ def main():
         dist.init_process_group("nccl", device_id=dev)
 
     eng_mod, ops, backend_mod = pkg("engine"), pkg("ops"), pkg("backend")
+    if world > 1 and args.ep and args.ep_transport == "p2p" and not ep_asked and cfg.name == "qwen3-30b-a3b":
+        # The default multi-GPU form needs every rank's receive buffers mapped into every process (CUDA IPC).
+        # Where that cannot be done, the model still fits one GPU, so the default falls back to replicas
+        # (all ranks alike; the line says so) rather than to the slower NCCL exchange.  --ep keeps EP.
+        probe = pkg("ep").PeerArena(256, world, 16, dev)
+        if probe.connect(ops, torch.distributed.group.WORLD):
+            torch.distributed.barrier()
+            probe.close(ops)
+        else:
+            args.ep = False
+            config["parallelism"] = (f"dp{world} (replicas: disjoint request batches, no data-path collective; "
+                                     f"peer memory unavailable: {'; '.join(probe.failures)[:200]})")
+        del probe
     t_setup = time.time()
     ep_group = torch.distributed.group.WORLD if world > 1 and args.ep else None
     engine = eng_mod.DecodeEngine(cfg, num_blocks=num_blocks, max_batch=args.batch, max_pages_per_seq=max_pages,
