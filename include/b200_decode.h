@@ -80,6 +80,21 @@ int b200_paged_attn_decode(const void* q, const void* k_pool, const void* v_pool
                            void* stream);
 
 /*
+ * b200_paged_attn_decode for the rows of a prompt chunk: batch rows 2i and 2i+1 are two consecutive tokens of
+ * one sequence and SHARE block_table row 2i (row 2i+1 of the table is not read); ctx_lens stays per row (the
+ * causal mask: token t attends to t+1 positions).  The second row rides in the upper half of the m16 MMA tile,
+ * which up to 8 query heads per kv head leave idle, so every page is fetched once for two rows.  Same results,
+ * bit for bit, as b200_paged_attn_decode on the same rows.  bf16, page_size 16, head_dim 128 with 4 kv heads or
+ * head_dim 64 with 2, at most 8 query heads per kv head; workspace as for b200_paged_attn_decode.  Replaces,
+ * for cache-hit prompts, the page gather of kv_cache/hf_format.py:21-45 + the HF prompt attention.
+ */
+int b200_paged_attn_decode_pairs(const void* q, const void* k_pool, const void* v_pool,
+                                 const int32_t* block_table, const int32_t* ctx_lens, void* out,
+                                 void* workspace, size_t workspace_bytes, int batch, int num_q_heads,
+                                 int num_kv_heads, int head_dim, int page_size, int num_blocks,
+                                 int max_pages_per_seq, float scale, int split_tokens, void* stream);
+
+/*
  * Paged decode attention for callers that cannot allocate device memory.
  * No counterpart in the reference: it exists for hosts of this library that own
  * no allocator at the point of the call - a server whose device memory was

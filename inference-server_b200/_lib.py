@@ -25,6 +25,7 @@ SIGNATURES = {
         c_int,
         [c_void_p] * 7 + [c_size_t] + [c_int] * 7 + [c_float, c_int, c_int, c_void_p],
     ),
+    "b200_paged_attn_decode_pairs": (c_int, [c_void_p] * 7 + [c_size_t] + [c_int] * 7 + [c_float, c_int, c_void_p]),
     "b200_paged_attn_decode_static": (c_int, [c_void_p] * 7 + [c_int] * 7 + [c_float, c_int, c_void_p]),
     "b200_kv_append": (c_int, [c_void_p] * 7 + [c_int] * 7 + [c_void_p]),
     "b200_add_rmsnorm": (c_int, [c_void_p, c_void_p, c_void_p, c_float, c_int, c_int, c_void_p, c_void_p]),

@@ -55,7 +55,10 @@ struct AttnCfg {
   static constexpr int kSmemBytes = kRingBytes + 1024 /* alignment slack */ + 16 * STAGES /* barriers */;
 };
 
-template <int D, int HKV, int STAGES, int CTAS>
+// PAIRS: two rows per CTA - batch rows 2i and 2i+1, which must share block_table row 2i (two consecutive tokens
+// of one prompt).  The second row rides in the upper eight rows of the m16 MMA tile, which a kv group of up to
+// eight query heads leaves idle, so a prompt chunk reads every page half as often.
+template <int D, int HKV, int STAGES, int CTAS, bool PAIRS = false>
 __global__ void __launch_bounds__((HKV + 1) * 32, CTAS)
 paged_attn_decode_kernel(const __grid_constant__ CUtensorMap k_map,
                          const __grid_constant__ CUtensorMap v_map,
@@ -64,7 +67,7 @@ paged_attn_decode_kernel(const __grid_constant__ CUtensorMap k_map,
                          const int* __restrict__ ctx_lens,
                          float* __restrict__ part_o, float2* __restrict__ part_ml,
                          __nv_bfloat16* __restrict__ out,
-                         int* __restrict__ err, int num_q_heads, int num_blocks, int max_pages,
+                         int* __restrict__ err, int batch, int num_q_heads, int num_blocks, int max_pages,
                          int split_tokens, int max_splits, float scale_log2) {
 #ifdef B200_DEVICE_OK
   using Cfg = AttnCfg<D, HKV, STAGES, CTAS>;
@@ -72,18 +75,38 @@ paged_attn_decode_kernel(const __grid_constant__ CUtensorMap k_map,
   const uint32_t ring = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const uint32_t bars = ring + Cfg::kRingBytes;  // full[STAGES], empty[STAGES]
 
-  const int b = blockIdx.x, split = blockIdx.y;
+  const int b = PAIRS ? 2 * blockIdx.x : blockIdx.x, split = blockIdx.y;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int group = num_q_heads / HKV;
+  const bool has1 = PAIRS && b + 1 < batch;  // the pair's second row exists
 
   int L = ctx_lens[b];
   if (L < 0 || L > max_pages * kPage) {
     if (threadIdx.x == 0) set_error(err, kErrDevBadCtxLen);
     L = L < 0 ? 0 : max_pages * kPage;
   }
+  int L0 = L, L1 = 0;  // PAIRS: lengths of the two rows; L becomes the longer one
+  if (PAIRS) {
+    if (has1) {
+      L1 = ctx_lens[b + 1];
+      if (L1 < 0 || L1 > max_pages * kPage) {
+        if (threadIdx.x == 0) set_error(err, kErrDevBadCtxLen);
+        L1 = L1 < 0 ? 0 : max_pages * kPage;
+      }
+    }
+    if (split == 0) {  // a row with no context attends to nothing: zeros
+      if (L0 == 0)
+        for (int i = threadIdx.x; i < num_q_heads * D; i += blockDim.x)
+          out[static_cast<size_t>(b) * num_q_heads * D + i] = __float2bfloat16(0.f);
+      if (has1 && L1 == 0)
+        for (int i = threadIdx.x; i < num_q_heads * D; i += blockDim.x)
+          out[static_cast<size_t>(b + 1) * num_q_heads * D + i] = __float2bfloat16(0.f);
+    }
+    L = max(L0, L1);
+  }
   const int start = split * split_tokens;
   if (start >= L) {  // uniform for the whole CTA
-    if (L == 0 && split == 0)  // a row with no context attends to nothing: zeros
+    if (!PAIRS && L == 0 && split == 0)  // a row with no context attends to nothing: zeros
       for (int i = threadIdx.x; i < num_q_heads * D; i += blockDim.x)
         out[static_cast<size_t>(b) * num_q_heads * D + i] = __float2bfloat16(0.f);
     return;
@@ -140,22 +163,25 @@ paged_attn_decode_kernel(const __grid_constant__ CUtensorMap k_map,
   const int kvh = warp;      // this warp's kv head
   const int gq = lane >> 2;  // fragment row (query head inside the kv group)
   const int tq = lane & 3;
-  const bool hi_rows = group > 8;
+  const bool hi_rows = PAIRS ? has1 : group > 8;
+  // upper eight tile rows: heads 8.. of the same row, or (PAIRS) heads 0..7 of the pair's second row
+  const bool hi_ok = PAIRS ? (has1 && gq < group) : gq + 8 < group;
 
   // Q fragments for every 16-wide slice of head_dim (A operand, rows = heads).
   uint32_t qa[D / 16][4];
   {
     const __nv_bfloat16* qb = q + (static_cast<size_t>(b) * num_q_heads + kvh * group) * D;
+    const __nv_bfloat16* qhi = PAIRS ? qb + static_cast<size_t>(num_q_heads) * D + static_cast<size_t>(gq) * D
+                                     : qb + static_cast<size_t>(gq + 8) * D;
 #pragma unroll
     for (int ks = 0; ks < D / 16; ++ks) {
       const int d0 = ks * 16 + 2 * tq;
       const uint32_t* r0 = reinterpret_cast<const uint32_t*>(qb + static_cast<size_t>(gq) * D + d0);
-      const uint32_t* r1 =
-          reinterpret_cast<const uint32_t*>(qb + static_cast<size_t>(gq + 8) * D + d0);
+      const uint32_t* r1 = reinterpret_cast<const uint32_t*>(qhi + d0);
       qa[ks][0] = gq < group ? __ldg(r0) : 0u;
-      qa[ks][1] = gq + 8 < group ? __ldg(r1) : 0u;
+      qa[ks][1] = hi_ok ? __ldg(r1) : 0u;
       qa[ks][2] = gq < group ? __ldg(r0 + 4) : 0u;
-      qa[ks][3] = gq + 8 < group ? __ldg(r1 + 4) : 0u;
+      qa[ks][3] = hi_ok ? __ldg(r1 + 4) : 0u;
     }
   }
 
@@ -191,7 +217,20 @@ paged_attn_decode_kernel(const __grid_constant__ CUtensorMap k_map,
       }
 
       const int tok0 = start + i * kPage + 2 * tq;  // token of s0[0]; s0[1] is +1, s1[*] is +8
-      if (start + i * kPage + kPage > L) {
+      if (PAIRS) {
+        // the two rows end at different tokens (a prompt's causal mask); the shorter one may even end before
+        // this page starts, then everything of it is masked here
+        if (start + i * kPage + kPage > min(L0, L1)) {
+          if (tok0 >= L0) s0[0] = -INFINITY;
+          if (tok0 + 1 >= L0) s0[1] = -INFINITY;
+          if (tok0 + 8 >= L0) s1[0] = -INFINITY;
+          if (tok0 + 9 >= L0) s1[1] = -INFINITY;
+          if (tok0 >= L1) s0[2] = -INFINITY;
+          if (tok0 + 1 >= L1) s0[3] = -INFINITY;
+          if (tok0 + 8 >= L1) s1[2] = -INFINITY;
+          if (tok0 + 9 >= L1) s1[3] = -INFINITY;
+        }
+      } else if (start + i * kPage + kPage > L) {
         if (tok0 >= L) s0[0] = s0[2] = -INFINITY;
         if (tok0 + 1 >= L) s0[1] = s0[3] = -INFINITY;
         if (tok0 + 8 >= L) s1[0] = s1[2] = -INFINITY;
@@ -202,9 +241,12 @@ paged_attn_decode_kernel(const __grid_constant__ CUtensorMap k_map,
       float mx0 = fmaxf(fmaxf(s0[0], s0[1]), fmaxf(s1[0], s1[1]));
       mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
       mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
-      const float mn0 = fmaxf(m0, mx0 * scale_log2);
+      // A PAIRS row that has seen nothing yet (everything masked so far) keeps m = -inf; its exponentials then
+      // take 0 as their reference point and come out 0 instead of NaN.
+      const float mnew0 = fmaxf(m0, mx0 * scale_log2);
+      const float mn0 = (PAIRS && mnew0 == -INFINITY) ? 0.f : mnew0;
       const float a0 = exp2f(m0 - mn0);
-      m0 = mn0;
+      m0 = mnew0;
       const float p00 = exp2f(s0[0] * scale_log2 - mn0), p01 = exp2f(s0[1] * scale_log2 - mn0);
       const float p10 = exp2f(s1[0] * scale_log2 - mn0), p11 = exp2f(s1[1] * scale_log2 - mn0);
       l0 = l0 * a0 + (p00 + p01) + (p10 + p11);
@@ -213,9 +255,10 @@ paged_attn_decode_kernel(const __grid_constant__ CUtensorMap k_map,
         float mx1 = fmaxf(fmaxf(s0[2], s0[3]), fmaxf(s1[2], s1[3]));
         mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
         mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
-        const float mn1 = fmaxf(m1, mx1 * scale_log2);
+        const float mnew1 = fmaxf(m1, mx1 * scale_log2);
+        const float mn1 = (PAIRS && mnew1 == -INFINITY) ? 0.f : mnew1;
         a1 = exp2f(m1 - mn1);
-        m1 = mn1;
+        m1 = mnew1;
         p02 = exp2f(s0[2] * scale_log2 - mn1);
         p03 = exp2f(s0[3] * scale_log2 - mn1);
         p12 = exp2f(s1[2] * scale_log2 - mn1);
@@ -256,6 +299,34 @@ paged_attn_decode_kernel(const __grid_constant__ CUtensorMap k_map,
   l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
   l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
   l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+
+  if (PAIRS) {
+    // each of the two rows has its own number of splits; a row takes part in this split only if it has tokens here
+    const int n0 = (L0 + split_tokens - 1) / split_tokens, n1 = (L1 + split_tokens - 1) / split_tokens;
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+      const int nr = half ? n1 : n0;
+      const bool ok = half ? hi_ok : gq < group;
+      if (!ok || split >= nr) continue;
+      const size_t qrow = (static_cast<size_t>(b + half) * num_q_heads + kvh * group + gq);
+      const float lr = half ? l1 : l0, mr = half ? m1 : m0;
+      if (nr == 1) {
+        const float inv = 1.f / lr;
+        __nv_bfloat16* od = out + qrow * D;
+#pragma unroll
+        for (int n = 0; n < D / 8; ++n)
+          *reinterpret_cast<uint32_t*>(od + n * 8 + 2 * tq) =
+              pack_bf16x2(o[n][2 * half] * inv, o[n][2 * half + 1] * inv);
+      } else {
+        const size_t prow = qrow * max_splits + split;
+#pragma unroll
+        for (int n = 0; n < D / 8; ++n)
+          *reinterpret_cast<float2*>(part_o + prow * D + n * 8 + 2 * tq) = make_float2(o[n][2 * half], o[n][2 * half + 1]);
+        if (tq == 0) part_ml[prow] = make_float2(mr, lr);
+      }
+    }
+    return;
+  }
 
   const int nsplits = (L + split_tokens - 1) / split_tokens;  // CTAs working on this sequence
   if (nsplits == 1) {
@@ -498,7 +569,7 @@ static AttnWorkspace carve(void* ws, int batch, int hq, int D, int max_splits) {
   return w;
 }
 
-template <int D, int HKV, int STAGES, int CTAS>
+template <int D, int HKV, int STAGES, int CTAS, bool PAIRS = false>
 static int launch_main(const void* q, const void* k_pool, const void* v_pool,
                        const int* block_table, const int* ctx_lens, void* out,
                        const AttnWorkspace& w, int batch, int hq, int num_blocks, int max_pages,
@@ -514,15 +585,16 @@ static int launch_main(const void* q, const void* k_pool, const void* v_pool,
   int dev = 0;
   B200_CUDA(cudaGetDevice(&dev));
   if (dev < 64 && !attr_done[dev]) {
-    B200_CUDA(cudaFuncSetAttribute(paged_attn_decode_kernel<D, HKV, STAGES, CTAS>,
+    B200_CUDA(cudaFuncSetAttribute(paged_attn_decode_kernel<D, HKV, STAGES, CTAS, PAIRS>,
                                    cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
     attr_done[dev] = true;
   }
-  dim3 grid(batch, max_splits);
+  dim3 grid(PAIRS ? (batch + 1) / 2 : batch, max_splits);
   const float scale_log2 = scale * 1.4426950408889634f;
-  paged_attn_decode_kernel<D, HKV, STAGES, CTAS><<<grid, Cfg::kThreads, Cfg::kSmemBytes, stream>>>(
+  paged_attn_decode_kernel<D, HKV, STAGES, CTAS, PAIRS><<<grid, Cfg::kThreads, Cfg::kSmemBytes, stream>>>(
       kmap, vmap, static_cast<const __nv_bfloat16*>(q), block_table, ctx_lens, w.o, w.ml,
-      static_cast<__nv_bfloat16*>(out), w.err, hq, num_blocks, max_pages, split_tokens, max_splits, scale_log2);
+      static_cast<__nv_bfloat16*>(out), w.err, batch, hq, num_blocks, max_pages, split_tokens, max_splits,
+      scale_log2);
   B200_CUDA(cudaGetLastError());
   if (max_splits > 1) {
     const int rows = batch * hq;
@@ -623,6 +695,45 @@ extern "C" int b200_paged_attn_decode(const void* q, const void* k_pool, const v
         num_q_heads, num_kv_heads, head_dim, page_size, num_blocks, max_pages_per_seq, scale);
   B200_CUDA(cudaGetLastError());
   return 0;
+}
+
+/* Prompt form: rows 2i and 2i+1 are two consecutive tokens of one sequence and share block_table row 2i. */
+extern "C" int b200_paged_attn_decode_pairs(const void* q, const void* k_pool, const void* v_pool,
+                                            const int32_t* block_table, const int32_t* ctx_lens, void* out,
+                                            void* workspace, size_t workspace_bytes, int batch, int num_q_heads,
+                                            int num_kv_heads, int head_dim, int page_size, int num_blocks,
+                                            int max_pages_per_seq, float scale, int split_tokens, void* stream) {
+  B200_REQUIRE(q && k_pool && v_pool && block_table && ctx_lens && out && workspace,
+               "paged_attn_decode_pairs: null pointer");
+  B200_REQUIRE(batch > 0 && num_q_heads > 0 && num_kv_heads > 0 && num_blocks > 0 && max_pages_per_seq > 0,
+               "paged_attn_decode_pairs: non-positive dimension");
+  B200_REQUIRE(num_q_heads % num_kv_heads == 0 && num_q_heads / num_kv_heads <= 8,
+               "paged_attn_decode_pairs: %d query heads per kv head (at most 8: the second row uses the upper half "
+               "of the MMA tile)", num_kv_heads ? num_q_heads / num_kv_heads : 0);
+  B200_REQUIRE(page_size == kPage && split_tokens > 0 && split_tokens % kPage == 0,
+               "paged_attn_decode_pairs: page_size %d must be %d and split_tokens %d a multiple of it", page_size, kPage,
+               split_tokens);
+  B200_REQUIRE((head_dim == 128 && num_kv_heads == 4) || (head_dim == 64 && num_kv_heads == 2),
+               "paged_attn_decode_pairs: built for head_dim 128 with 4 kv heads and head_dim 64 with 2 kv heads, got "
+               "%d / %d", head_dim, num_kv_heads);
+  B200_REQUIRE((reinterpret_cast<uintptr_t>(k_pool) & 15) == 0 && (reinterpret_cast<uintptr_t>(v_pool) & 15) == 0 &&
+                   (reinterpret_cast<uintptr_t>(q) & 3) == 0,
+               "paged_attn_decode_pairs: pools must be 16-byte aligned");
+  int rc = check_device(nullptr);
+  if (rc) return rc;
+  const int ms = max_splits_of(max_pages_per_seq, page_size, split_tokens);
+  B200_REQUIRE(ms <= 65535, "paged_attn_decode_pairs: grid too large");
+  AttnWorkspace w = carve(workspace, batch, num_q_heads, head_dim, ms);
+  if (workspace_bytes < w.bytes) {
+    set_detail("paged_attn_decode_pairs: workspace %zu < required %zu", workspace_bytes, w.bytes);
+    return -kErrWorkspace;
+  }
+  cudaStream_t st = as_stream(stream);
+  if (head_dim == 128)
+    return launch_main<128, 4, 3, 2, true>(q, k_pool, v_pool, block_table, ctx_lens, out, w, batch, num_q_heads,
+                                           num_blocks, max_pages_per_seq, scale, split_tokens, ms, st);
+  return launch_main<64, 2, 6, 4, true>(q, k_pool, v_pool, block_table, ctx_lens, out, w, batch, num_q_heads,
+                                        num_blocks, max_pages_per_seq, scale, split_tokens, ms, st);
 }
 
 extern "C" int b200_kv_append(const void* k_new, const void* v_new, void* k_pool, void* v_pool,

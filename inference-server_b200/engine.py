@@ -217,7 +217,7 @@ class DecodeEngine:
             self.kernel_launches_per_step += cfg.layers * (3 + (2 if ep_transport == "p2p" else 0))
 
     # ------------------------------------------------------------------ step
-    def _forward(self, tokens, pos, table, attn_ws, moe_ws, split_tokens, ep: bool) -> torch.Tensor:
+    def _forward(self, tokens, pos, table, attn_ws, moe_ws, split_tokens, ep: bool, pairs: bool = False) -> torch.Tensor:
         """The layer stack for R rows: row i is token `tokens[i]` at position `pos[i]` of the sequence whose
         pages are `table[i]`; it attends to positions 0..pos[i].  Decode passes one row per sequence; a prompt
         chunk passes one row per prompt token with the sequence's table repeated - the same kernels, reading
@@ -237,7 +237,7 @@ class DecodeEngine:
             q = ops.qk_norm_rope_append(qkv, w.q_norm, w.k_norm, self.cos, self.sin, pos, table, self.k_pools[li],
                                         self.v_pools[li], Hq, cfg.rms_eps, attn_ws)
             attn = ops.paged_attn_decode(q, self.k_pools[li], self.v_pools[li], table, new_len, self.scale,
-                                         split_tokens, attn_ws)
+                                         split_tokens, attn_ws, pairs=pairs)
             o = torch.matmul(attn.view(R, Hq * D), w.wo.t())
             h2 = ops.add_rmsnorm(x, o, w.ln2, cfg.rms_eps)
             logits = torch.matmul(h2, w.router.t())  # bf16, routed as is
@@ -305,7 +305,8 @@ class DecodeEngine:
 
         Runs the same paged kernels as decode, in chunks of `chunk` prompt tokens: every token of a chunk is a
         row with its own position, all rows share the sequence's block table, and attention reads the pages in
-        place (cached prefix pages included) - there is no dense gather of the KV.  This replaces the
+        place (cached prefix pages included, two rows per CTA: b200_paged_attn_decode_pairs) - there is no dense
+        gather of the KV.  This replaces the
         reference's page gather for cache hits (src/inference_server/kv_cache/hf_format.py:21-45).  The K/V
         of a whole chunk are written to their page slots before the chunk's attention runs, and row i only
         looks at positions <= its own, which is the causal mask.
@@ -329,6 +330,8 @@ class DecodeEngine:
                                                              self._prefill_split, self.device)
             self._prefill_moe_ws = ops.moe_fp8_workspace(chunk, cfg.experts, cfg.top_k, cfg.hidden, cfg.moe_inter,
                                                          self.device)
+        # consecutive prompt tokens share the table, so attention takes them two rows per CTA where it can
+        pairs = ops.paged_attn_pairs_supported(cfg.q_heads, cfg.kv_heads, cfg.head_dim, PAGE, torch.bfloat16)
         row = torch.zeros(self.max_pages, dtype=torch.int32)
         row[: len(block_ids)] = torch.tensor(block_ids, dtype=torch.int32)
         row = row.to(self.device)
@@ -339,7 +342,7 @@ class DecodeEngine:
             pos = torch.arange(lo, hi, device=self.device, dtype=torch.int32)
             table = row.unsqueeze(0).expand(hi - lo, -1).contiguous()
             h = self._forward(tokens, pos, table, self._prefill_attn_ws, self._prefill_moe_ws, self._prefill_split,
-                              False)
+                              False, pairs=pairs)
             h_last = h[-1:]
         logits = torch.matmul(h_last, self.lm_head.t())[0]
         return int(logits.argmax()), logits

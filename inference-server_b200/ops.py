@@ -75,11 +75,14 @@ def paged_attn_decode(
     split_tokens: int | None = None,
     workspace: torch.Tensor | None = None,
     out: torch.Tensor | None = None,
+    pairs: bool = False,
 ) -> torch.Tensor:
     """softmax(q K^T * scale) V over the pages listed in `block_table`.
 
     q [B, Hq, D]; pools [num_blocks, Hkv, page, D] (the reference BlockManager
     layout); block_table [B, max_pages] int32; ctx_lens [B] int32.
+    `pairs`: rows 2i and 2i+1 are consecutive tokens of one sequence and share table row 2i (a prompt chunk);
+    every page is then fetched once for the two rows.  See `paged_attn_pairs_supported`.
     """
     _need(q, "q")
     _need(k_pool, "k_pool", q.dtype)
@@ -101,6 +104,14 @@ def paged_attn_decode(
         workspace = paged_attn_workspace(B, Hq, D, max_pages, page, split_tokens, q.device)
     if out is None:
         out = torch.empty_like(q)
+    if pairs:
+        rc = _lib.load().b200_paged_attn_decode_pairs(
+            _ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(block_table), _ptr(ctx_lens), _ptr(out),
+            _ptr(workspace), workspace.numel(), B, Hq, Hkv, D, page, nb, max_pages, float(scale),
+            int(split_tokens), _stream(),
+        )
+        check(rc, "b200_paged_attn_decode_pairs")
+        return out
     rc = _lib.load().b200_paged_attn_decode(
         _ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(block_table), _ptr(ctx_lens), _ptr(out),
         _ptr(workspace), workspace.numel(), B, Hq, Hkv, D, page, nb, max_pages, float(scale),
@@ -108,6 +119,12 @@ def paged_attn_decode(
     )
     check(rc, "b200_paged_attn_decode")
     return out
+
+
+def paged_attn_pairs_supported(num_q_heads: int, num_kv_heads: int, head_dim: int, page_size: int, dtype) -> bool:
+    """Whether b200_paged_attn_decode_pairs is built for this shape."""
+    return (dtype == torch.bfloat16 and page_size == 16 and num_q_heads % num_kv_heads == 0
+            and num_q_heads // num_kv_heads <= 8 and (head_dim, num_kv_heads) in ((128, 4), (64, 2)))
 
 
 def kv_append(k_new, v_new, k_pool, v_pool, block_table, positions, status: torch.Tensor | None = None):

@@ -165,3 +165,34 @@ def test_host_side_argument_errors(ops):
     tiny = torch.zeros(8, dtype=torch.uint8, device=dev)
     with pytest.raises(Exception, match="workspace"):
         ops.paged_attn_decode(q.to(dev), kp.to(dev), vp.to(dev), table.to(dev), ctx.to(dev), 0.1, split_tokens=64, workspace=tiny)
+
+
+@pytest.mark.parametrize("Hq,Hkv,D", [(32, 4, 128), (8, 2, 64), (16, 4, 128)])
+@pytest.mark.parametrize("split", [64, 256])
+def test_pair_form_gives_the_same_bits_as_one_row_per_cta(ops, Hq, Hkv, D, split):
+    """b200_paged_attn_decode_pairs: rows 2i and 2i+1 share table row 2i and are computed by one CTA (the second
+    row in the upper half of the MMA tile).  Every row must come out bit-identical to the one-row kernel: a
+    prompt's consecutive lengths, equal lengths, a second row that starts in a later split than the first
+    ends, empty rows, and an odd row count."""
+    lens_pairs = [(1, 2), (15, 16), (16, 17), (63, 64), (64, 65), (200, 201), (300, 300), (7, 500), (500, 7),
+                  (0, 40), (40, 0), (0, 0), (129, 130), (511, 512)]
+    lens = [l for pr in lens_pairs for l in pr] + [333]  # odd count: the last pair has one row
+    B = len(lens)
+    share = [max(lens[2 * (i // 2)], lens[min(B - 1, 2 * (i // 2) + 1)]) for i in range(B)]
+    q, kp, vp, table, ctx = build_case(B, Hq, Hkv, D, share, seed=B + Hq)  # pages for the longer row of a pair
+    for i in range(1, B, 2):
+        table[i] = table[i - 1]  # the pair shares the first row's table
+    ctx = torch.tensor(lens, dtype=torch.int32)
+    dev = "cuda"
+    q, kp, vp, table, ctx = [t.to(dev) for t in (q, kp, vp, table, ctx)]
+    ws = ops.paged_attn_workspace(B, Hq, D, table.shape[1], 16, split, dev)
+    one = ops.paged_attn_decode(q, kp, vp, table, ctx, D ** -0.5, split, ws).clone()
+    ops.read_status(ws, "one row per CTA")
+    ws2 = ops.paged_attn_workspace(B, Hq, D, table.shape[1], 16, split, dev)
+    scrambled = table.clone()
+    scrambled[1::2] = 0  # odd table rows are not read by the pair form
+    two = ops.paged_attn_decode(q, kp, vp, scrambled, ctx, D ** -0.5, split, ws2, pairs=True)
+    ops.read_status(ws2, "pairs")
+    assert torch.equal(one, two), f"rows differ: {(one != two).flatten(1).any(1).nonzero().flatten().tolist()}"
+    assert ops.paged_attn_pairs_supported(Hq, Hkv, D, 16, torch.bfloat16)
+    assert not ops.paged_attn_pairs_supported(64, 4, 128, 16, torch.bfloat16)  # 16 heads per kv head: no idle rows
