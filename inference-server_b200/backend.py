@@ -107,6 +107,7 @@ class B200Backend:
                              f"[num_blocks, {want[0]}, {want[1]}, {want[2]}] per layer, block_size 16)")
         eng.k_pools, eng.v_pools = bm.k_pools, bm.v_pools
         eng.num_blocks = bm.total_blocks
+        eng.scratch_block = None  # the manager's pools have no spare page: graphs per exact batch size
         eng._graphs.clear()
         self._alloc = None  # pages now come from the reference BlockManager
 

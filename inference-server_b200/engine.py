@@ -143,7 +143,7 @@ class DecodeEngine:
                  embed: torch.Tensor | None = None, lm_head: torch.Tensor | None = None,
                  final_norm: torch.Tensor | None = None, k_pools=None, v_pools=None, use_graphs: bool = True,
                  split_tokens: int | None = None, ep_group=None, ep_capacity: int | None = None,
-                 ep_transport: str = "p2p"):
+                 ep_transport: str = "p2p", graph_buckets: bool = True):
         if not torch.cuda.is_available():
             raise RuntimeError("DecodeEngine needs a CUDA device; this path has no CPU implementation")
         self.cfg = cfg
@@ -171,7 +171,12 @@ class DecodeEngine:
         self.lm_head = lm_head if lm_head is not None else (
             torch.randn(cfg.vocab_size, cfg.hidden, device=self.device, generator=gen) * std).to(bf)
         self.final_norm = final_norm if final_norm is not None else torch.ones(cfg.hidden, device=self.device, dtype=bf)
-        shape = (num_blocks, cfg.kv_heads, PAGE, cfg.head_dim)
+        # Pools the engine allocates itself get one block more than the caller may hand out: the scratch page
+        # that the padding rows of a bucketed CUDA graph write their K/V to (see step).  Pools given from outside
+        # (a reference BlockManager's) have no such page; graphs are then captured per exact batch size.
+        own_pools = k_pools is None and v_pools is None
+        self.scratch_block = num_blocks if (own_pools and graph_buckets and ep_group is None) else None
+        shape = (num_blocks + (1 if self.scratch_block is not None else 0), cfg.kv_heads, PAGE, cfg.head_dim)
         self.k_pools = k_pools if k_pools is not None else [torch.zeros(shape, device=self.device, dtype=bf) for _ in range(cfg.layers)]
         self.v_pools = v_pools if v_pools is not None else [torch.zeros(shape, device=self.device, dtype=bf) for _ in range(cfg.layers)]
         self.cos, self.sin = rope_tables(cfg.head_dim, cfg.rope_theta, max_pages_per_seq * PAGE, self.device, bf)
@@ -271,6 +276,18 @@ class DecodeEngine:
                                  lambda o, i: dist.all_to_all_single(o, i, group=st.group), residual=x,
                                  norm_weight=next_norm, eps=self.cfg.rms_eps)
 
+    GRAPH_BUCKETS = (1, 2, 4, 8, 16, 24, 32, 48, 64, 96, 128, 192, 256, 384, 512, 768, 1024)
+
+    def graph_batch(self, B: int) -> int:
+        """Rows the captured graph for a batch of B runs: B itself, or with a scratch page the next bucket, so
+        that a batch whose size changes with every admitted and finished request reuses a handful of graphs."""
+        if self.scratch_block is None:
+            return B
+        for b in self.GRAPH_BUCKETS:
+            if b >= B:
+                return min(b, self.max_batch)
+        return self.max_batch
+
     def step(self, B: int) -> torch.Tensor:
         """Run one decode step for the first B rows of the static state; returns next tokens (device)."""
         if B < 1 or B > self.max_batch:
@@ -278,6 +295,14 @@ class DecodeEngine:
         if not self.use_graphs:
             self._step_eager(B)
             return self.next_tokens[:B]
+        rows = self.graph_batch(B)
+        if rows > B:
+            # padding rows: token 0 at position 0 of a sequence whose only page is the scratch page; reset every
+            # step because the graph advances their lengths like everyone's
+            self.tokens[B:rows] = 0
+            self.ctx_lens[B:rows] = 0
+            self.block_table[B:rows, 0] = self.scratch_block
+        real, B = B, rows
         g = self._graphs.get(B)
         if g is None:
             saved = self.ctx_lens.clone()
@@ -286,6 +311,9 @@ class DecodeEngine:
             with torch.cuda.stream(stream):
                 for _ in range(2):  # warm-up: library handles, function attributes, tensor maps
                     self._step_eager(B)
+                    # every warm-up run writes the K/V slot of the CURRENT position only (the one the real step
+                    # will overwrite): a run that advanced could cross into a page the row does not own yet
+                    self.ctx_lens.copy_(saved)
             torch.cuda.current_stream().wait_stream(stream)
             torch.cuda.synchronize()
             g = torch.cuda.CUDAGraph()
@@ -295,7 +323,7 @@ class DecodeEngine:
             torch.cuda.synchronize()
             self._graphs[B] = g
         g.replay()
-        return self.next_tokens[:B]
+        return self.next_tokens[:real]
 
     # --------------------------------------------------------------- prefill
     @torch.no_grad()
