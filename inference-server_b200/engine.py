@@ -181,6 +181,7 @@ class DecodeEngine:
         self.v_pools = v_pools if v_pools is not None else [torch.zeros(shape, device=self.device, dtype=bf) for _ in range(cfg.layers)]
         self.cos, self.sin = rope_tables(cfg.head_dim, cfg.rope_theta, max_pages_per_seq * PAGE, self.device, bf)
         self.scale = cfg.head_dim ** -0.5
+        self._fixed_split = split_tokens
         self.split_tokens = split_tokens or ops.default_split_tokens(max_batch, cfg.kv_heads, max_pages_per_seq * PAGE)
 
         # static step state (read by the captured graphs)
@@ -192,6 +193,9 @@ class DecodeEngine:
                                                 self.split_tokens, self.device)
         self.moe_ws = ops.moe_fp8_workspace(max_batch, cfg.experts, cfg.top_k, cfg.hidden, cfg.moe_inter, self.device)
         self._graphs: dict[int, torch.cuda.CUDAGraph] = {}
+        # attention split size and workspace per graph size: few rows want short splits (enough CTAs to fill the
+        # GPU), a full batch long ones; the full batch's pair is (split_tokens, attn_ws)
+        self._attn_by_rows: dict[int, tuple[int, torch.Tensor]] = {max_batch: (self.split_tokens, self.attn_ws)}
         self.ep_state = None
         if self.ep_world > 1:
             from . import ep
@@ -255,10 +259,30 @@ class DecodeEngine:
                                         cfg.norm_topk_prob, moe_ws, residual=x, norm_weight=nxt, eps=cfg.rms_eps)
         return h
 
+    def _attn_for(self, rows: int) -> tuple[int, torch.Tensor]:
+        """(split_tokens, workspace) of the attention kernel for a step of `rows` rows."""
+        pair = self._attn_by_rows.get(rows)
+        if pair is None:
+            cfg = self.cfg
+            split = self._fixed_split or ops.default_split_tokens(rows, cfg.kv_heads, self.max_pages * PAGE)
+            pair = (split, ops.paged_attn_workspace(rows, cfg.q_heads, cfg.head_dim, self.max_pages, PAGE, split,
+                                                    self.device))
+            self._attn_by_rows[rows] = pair
+        return pair
+
+    def check_status(self, where: str = "decode engine") -> None:
+        """Synchronise and raise if any kernel of this engine has recorded a device-side finding."""
+        for rows, (_, ws) in self._attn_by_rows.items():
+            ops.read_status(ws, f"{where}: attention ({rows} rows)")
+        ops.read_status(self.moe_ws, f"{where}: MoE")
+        if self.ep_state is not None and getattr(self.ep_state, "arena", None) is not None:
+            ops.read_status(self.ep_state.status, f"{where}: peer-memory exchange")
+
     def _step_eager(self, B: int) -> None:
         """One decode step over rows [0, B) of the static buffers; advances ctx_lens by one."""
-        h = self._forward(self.tokens[:B], self.ctx_lens[:B], self.block_table[:B], self.attn_ws, self.moe_ws,
-                          self.split_tokens, self.ep_state is not None)
+        split, attn_ws = self._attn_for(B)
+        h = self._forward(self.tokens[:B], self.ctx_lens[:B], self.block_table[:B], attn_ws, self.moe_ws,
+                          split, self.ep_state is not None)
         self.last_logits = torch.matmul(h, self.lm_head.t())
         self.next_tokens[:B] = self.last_logits.argmax(dim=-1)
         self.ctx_lens[:B] += 1

@@ -46,12 +46,13 @@ def test_bucketed_graph_equals_exact_graph_and_keeps_off_foreign_pages(ops):
             e.tokens[:B].copy_(nxt)
             toks.append(nxt)
         torch.cuda.synchronize()
-        ops.read_status(e.attn_ws, name)
-        ops.read_status(e.moe_ws, name)
+        e.check_status(name)
         outs[name] = (torch.stack(toks), e.last_logits[:B].clone())
     assert torch.equal(outs["bucket"][0], outs["exact"][0])
     assert torch.equal(outs["bucket"][1], outs["exact"][1])
     assert a.ctx_lens[:B].tolist() == [17, 18, 32] and sorted(a._graphs) == [4] and sorted(b._graphs) == [3]
+    # few rows get their own (shorter) attention split and workspace; the full batch keeps the engine's
+    assert set(a._attn_by_rows) == {4, 8} and a._attn_by_rows[8][1] is a.attn_ws
     # pages of the real rows are identical in both engines; no other page changed - block 0 (what an unallocated
     # table entry points to) included; only the scratch page of the bucketed engine was written
     for li in range(a.cfg.layers):
