@@ -190,11 +190,16 @@ int b200_qk_norm_rope_append(const void* qkv, const void* q_norm_weight, const v
  *
  *   logits       [num_tokens, num_experts], logits_dtype B200_DTYPE_F32 or
  *                B200_DTYPE_BF16 (the router projection's own output type)
+ *   num_valid_rows  optional device int32: rows at or beyond it are padding of a
+ *                fixed-shape step and get expert id -1 ("no expert") and weight 0;
+ *                b200_moe_permute* leave such pairs out (row_of_pair -1) and the
+ *                combine kernels add nothing for them.  NULL: every row is real.
  *   topk_ids     [num_tokens, top_k] int32, value-descending
  *   topk_weights [num_tokens, top_k] fp32
  */
 int b200_moe_route(const void* logits, int logits_dtype, int num_tokens, int num_experts, int top_k,
-                   int renormalize, int32_t* topk_ids, float* topk_weights, void* stream);
+                   int renormalize, const int32_t* num_valid_rows, int32_t* topk_ids, float* topk_weights,
+                   void* stream);
 
 /*
  * Replaces: the sort-by-expert / offsets step of the grouped expert forward

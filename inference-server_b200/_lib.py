@@ -30,7 +30,7 @@ SIGNATURES = {
     "b200_kv_append": (c_int, [c_void_p] * 7 + [c_int] * 7 + [c_void_p]),
     "b200_add_rmsnorm": (c_int, [c_void_p, c_void_p, c_void_p, c_float, c_int, c_int, c_void_p, c_void_p]),
     "b200_qk_norm_rope_append": (c_int, [c_void_p] * 11 + [c_int] * 4 + [c_float] + [c_int] * 4 + [c_void_p]),
-    "b200_moe_route": (c_int, [c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p]),
+    "b200_moe_route": (c_int, [c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p]),
     "b200_moe_permute_workspace_bytes": (c_size_t, [c_int] * 3),
     "b200_moe_max_tiles": (c_int, [c_int] * 3),
     "b200_moe_permute": (

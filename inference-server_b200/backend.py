@@ -24,7 +24,11 @@ base.py:16-18) and owns bf16 pools of the right shape, the engine reads and
 writes those very pools (kv_cache/block_manager.py:33-49), prefix hits from
 ``lookup`` (kv_cache/cache_manager.py:41-80) are used in place as shared
 read-only pages, and prompts are registered with ``store`` (:82-127) exactly as
-TorchBackend does.  Without an adapter the backend keeps its own free list.
+TorchBackend does.  The manager may return a partially filled block in the middle
+of a hit (:60-70); the kernels need every page but the last to be full, so the
+leading full blocks are shared and the tokens from the first partial block on are
+copied, compacted, into private pages of the row (no recomputation).  Without an
+adapter the backend keeps its own free list.
 
 The module has no CPU path for the arithmetic: constructing the engine needs a
 CUDA device.  ``PagedBatch``/``SeqKV`` bookkeeping is plain Python and is what
@@ -89,6 +93,9 @@ class B200Backend:
         self.max_new_tokens = max_new_tokens
         self._table_cpu = None
         self._lens_cpu = None
+        self._synced_batch = None  # the PagedBatch whose table is on the device right now
+        self.status_check_every = 32  # decode steps between reads of the kernels' device status words
+        self._steps_since_check = 0
 
     # ------------------------------------------------------------ lifecycle
     def set_cache_adapter(self, adapter) -> None:
@@ -111,15 +118,75 @@ class B200Backend:
         eng._graphs.clear()
         self._alloc = None  # pages now come from the reference BlockManager
 
-    def load_model(self, model_name: str) -> None:
-        """Build a random-init engine of a named shape (no checkpoints are available offline)."""
-        from .engine import CONFIGS, DecodeEngine
+    def load_model(self, model_name: str, num_blocks: int = 4096, max_batch: int = 64,
+                   max_pages_per_seq: int = 256) -> None:
+        """Load a Qwen3-MoE checkpoint as TorchBackend.load_model does (torch_backend.py:33-53):
+        ``AutoModelForCausalLM.from_pretrained(model_name, dtype=bfloat16)``, EOS ids from the model
+        config; the weights are then converted to the engine's run-time formats (``engine_from_hf``: dense
+        weights bf16, experts e4m3 with 128x128 block scales - taken as stored when the checkpoint is FP8).
+        One of the built-in shape names (``engine.CONFIGS``) builds a random-init engine of that shape
+        instead, for benchmarks without a checkpoint.  Needs a CUDA device either way."""
+        from . import engine as eng_mod
 
-        if model_name not in CONFIGS:
-            raise ValueError(f"unknown model shape {model_name!r}; available: {sorted(CONFIGS)}")
-        cfg = CONFIGS[model_name]
-        self.engine = DecodeEngine(cfg, num_blocks=4096, max_batch=64, max_pages_per_seq=256)
+        if model_name in eng_mod.CONFIGS:
+            self.engine = eng_mod.DecodeEngine(eng_mod.CONFIGS[model_name], num_blocks=num_blocks, max_batch=max_batch,
+                                               max_pages_per_seq=max_pages_per_seq)
+        else:
+            model, self.tokenizer = self._read_checkpoint(model_name)
+            eos = model.config.eos_token_id
+            self._eos_ids = set(eos) if isinstance(eos, (list, tuple)) else ({eos} if eos is not None else set())
+            self.engine = self._engine_from_model(model, num_blocks, max_batch, max_pages_per_seq)
+            del model
         self._alloc = _FreeListAllocator(self.engine.num_blocks)
+        self._table_cpu = self._lens_cpu = self._synced_batch = None
+        if self.cache_adapter is not None:
+            self.set_cache_adapter(self.cache_adapter)
+
+    @staticmethod
+    def _read_checkpoint(model_name: str):
+        """(model on the host in bf16, tokenizer or None).  The tokenizer is optional here: the scheduler
+        path passes token ids, and a checkpoint directory without tokenizer files still serves them."""
+        from transformers import AutoModelForCausalLM, AutoTokenizer
+
+        try:
+            tok = AutoTokenizer.from_pretrained(model_name)
+            if tok.pad_token is None:
+                tok.pad_token = tok.eos_token
+        except Exception:
+            tok = None
+        model = AutoModelForCausalLM.from_pretrained(model_name, dtype=torch.bfloat16)
+        model.eval()
+        return model, tok
+
+    @staticmethod
+    def _engine_from_model(model, num_blocks: int, max_batch: int, max_pages_per_seq: int):
+        from . import engine as eng_mod
+
+        return eng_mod.engine_from_hf(model, num_blocks=num_blocks, max_batch=max_batch,
+                                      max_pages_per_seq=max_pages_per_seq)
+
+    def enable_expert_parallel_rounds(self, group=None, idle_sleep: float = 0.002) -> None:
+        """Data-parallel serving over an expert-parallel engine: every rank has its own scheduler and its own
+        requests, yet each MoE layer of a pass exchanges rows with all ranks, so the ranks must run their passes
+        in common rounds.  After this call every prompt chunk and decode step of this backend first agrees a
+        round with the other ranks (``ep.RoundGate``), and a background thread answers, with an idle pass, the
+        rounds that other ranks start while this one has nothing to run.  Collective: call it on every rank.
+        The thread and the serving calls exclude each other through ``_lock``, which the scheduler holds for
+        its whole tick (scheduler.py:184); direct callers of prefill / decode_step_batched must hold it too."""
+        from . import ep
+
+        if getattr(self.engine, "ep_state", None) is None:
+            raise ValueError("the engine is not expert-parallel")
+        self._round_keeper = ep.RoundKeeper(ep.RoundGate(group), self.engine.idle_pass, self._lock, idle_sleep).start()
+        self.engine.round_hook = self._round_keeper.work_round
+
+    def close(self) -> None:
+        """Leave the expert-parallel rounds (the other ranks are told at their next round)."""
+        keeper = getattr(self, "_round_keeper", None)
+        if keeper is not None:
+            keeper.close()
+            self.engine.round_hook = None
+            self._round_keeper = None
 
     def kv_shape_per_layer(self) -> list[tuple[int, int]]:
         cfg = self.engine.cfg
@@ -155,8 +222,12 @@ class B200Backend:
             ids = self._alloc.allocate(n)
             return ids, ids
         bm = self.cache_adapter.block_manager
+        # The manager evicts only from inside its own store() (cache_manager.py:93-98) and offers no public
+        # call for it, because the reference keeps live sequences outside the pool.  Here live sequences sit in
+        # pool pages, so room for them is made the way store() makes it: one unreferenced block at a time.
+        evict = getattr(self.cache_adapter, "_evict_one", None)
         while n > bm.free_blocks:
-            if not self.cache_adapter._evict_one():
+            if evict is None or not evict():
                 raise MemoryError(f"Requested {n} blocks but only {bm.free_blocks} available")
         blocks = bm.allocate(n)
         return [b.block_id for b in blocks], blocks
@@ -171,34 +242,81 @@ class B200Backend:
 
     # -------------------------------------------------------------- prefill
     def _lookup(self, token_ids: list[int], session_id: str):
-        """Prefix lookup as TorchBackend does (torch_backend.py:113-119), keeping only the
-        leading run of full pages: the kernels need every page but the last to be full."""
+        """Prefix lookup as TorchBackend does (torch_backend.py:113-119).
+
+        Returns (usable, shared_ids, tail, held): `usable` cached tokens can be skipped (always at least one
+        token is left to run, so a full hit recomputes only its last token); the leading full blocks that lie
+        wholly below `usable` are shared in place (`shared_ids`, still acquired); `tail` lists, for every
+        further usable token, the (block id, slot) that holds its K/V - these come from a partially filled
+        block in the middle of the hit or from the hit's last block, and the caller copies them into private
+        pages; `held` are the acquired blocks behind `tail`, to release once the copy is queued."""
         cache = self.cache_adapter
         if cache is None or not getattr(cache.block_manager, "k_pools", None):
-            return 0, []
+            return 0, [], [], []
         matched, blocks = cache.lookup(token_ids, session_id=session_id)
-        keep = []
+        usable = min(matched, len(token_ids) - 1)
+        shared, tail, held = [], [], []
+        pos, sharing = 0, True
         for blk in blocks:
-            if blk.num_tokens_stored != PAGE:
-                break
-            keep.append(blk)
-        for blk in blocks[len(keep):]:
-            blk.release()  # not used by this row
-        usable = min(len(keep) * PAGE, len(token_ids) - 1)  # always leave one token to run
-        usable -= usable % PAGE
-        for blk in keep[usable // PAGE:]:
-            blk.release()
-        return usable, [b.block_id for b in keep[: usable // PAGE]]
+            n = blk.num_tokens_stored
+            if sharing and n == PAGE and pos + PAGE <= usable:
+                shared.append(blk)
+            else:
+                sharing = False
+                take = max(0, min(n, usable - pos))
+                if take:
+                    tail += [(blk.block_id, s) for s in range(take)]
+                    held.append(blk)
+                else:
+                    blk.release()  # nothing of this block is used by the row
+            pos += n
+        return usable, [b.block_id for b in shared], tail, held
+
+    def _adopt_tail(self, kv: SeqKV, first_pos: int, tail: list, held: list) -> None:
+        """Copy the cached tokens listed in `tail` into the row's own pages at positions first_pos.. and let
+        go of the blocks they came from."""
+        try:
+            if tail:
+                dst = [(kv.block_ids[(first_pos + i) // PAGE], (first_pos + i) % PAGE) for i in range(len(tail))]
+                self.engine.copy_kv_tokens(tail, dst)
+        finally:
+            for blk in held:
+                blk.release()
+
+    def _release_shared(self, shared_ids: list[int]) -> None:
+        cache = self.cache_adapter
+        if cache is None:
+            return
+        for bid in shared_ids:
+            cache.block_manager.blocks[bid].release()
 
     def prefill(self, token_ids: list[int], session_id: str = "default"):
-        """(per_row_kv, first_token_id, kv_length), as base.py:57-61."""
-        matched, shared_ids = self._lookup(token_ids, session_id)
-        self.last_cache_hit_tokens = matched
+        """(per_row_kv, first_token_id, kv_length), as base.py:57-61.  Whatever raises on the way (a prompt
+        wider than the block table, no pages left, a device finding) leaves no page and no block reference
+        behind: the scheduler rejects the one request (scheduler.py:299-304) and carries on."""
         n = len(token_ids)
         total_pages = (n + self.max_new_tokens + PAGE - 1) // PAGE
-        ids, handles = self._take_pages(total_pages - len(shared_ids))
-        kv = SeqKV(block_ids=shared_ids + ids, ctx_len=n, private_blocks=handles)
-        first, _ = self.engine.prefill(token_ids, kv.block_ids, cached_tokens=matched)
+        if n == 0:
+            raise ValueError("prefill needs at least one token")
+        if total_pages > self.engine.max_pages:
+            raise ValueError(f"prompt of {n} tokens plus {self.max_new_tokens} reserved needs {total_pages} pages; "
+                             f"the block table is {self.engine.max_pages} wide")
+        matched, shared_ids, tail, held = self._lookup(token_ids, session_id)
+        self.last_cache_hit_tokens = matched
+        handles = []
+        try:
+            ids, handles = self._take_pages(total_pages - len(shared_ids))
+            kv = SeqKV(block_ids=shared_ids + ids, ctx_len=n, private_blocks=handles)
+            tail_blocks, held = held, []
+            self._adopt_tail(kv, len(shared_ids) * PAGE, tail, tail_blocks)
+            first, _ = self.engine.prefill(token_ids, kv.block_ids, cached_tokens=matched)
+            self._check_status("prefill")
+        except BaseException:
+            for blk in held:
+                blk.release()
+            self._give_back(handles)
+            self._release_shared(shared_ids)
+            raise
         self._store(token_ids, kv, matched, session_id)
         return kv, first, n
 
@@ -218,23 +336,45 @@ class B200Backend:
         cache.store(token_ids, per_layer, skip_tokens=matched, session_id=session_id)
 
     def prefill_lookup(self, token_ids: list[int], session_id: str = "default"):
-        matched, shared_ids = self._lookup(token_ids, session_id)
+        matched, shared_ids, tail, held = self._lookup(token_ids, session_id)
         self.last_cache_hit_tokens = matched
         if matched == 0:
             return None, 0
-        return SeqKV(block_ids=shared_ids, ctx_len=matched, reserve_tokens=len(token_ids)), matched
+        handles = []
+        try:
+            ids, handles = self._take_pages((matched + PAGE - 1) // PAGE - len(shared_ids))
+            kv = SeqKV(block_ids=shared_ids + ids, ctx_len=matched, private_blocks=handles,
+                       reserve_tokens=len(token_ids))
+            tail_blocks, held = held, []
+            self._adopt_tail(kv, len(shared_ids) * PAGE, tail, tail_blocks)
+        except BaseException:
+            for blk in held:
+                blk.release()
+            self._give_back(handles)
+            self._release_shared(shared_ids)
+            raise
+        return kv, matched
 
     def prefill_chunk(self, chunk_token_ids: list[int], partial_kv):
-        """Forward one chunk on top of partial_kv (base.py:71-78)."""
+        """Forward one chunk on top of partial_kv (base.py:71-78).  If the chunk cannot run, the pages taken
+        for it go back; the partial KV of the earlier chunks stays as it was."""
         kv = partial_kv if partial_kv is not None else SeqKV(block_ids=[], ctx_len=0)
         new_len = kv.ctx_len + len(chunk_token_ids)
-        need = (new_len + self.max_new_tokens + PAGE - 1) // PAGE - len(kv.block_ids)
-        ids, handles = self._take_pages(need)
+        total_pages = (new_len + self.max_new_tokens + PAGE - 1) // PAGE
+        if total_pages > self.engine.max_pages:
+            raise ValueError(f"{new_len} tokens plus {self.max_new_tokens} reserved need {total_pages} pages; "
+                             f"the block table is {self.engine.max_pages} wide")
+        ids, handles = self._take_pages(total_pages - len(kv.block_ids))
+        try:
+            # only the tokens past `cached_tokens` are embedded; the earlier ones are already pages
+            tokens = [0] * kv.ctx_len + list(chunk_token_ids)
+            last, _ = self.engine.prefill(tokens, kv.block_ids + ids, cached_tokens=kv.ctx_len)
+            self._check_status("prefill_chunk")
+        except BaseException:
+            self._give_back(handles)
+            raise
         kv.block_ids += ids
         kv.private_blocks += handles
-        # only the tokens past `cached_tokens` are embedded; the earlier ones are already pages
-        tokens = [0] * kv.ctx_len + list(chunk_token_ids)
-        last, _ = self.engine.prefill(tokens, kv.block_ids, cached_tokens=kv.ctx_len)
         kv.ctx_len = new_len
         return kv, last, new_len
 
@@ -279,7 +419,9 @@ class B200Backend:
         B = len(batch.rows)
         if B > eng.max_batch:
             raise ValueError(f"batch {B} exceeds the engine's max_batch {eng.max_batch}")
-        if batch.dirty or self._table_cpu is None:
+        # the device table belongs to the engine, not to a batch: a second live PagedBatch (generate_step with
+        # separate caches, generate_batch beside the scheduler's batch) must re-upload even when it is clean
+        if batch.dirty or self._table_cpu is None or self._synced_batch is None or self._synced_batch() is not batch:
             if self._table_cpu is None:
                 pin = torch.cuda.is_available()
                 self._table_cpu = torch.zeros(eng.max_batch, eng.max_pages, dtype=torch.int32, pin_memory=pin)
@@ -293,7 +435,15 @@ class B200Backend:
             eng.block_table.copy_(self._table_cpu, non_blocking=True)
             eng.ctx_lens.copy_(self._lens_cpu, non_blocking=True)
             batch.dirty = False
+            self._synced_batch = weakref.ref(batch)  # weak: a dropped batch must still give its pages back
         return B
+
+    def _check_status(self, where: str) -> None:
+        """Raise if a kernel recorded a finding (a block id outside the pool, a wait that ran out, an
+        expert-parallel capacity overflow): such a step produced tokens from clamped or skipped data."""
+        check = getattr(self.engine, "check_status", None)
+        if check is not None:
+            check(where)
 
     def decode_step_batched(self, current_tokens, batched_kv, attention_mask=None, position_ids=None):
         """One decode step for every row (base.py:89-99).  Returns (next_tokens [B] on the host, batched_kv)."""
@@ -312,6 +462,12 @@ class B200Backend:
         out = nxt.to("cpu")  # synchronises: the scheduler reads every row right away
         for row in batch.rows:
             row.ctx_len += 1
+        # The stream is idle after that read, so looking at the status words costs a few 4-byte copies; doing
+        # it every few steps keeps a silent device finding from producing more than that many wrong tokens.
+        self._steps_since_check += 1
+        if self._steps_since_check >= self.status_check_every:
+            self._steps_since_check = 0
+            self._check_status("decode_step_batched")
         return out, batch
 
     # ------------------------------------------- legacy whole-request entry points

@@ -28,29 +28,70 @@ int cuda_fail(cudaError_t e, const char* where) {
   return -kErrCuda;
 }
 
-int check_device(int* device_out) {
+// Per-device facts and per-(kernel, device) attribute calls, remembered under one mutex so that concurrent
+// first calls from several host threads neither race nor repeat the driver call.
+struct DeviceFacts {
+  int device, major, sm_count;
+};
+static std::mutex g_dev_mu;
+static std::vector<DeviceFacts> g_devices;
+struct KernelAttr {
+  const void* kernel;
+  int device, bytes;
+};
+static std::vector<KernelAttr> g_kernel_attrs;
+
+static int device_facts(DeviceFacts* out) {
   int dev = 0;
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess) return cuda_fail(e, "cudaGetDevice");
-  static int major_of[64];
-  static bool known[64] = {false};
-  int major = 0;
-  if (dev < 64 && known[dev]) {
-    major = major_of[dev];
-  } else {
-    e = cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev);
-    if (e != cudaSuccess) return cuda_fail(e, "cudaDeviceGetAttribute");
-    if (dev < 64) {
-      major_of[dev] = major;
-      known[dev] = true;
+  std::lock_guard<std::mutex> lock(g_dev_mu);
+  for (const DeviceFacts& f : g_devices)
+    if (f.device == dev) {
+      *out = f;
+      return 0;
     }
-  }
-  if (major != 10) {
-    set_detail("device %d has compute capability %d.x; this library is built for sm_100a only", dev,
-               major);
+  DeviceFacts f{dev, 0, 0};
+  e = cudaDeviceGetAttribute(&f.major, cudaDevAttrComputeCapabilityMajor, dev);
+  if (e != cudaSuccess) return cuda_fail(e, "cudaDeviceGetAttribute(major)");
+  e = cudaDeviceGetAttribute(&f.sm_count, cudaDevAttrMultiProcessorCount, dev);
+  if (e != cudaSuccess) return cuda_fail(e, "cudaDeviceGetAttribute(sm count)");
+  g_devices.push_back(f);
+  *out = f;
+  return 0;
+}
+
+int check_device(int* device_out) {
+  DeviceFacts f;
+  int rc = device_facts(&f);
+  if (rc) return rc;
+  if (f.major != 10) {
+    set_detail("device %d has compute capability %d.x; this library is built for sm_100a only", f.device,
+               f.major);
     return -kErrUnsupported;
   }
-  if (device_out) *device_out = dev;
+  if (device_out) *device_out = f.device;
+  return 0;
+}
+
+int device_sm_count(int* out) {
+  DeviceFacts f;
+  int rc = device_facts(&f);
+  if (rc) return rc;
+  *out = f.sm_count > 0 ? f.sm_count : 148;
+  return 0;
+}
+
+int ensure_dynamic_smem(const void* kernel, int bytes) {
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return cuda_fail(e, "cudaGetDevice");
+  std::lock_guard<std::mutex> lock(g_dev_mu);
+  for (const KernelAttr& a : g_kernel_attrs)
+    if (a.kernel == kernel && a.device == dev && a.bytes >= bytes) return 0;
+  e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+  if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute(max dynamic shared memory)");
+  g_kernel_attrs.push_back(KernelAttr{kernel, dev, bytes});
   return 0;
 }
 

@@ -14,6 +14,13 @@ namespace b200 {
 // Returns 0 when the current device is sm_100-class, else a negative error.
 int check_device(int* device_out);
 
+// Raises a kernel's dynamic shared-memory limit to `bytes` once per (kernel, device); later calls for the same
+// pair only look the pair up.  Safe to call from several host threads.  Returns 0 or a negative error code.
+int ensure_dynamic_smem(const void* kernel, int bytes);
+
+// Multiprocessor count of the current device (cached per device, thread-safe).
+int device_sm_count(int* out);
+
 // Looks up (or encodes and caches) a 2-D row-major tensor map:
 //   rows x cols elements of `elem_bytes` (1 = uint8, 2 = bf16), row pitch =
 //   cols * elem_bytes, box = box_rows x box_cols, 128-byte swizzle.

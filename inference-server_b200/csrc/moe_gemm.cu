@@ -53,18 +53,6 @@ constexpr int kGemmSmem = kGemmStages * kStageBytesG + 1024 /* align */ + 128 /*
 
 enum : int { kModeGateUp = 0, kModeDown = 1 };
 
-// Optional timeline trace for tuning: compiled in only with -DB200_GEMM_TRACE.
-#ifdef B200_GEMM_TRACE
-__device__ long long* g_gemm_trace = nullptr;  // [role 0..3][4096] clock64 stamps of CTA 0
-#define B200_TRACE(role, idx)                                                         \
-  do {                                                                                \
-    if (blockIdx.x == 0 && g_gemm_trace != nullptr && (idx) < 4096)                   \
-      g_gemm_trace[(role) * 4096 + (idx)] = clock64();                                \
-  } while (0)
-#else
-#define B200_TRACE(role, idx) do { } while (0)
-#endif
-
 struct GemmParams {
   const float* a_scale;  // [rows, k_blocks]
   const float* b_scale;  // [E, n_rows / 128, k_blocks]
@@ -86,7 +74,17 @@ struct GemmParams {
   __nv_bfloat16* y_peers[kMaxEpWorld];
   int peer_capacity;
   int my_rank;
+  // bounds the tile list is checked against: a stale or foreign list must not steer a load or a store
+  int num_rows, num_experts, max_tiles;
 };
+
+// A tile record is usable when it names an existing expert and rows inside the activation matrix.  All three
+// roles of the kernel evaluate this on the same record and skip the same tiles, so their ring and accumulator
+// counters stay in step.
+__device__ __forceinline__ bool tile_ok(const MoeTile& t, const GemmParams& p) {
+  return t.expert >= 0 && t.expert < p.num_experts && t.rows > 0 && t.rows <= kTileM && t.row0 >= 0 &&
+         t.row0 + t.rows <= p.num_rows;
+}
 
 template <int MODE>
 __global__ void __launch_bounds__(kGemmThreads, 1)
@@ -124,7 +122,12 @@ moe_fp8_gemm_kernel(const __grid_constant__ CUtensorMap a_map,
   tc_fence_after();
   const uint32_t tmem_base = *tmem_base_sm;
 
-  const int total = (*p.num_tiles) * p.n_tiles;
+  int listed = *p.num_tiles;
+  if (listed < 0 || listed > p.max_tiles) {
+    if (threadIdx.x == 0) set_error(p.err, kErrDevBadExpert);
+    listed = listed < 0 ? 0 : p.max_tiles;
+  }
+  const int total = listed * p.n_tiles;
 
   if (warp < 4) {
   asm volatile("setmaxnreg.dec.sync.aligned.u32 40;");
@@ -137,6 +140,10 @@ moe_fp8_gemm_kernel(const __grid_constant__ CUtensorMap a_map,
       bool alive = true;
       for (int w = blockIdx.x; w < total && alive; w += gridDim.x) {
         const MoeTile tile = p.tiles[w / p.n_tiles];
+        if (!tile_ok(tile, p)) {
+          set_error(p.err, kErrDevBadExpert);
+          continue;
+        }
         const int j = w % p.n_tiles;
         // the two 128-row blocks of W this tile multiplies with: block index inside the expert
         int nb0, nb1;
@@ -156,7 +163,6 @@ moe_fp8_gemm_kernel(const __grid_constant__ CUtensorMap a_map,
           const uint32_t slot = it % kGemmStages, phase = (it / kGemmStages) & 1;
           alive = mbar_wait(bar_empty + 8 * slot, phase ^ 1, p.err);
           if (!alive) break;
-          B200_TRACE(0, it);
           const uint32_t sa = ring + slot * kStageBytesG, sb = sa + kABytes;
           mbar_arrive_expect_tx(bar_full + 8 * slot, kStageBytesG);
           tma_load_2d(sa, &a_map, bar_full + 8 * slot, kb * kBlockK, tile.row0);
@@ -173,14 +179,13 @@ moe_fp8_gemm_kernel(const __grid_constant__ CUtensorMap a_map,
       uint32_t it = 0;
       bool alive = true;
       for (int w = blockIdx.x; w < total && alive; w += gridDim.x) {
+        if (!tile_ok(p.tiles[w / p.n_tiles], p)) continue;
         for (int kb = 0; kb < p.k_blocks; ++kb, ++it) {
           const uint32_t slot = it % kGemmStages, phase = (it / kGemmStages) & 1;
           const uint32_t buf = it & 1, aphase = (it >> 1) & 1;
           alive = mbar_wait(bar_full + 8 * slot, phase, p.err);
-          B200_TRACE(1, 2 * it);
           alive = alive && mbar_wait(bar_tempty + 8 * buf, aphase ^ 1, p.err);
           if (!alive) break;
-          B200_TRACE(1, 2 * it + 1);
           tc_fence_after();
           const uint32_t sa = ring + slot * kStageBytesG, sb = sa + kABytes;
           const uint64_t a_desc = umma_desc_k128(sa), b_desc = umma_desc_k128(sb);
@@ -203,8 +208,9 @@ moe_fp8_gemm_kernel(const __grid_constant__ CUtensorMap a_map,
     const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
     uint32_t it = 0, tile_it = 0;
     bool alive = true;
-    for (int w = blockIdx.x; w < total && alive; w += gridDim.x, ++tile_it) {
+    for (int w = blockIdx.x; w < total && alive; w += gridDim.x) {
       const MoeTile tile = p.tiles[w / p.n_tiles];
+      if (!tile_ok(tile, p)) continue;
       const int j = w % p.n_tiles;
       const bool row_ok = r < tile.rows;
       const size_t grow = static_cast<size_t>(tile.row0) + r;
@@ -228,7 +234,6 @@ moe_fp8_gemm_kernel(const __grid_constant__ CUtensorMap a_map,
         const float s0 = sa * __ldg(bs0 + kb), s1 = sa * __ldg(bs1 + kb);
         alive = mbar_wait(bar_tfull + 8 * buf, aphase, p.err);
         if (!alive) break;
-        if (threadIdx.x == 128) B200_TRACE(2, 2 * it);
         tc_fence_after();
         const uint32_t t0 = lane_addr + buf * kTileN;
 #pragma unroll
@@ -268,10 +273,8 @@ moe_fp8_gemm_kernel(const __grid_constant__ CUtensorMap a_map,
             acc[c * 32 + 32 + i + 1] = r1.y;
           }
         }
-        if (threadIdx.x == 128) B200_TRACE(2, 2 * it + 1);
       }
       if (!alive) break;
-      if (threadIdx.x == 128) B200_TRACE(3, 4 * tile_it);
 
       if (MODE == kModeGateUp) {
         // acc[0..63] = gate, acc[64..127] = up for inter columns j*128 + half*64 + i
@@ -287,7 +290,6 @@ moe_fp8_gemm_kernel(const __grid_constant__ CUtensorMap a_map,
           acc[i] = h;
           amax = fmaxf(amax, fabsf(h));
         }
-        if (threadIdx.x == 128) B200_TRACE(3, 4 * tile_it + 1);
         float* ax = amax_sm + (tile_it & 1) * 2 * kTileM;
         ax[half * kTileM + r] = amax;
         // The partner thread (same row, other column half) holds the rest of the
@@ -298,7 +300,6 @@ moe_fp8_gemm_kernel(const __grid_constant__ CUtensorMap a_map,
         if (lane == 0) mbar_arrive(bar_amax + 8 * (tile_it & 1));
         alive = mbar_wait(bar_amax + 8 * (tile_it & 1), (tile_it >> 1) & 1, p.err);
         if (!alive) break;
-        if (threadIdx.x == 128) B200_TRACE(3, 4 * tile_it + 2);
         amax = fmaxf(amax, ax[(half ^ 1) * kTileM + r]);
         const float s = amax > 0.f ? amax / 448.f : 1.f;
         const float inv_s = 1.f / s;
@@ -341,7 +342,7 @@ moe_fp8_gemm_kernel(const __grid_constant__ CUtensorMap a_map,
           }
         }
       }
-      if (threadIdx.x == 128) B200_TRACE(3, 4 * tile_it + 3);
+      ++tile_it;
     }
   }
 
@@ -357,17 +358,11 @@ moe_fp8_gemm_kernel(const __grid_constant__ CUtensorMap a_map,
 template <int MODE>
 static int launch_gemm(const CUtensorMap& a_map, const CUtensorMap& b_map, const GemmParams& p,
                        cudaStream_t st) {
-  int dev = 0;
-  B200_CUDA(cudaGetDevice(&dev));
-  static bool attr_done[64] = {false};
-  static int sm_count[64] = {0};
-  if (dev < 64 && !attr_done[dev]) {
-    B200_CUDA(cudaFuncSetAttribute(moe_fp8_gemm_kernel<MODE>,
-                                   cudaFuncAttributeMaxDynamicSharedMemorySize, kGemmSmem));
-    B200_CUDA(cudaDeviceGetAttribute(&sm_count[dev], cudaDevAttrMultiProcessorCount, dev));
-    attr_done[dev] = true;
-  }
-  const int grid = dev < 64 && sm_count[dev] > 0 ? sm_count[dev] : 148;
+  int rc = ensure_dynamic_smem(reinterpret_cast<const void*>(&moe_fp8_gemm_kernel<MODE>), kGemmSmem);
+  if (rc) return rc;
+  int grid = 148;
+  rc = device_sm_count(&grid);
+  if (rc) return rc;
   moe_fp8_gemm_kernel<MODE><<<grid, kGemmThreads, kGemmSmem, st>>>(a_map, b_map, p);
   B200_CUDA(cudaGetLastError());
   return 0;
@@ -376,13 +371,6 @@ static int launch_gemm(const CUtensorMap& a_map, const CUtensorMap& b_map, const
 }  // namespace b200
 
 using namespace b200;
-
-#ifdef B200_GEMM_TRACE
-extern "C" int b200_set_gemm_trace(void* buf) {
-  long long* p = static_cast<long long*>(buf);
-  return cudaMemcpyToSymbol(b200::g_gemm_trace, &p, sizeof(p)) == cudaSuccess ? 0 : -4;
-}
-#endif
 
 static int aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 
@@ -424,6 +412,9 @@ extern "C" int b200_moe_fp8_gemm_gate_up(const void* xq, const float* x_scale, c
   p.inter = inter;
   p.n_tiles = inter / 128;
   p.tiled = weight_layout;
+  p.num_rows = num_rows;
+  p.num_experts = num_experts;
+  p.max_tiles = (num_rows + kTileM - 1) / kTileM + num_experts;
   return launch_gemm<kModeGateUp>(a_map, b_map, p, as_stream(stream));
 }
 
@@ -465,6 +456,9 @@ static int gemm_down_impl(const void* hq, const float* h_scale, const void* w2, 
   p.inter = inter;
   p.n_tiles = hidden / kTileN;
   p.tiled = weight_layout;
+  p.num_rows = num_rows;
+  p.num_experts = num_experts;
+  p.max_tiles = (num_rows + kTileM - 1) / kTileM + num_experts;
   if (y_peers != nullptr) {
     B200_REQUIRE(ep_world >= 1 && ep_world <= kMaxEpWorld && ep_capacity > 0 && ep_rank >= 0 && ep_rank < ep_world &&
                      out_row_map != nullptr,

@@ -87,7 +87,7 @@ static int moe_forward_impl(const void* x, const void* router_logits, int logits
   void* status = ws;
   const int rows = num_tokens * top_k;
 
-  int rc = b200_moe_route(router_logits, logits_dtype, num_tokens, num_experts, top_k, renormalize,
+  int rc = b200_moe_route(router_logits, logits_dtype, num_tokens, num_experts, top_k, renormalize, nullptr,
                           topk_ids, topk_w, stream);
   if (rc) return rc;
   rc = b200_moe_permute_quant(topk_ids, x, num_tokens, num_experts, top_k, hidden, sorted_pair, row_of_pair,

@@ -7,7 +7,10 @@
 //            value descending, equal values by lower expert id; weights are the
 //            selected probabilities, renormalised to sum to 1 when `renorm`.
 //            Selection compares the logits themselves (softmax is monotone), so
-//            expert ids do not depend on how exp() rounds.
+//            expert ids do not depend on how exp() rounds.  Rows at or beyond an
+//            optional device-side row count get expert id -1 ("no expert") and
+//            weight 0: the permutation leaves such pairs out and the combine adds
+//            nothing for them (padding rows of a fixed-shape step).
 //   permute  the T*K (token, slot) pairs, numbered token-major, are stably
 //            sorted by expert id: rows of one expert are contiguous and keep
 //            ascending pair order.
@@ -31,10 +34,17 @@ __device__ __forceinline__ float logit_f32(const __nv_bfloat16* p, size_t i) { r
 template <typename LT>
 __global__ void __launch_bounds__(kRouteWarps * 32)
 moe_route_kernel(const LT* __restrict__ logits, int T, int E, int K, int renorm,
-                 int* __restrict__ topk_ids, float* __restrict__ topk_w) {
+                 const int* __restrict__ num_valid, int* __restrict__ topk_ids, float* __restrict__ topk_w) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int t = blockIdx.x * kRouteWarps + warp;
   if (t >= T) return;
+  if (num_valid != nullptr && t >= *num_valid) {
+    if (lane < K) {
+      topk_ids[static_cast<size_t>(t) * K + lane] = -1;
+      topk_w[static_cast<size_t>(t) * K + lane] = 0.f;
+    }
+    return;
+  }
   float v[kRouteMaxPerLane];
   float mx = -INFINITY;
 #pragma unroll
@@ -160,7 +170,8 @@ moe_scatter_kernel(const int* __restrict__ topk_ids, const int* __restrict__ ran
   if (i < n_pairs) {
     const int e = topk_ids[i];
     if (e < 0 || e >= E) {
-      set_error(err, kErrDevBadExpert);
+      if (e != -1) set_error(err, kErrDevBadExpert);  // -1 is "no expert": the pair is left out, not an error
+      row_of_pair[i] = -1;
     } else {
       const int dst = off[e] + rank[i];
       sorted_pair[dst] = i;
@@ -343,7 +354,9 @@ __global__ void moe_scatter_quant_kernel(const __nv_bfloat16* __restrict__ x, co
     const int e = topk_ids[pair];
     int d = -1;
     if (e < 0 || e >= E) {
-      set_error(err, kErrDevBadExpert);
+      if (e != -1) set_error(err, kErrDevBadExpert);  // -1 is "no expert": the pair is left out, not an error
+      row_of_pair[pair] = -1;
+      if (slot_of_pair != nullptr) slot_of_pair[pair] = -1;
     } else {
       d = off[e] + rank[pair];
       sorted_pair[d] = pair;
@@ -501,8 +514,8 @@ __global__ void moe_combine_add_rmsnorm_kernel(const __nv_bfloat16* __restrict__
 using namespace b200;
 
 extern "C" int b200_moe_route(const void* logits, int logits_dtype, int num_tokens, int num_experts,
-                              int top_k, int renormalize, int32_t* topk_ids, float* topk_weights,
-                              void* stream) {
+                              int top_k, int renormalize, const int32_t* num_valid_rows, int32_t* topk_ids,
+                              float* topk_weights, void* stream) {
   B200_REQUIRE(logits && topk_ids && topk_weights, "moe_route: null pointer");
   B200_REQUIRE(num_tokens >= 0, "moe_route: negative token count");
   B200_REQUIRE(logits_dtype == 0 || logits_dtype == 1, "moe_route: logits dtype %d is neither 0 (bf16) nor 1 (f32)",
@@ -517,11 +530,12 @@ extern "C" int b200_moe_route(const void* logits, int logits_dtype, int num_toke
   const int blocks = (num_tokens + kRouteWarps - 1) / kRouteWarps;
   if (logits_dtype == 1)
     moe_route_kernel<float><<<blocks, kRouteWarps * 32, 0, as_stream(stream)>>>(
-        static_cast<const float*>(logits), num_tokens, num_experts, top_k, renormalize, topk_ids, topk_weights);
+        static_cast<const float*>(logits), num_tokens, num_experts, top_k, renormalize, num_valid_rows, topk_ids,
+        topk_weights);
   else
     moe_route_kernel<__nv_bfloat16><<<blocks, kRouteWarps * 32, 0, as_stream(stream)>>>(
-        static_cast<const __nv_bfloat16*>(logits), num_tokens, num_experts, top_k, renormalize, topk_ids,
-        topk_weights);
+        static_cast<const __nv_bfloat16*>(logits), num_tokens, num_experts, top_k, renormalize, num_valid_rows,
+        topk_ids, topk_weights);
   B200_CUDA(cudaGetLastError());
   return 0;
 }
@@ -598,8 +612,13 @@ static int permute_quant_impl(const int32_t* topk_ids, const void* x, int num_to
   }
   int rc = check_device(nullptr);
   if (rc) return rc;
-  if (num_tokens == 0) return 0;
   cudaStream_t st = as_stream(stream);
+  if (num_tokens == 0) {
+    // nothing to place, but a GEMM that follows must not find the previous call's tiles
+    B200_CUDA(cudaMemsetAsync(num_tiles, 0, sizeof(int32_t), st));
+    B200_CUDA(cudaMemsetAsync(expert_offsets, 0, (static_cast<size_t>(num_experts) + 1) * sizeof(int32_t), st));
+    return 0;
+  }
   uint8_t* p = static_cast<uint8_t*>(workspace);
   int* err = reinterpret_cast<int*>(p);
   int* counts = reinterpret_cast<int*>(p + 256);
@@ -776,8 +795,13 @@ extern "C" int b200_moe_permute_gather_fp8(const int32_t* ids, int num_rows, int
   }
   int rc = check_device(nullptr);
   if (rc) return rc;
-  if (num_rows == 0) return 0;
   cudaStream_t st = as_stream(stream);
+  if (num_rows == 0) {
+    // nothing received, but a GEMM that follows must not find the previous call's tiles
+    B200_CUDA(cudaMemsetAsync(num_tiles, 0, sizeof(int32_t), st));
+    B200_CUDA(cudaMemsetAsync(expert_offsets, 0, (static_cast<size_t>(num_experts) + 1) * sizeof(int32_t), st));
+    return 0;
+  }
   uint8_t* p = static_cast<uint8_t*>(workspace);
   int* err = reinterpret_cast<int*>(p);
   int* counts = reinterpret_cast<int*>(p + 256);

@@ -581,14 +581,9 @@ static int launch_main(const void* q, const void* k_pool, const void* v_pool,
   if (rc) return rc;
   rc = get_tensor_map_2d(v_pool, rows, D, 2, HKV * kPage, 64, &vmap);
   if (rc) return rc;
-  static bool attr_done[64] = {false};
-  int dev = 0;
-  B200_CUDA(cudaGetDevice(&dev));
-  if (dev < 64 && !attr_done[dev]) {
-    B200_CUDA(cudaFuncSetAttribute(paged_attn_decode_kernel<D, HKV, STAGES, CTAS, PAIRS>,
-                                   cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
-    attr_done[dev] = true;
-  }
+  rc = ensure_dynamic_smem(reinterpret_cast<const void*>(&paged_attn_decode_kernel<D, HKV, STAGES, CTAS, PAIRS>),
+                           Cfg::kSmemBytes);
+  if (rc) return rc;
   dim3 grid(PAIRS ? (batch + 1) / 2 : batch, max_splits);
   const float scale_log2 = scale * 1.4426950408889634f;
   paged_attn_decode_kernel<D, HKV, STAGES, CTAS, PAIRS><<<grid, Cfg::kThreads, Cfg::kSmemBytes, stream>>>(

@@ -173,9 +173,10 @@ class DecodeEngine:
         self.final_norm = final_norm if final_norm is not None else torch.ones(cfg.hidden, device=self.device, dtype=bf)
         # Pools the engine allocates itself get one block more than the caller may hand out: the scratch page
         # that the padding rows of a bucketed CUDA graph write their K/V to (see step).  Pools given from outside
-        # (a reference BlockManager's) have no such page; graphs are then captured per exact batch size.
+        # (a reference BlockManager's) have no such page; graphs are then captured per exact batch size, and an
+        # expert-parallel engine (whose exchange always runs at the full shape) can only step at its full batch.
         own_pools = k_pools is None and v_pools is None
-        self.scratch_block = num_blocks if (own_pools and graph_buckets and ep_group is None) else None
+        self.scratch_block = num_blocks if (own_pools and graph_buckets) else None
         shape = (num_blocks + (1 if self.scratch_block is not None else 0), cfg.kv_heads, PAGE, cfg.head_dim)
         self.k_pools = k_pools if k_pools is not None else [torch.zeros(shape, device=self.device, dtype=bf) for _ in range(cfg.layers)]
         self.v_pools = v_pools if v_pools is not None else [torch.zeros(shape, device=self.device, dtype=bf) for _ in range(cfg.layers)]
@@ -193,6 +194,9 @@ class DecodeEngine:
                                                 self.split_tokens, self.device)
         self.moe_ws = ops.moe_fp8_workspace(max_batch, cfg.experts, cfg.top_k, cfg.hidden, cfg.moe_inter, self.device)
         self._graphs: dict[int, torch.cuda.CUDAGraph] = {}
+        # rows of the current pass that are real (expert parallelism only): the router gives the rows beyond
+        # it no expert, so they send nothing and receive nothing
+        self.n_valid = torch.zeros(1, dtype=torch.int32, device=self.device)
         # attention split size and workspace per graph size: few rows want short splits (enough CTAs to fill the
         # GPU), a full batch long ones; the full batch's pair is (split_tokens, attn_ws)
         self._attn_by_rows: dict[int, tuple[int, torch.Tensor]] = {max_batch: (self.split_tokens, self.attn_ws)}
@@ -217,6 +221,14 @@ class DecodeEngine:
             self.ep_transport = ep_transport
             self.ep_state = ep.EPState(max_batch, cfg.hidden, cfg.top_k, cfg.experts, self.ep_world, cap, self.device,
                                        ep_group, arena=arena)
+        # Expert parallelism: every rank must run the same number of exchange passes.  `round_hook`, when set,
+        # is called before every pass that has work (a decode step, a prompt chunk) and is where the ranks agree
+        # that a round runs (ep.RoundGate); a rank without work answers with `idle_pass`.
+        self.round_hook = None
+        if self.ep_state is not None and self.use_graphs and self.scratch_block is not None:
+            # The exchange has one shape, so there is one graph; it is built here, where every rank is (its
+            # warm-up runs are real exchanges and must happen on all ranks together), with padding rows only.
+            self._build_graph(self.max_batch, pad_from=0)
         # per layer: qk_norm_rope_append, attention + split reduce, add_rmsnorm, route, rank, scatter+quant, gemm x2,
         # combine+norm; + the first norm
         self.kernel_launches_per_step = cfg.layers * 10 + 1
@@ -253,7 +265,7 @@ class DecodeEngine:
             nxt = self.layers[li + 1].ln1 if li + 1 < len(self.layers) else self.final_norm
             # MoE layer; its combine also adds into the residual stream and applies the next norm
             if ep:
-                h = self._ep_moe(h2, logits, w, x, nxt, R)
+                h = self._ep_moe(h2, logits, w, x, nxt, R)  # rows >= n_valid take no part
             else:
                 h = ops.moe_fp8_forward(h2, logits, w.w13, w.w13_scale, w.w2, w.w2_scale, cfg.top_k,
                                         cfg.norm_topk_prob, moe_ws, residual=x, norm_weight=nxt, eps=cfg.rms_eps)
@@ -271,12 +283,46 @@ class DecodeEngine:
         return pair
 
     def check_status(self, where: str = "decode engine") -> None:
-        """Synchronise and raise if any kernel of this engine has recorded a device-side finding."""
+        """Synchronise and raise if any kernel of this engine has recorded a device-side finding: a block id,
+        length or expert id outside its range (the kernels clamp or skip those, so the tokens are wrong), a
+        bounded wait that ran out, or an expert-parallel dispatch that overflowed its capacity (the dropped
+        pairs contribute nothing)."""
         for rows, (_, ws) in self._attn_by_rows.items():
             ops.read_status(ws, f"{where}: attention ({rows} rows)")
         ops.read_status(self.moe_ws, f"{where}: MoE")
-        if self.ep_state is not None and getattr(self.ep_state, "arena", None) is not None:
-            ops.read_status(self.ep_state.status, f"{where}: peer-memory exchange")
+        for name in ("_prefill_attn_ws", "_prefill_moe_ws"):
+            ws = getattr(self, name, None)
+            if ws is not None:
+                ops.read_status(ws, f"{where}: prompt pass ({name[9:-3]})")
+        st = self.ep_state
+        if st is not None:
+            if getattr(st, "arena", None) is not None:
+                ops.read_status(st.status, f"{where}: peer-memory exchange")
+            for name in ("perm_send", "perm_local"):
+                perm = getattr(st, name, None)
+                if perm is not None:
+                    ops.read_status(perm.workspace, f"{where}: expert-parallel {name}")
+            if bool(st.overflow.item()):
+                raise RuntimeError(f"{where}: expert-parallel dispatch overflowed its per-destination capacity of "
+                                   f"{st.C} rows; the dropped (token, expert) pairs were left out of the result. "
+                                   "Build the engine with a larger ep_capacity.")
+
+    def copy_kv_tokens(self, src: list[tuple[int, int]], dst: list[tuple[int, int]]) -> None:
+        """Copy the K/V of single tokens between page slots, in every layer: src[i] = (block, slot) ->
+        dst[i].  Used when a prefix-cache hit ends in, or runs through, a partially filled block: those tokens
+        are compacted into the row's own pages instead of being recomputed."""
+        if len(src) != len(dst):
+            raise ValueError("src and dst must list the same number of tokens")
+        if not src:
+            return
+        dev = self.k_pools[0].device
+        sb = torch.tensor([b for b, _ in src], device=dev)
+        ss = torch.tensor([s for _, s in src], device=dev)
+        db = torch.tensor([b for b, _ in dst], device=dev)
+        ds = torch.tensor([s for _, s in dst], device=dev)
+        for kp, vp in zip(self.k_pools, self.v_pools):
+            kp[db, :, ds, :] = kp[sb, :, ss, :]
+            vp[db, :, ds, :] = vp[sb, :, ss, :]
 
     def _step_eager(self, B: int) -> None:
         """One decode step over rows [0, B) of the static buffers; advances ctx_lens by one."""
@@ -289,22 +335,29 @@ class DecodeEngine:
 
     def _ep_moe(self, h2, logits, w: LayerWeights, x, next_norm, B: int) -> torch.Tensor:
         """Expert-parallel MoE layer: dispatch and combine around the local grouped GEMMs, by NCCL all-to-all
-        or, with a peer arena, by stores into the other ranks' memory."""
+        or, with a peer arena, by stores into the other ranks' memory.  The exchange has one fixed shape (the
+        engine's full batch on every rank); a pass with fewer real rows runs it with padding rows that the
+        router leaves without an expert (`n_valid`)."""
         import torch.distributed as dist
 
         from . import ep
         st = self.ep_state
         if B != st.T:
-            raise ValueError("expert-parallel decode runs at the engine's full batch (every rank the same size)")
+            raise ValueError("an expert-parallel pass runs at the exchange's full shape; pad it (see step / prefill)")
         return ep.ep_moe_forward(st, h2, logits, w.w13, w.w13_scale, w.w2, w.w2_scale, self.cfg.norm_topk_prob, ops,
                                  lambda o, i: dist.all_to_all_single(o, i, group=st.group), residual=x,
-                                 norm_weight=next_norm, eps=self.cfg.rms_eps)
+                                 norm_weight=next_norm, eps=self.cfg.rms_eps, n_valid=self.n_valid)
 
     GRAPH_BUCKETS = (1, 2, 4, 8, 16, 24, 32, 48, 64, 96, 128, 192, 256, 384, 512, 768, 1024)
 
     def graph_batch(self, B: int) -> int:
         """Rows the captured graph for a batch of B runs: B itself, or with a scratch page the next bucket, so
         that a batch whose size changes with every admitted and finished request reuses a handful of graphs."""
+        if self.ep_state is not None:
+            if self.scratch_block is None and B != self.max_batch:
+                raise ValueError("this expert-parallel engine reads pools it does not own (no scratch page for "
+                                 "padding rows), so it can only step at its full batch")
+            return self.max_batch  # the exchange has one shape; fewer rows are padded up to it
         if self.scratch_block is None:
             return B
         for b in self.GRAPH_BUCKETS:
@@ -312,42 +365,70 @@ class DecodeEngine:
                 return min(b, self.max_batch)
         return self.max_batch
 
-    def step(self, B: int) -> torch.Tensor:
-        """Run one decode step for the first B rows of the static state; returns next tokens (device)."""
-        if B < 1 or B > self.max_batch:
-            raise ValueError(f"batch {B} outside [1, {self.max_batch}]")
-        if not self.use_graphs:
+    def _pad_rows(self, lo: int, hi: int) -> None:
+        """Make rows [lo, hi) of the static state padding rows: token 0 at position 0 of a sequence whose only
+        page is the scratch page."""
+        if hi > lo:
+            self.tokens[lo:hi] = 0
+            self.ctx_lens[lo:hi] = 0
+            self.block_table[lo:hi, 0] = self.scratch_block
+
+    def _build_graph(self, B: int, pad_from: int | None = None) -> torch.cuda.CUDAGraph:
+        """Capture the step for B rows (two eager warm-up runs, then the capture).  `pad_from`: rows from
+        there on are set up as padding rows first."""
+        if pad_from is not None:
+            self._pad_rows(pad_from, B)
+            self.n_valid.fill_(pad_from)
+        saved = self.ctx_lens.clone()
+        stream = torch.cuda.Stream(device=self.device)
+        stream.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(stream):
+            for _ in range(2):  # warm-up: library handles, function attributes, tensor maps
+                self._step_eager(B)
+                # every warm-up run writes the K/V slot of the CURRENT position only (the one the real step
+                # will overwrite): a run that advanced could cross into a page the row does not own yet
+                self.ctx_lens.copy_(saved)
+        torch.cuda.current_stream().wait_stream(stream)
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            self._step_eager(B)
+        self.ctx_lens.copy_(saved)  # warm-up and capture advanced nothing the caller asked for
+        torch.cuda.synchronize()
+        self._graphs[B] = g
+        return g
+
+    def step(self, B: int, joined: bool = False) -> torch.Tensor:
+        """Run one decode step for the first B rows of the static state; returns next tokens (device).
+        On an expert-parallel engine B may be anything from 0 (an idle rank keeping the exchange company) to
+        the full batch; `joined` says the caller has already agreed the round with the other ranks."""
+        lowest = 0 if self.ep_state is not None else 1
+        if B < lowest or B > self.max_batch:
+            raise ValueError(f"batch {B} outside [{lowest}, {self.max_batch}]")
+        if not self.use_graphs and self.ep_state is None:
             self._step_eager(B)
             return self.next_tokens[:B]
         rows = self.graph_batch(B)
+        if self.ep_state is not None:
+            if self.round_hook is not None and not joined:
+                self.round_hook()
+            self.n_valid.fill_(B)
         if rows > B:
-            # padding rows: token 0 at position 0 of a sequence whose only page is the scratch page; reset every
-            # step because the graph advances their lengths like everyone's
-            self.tokens[B:rows] = 0
-            self.ctx_lens[B:rows] = 0
-            self.block_table[B:rows, 0] = self.scratch_block
+            # padding rows: reset every step because the graph advances their lengths like everyone's
+            self._pad_rows(B, rows)
         real, B = B, rows
+        if not self.use_graphs:
+            self._step_eager(B)
+            return self.next_tokens[:real]
         g = self._graphs.get(B)
         if g is None:
-            saved = self.ctx_lens.clone()
-            stream = torch.cuda.Stream(device=self.device)
-            stream.wait_stream(torch.cuda.current_stream())
-            with torch.cuda.stream(stream):
-                for _ in range(2):  # warm-up: library handles, function attributes, tensor maps
-                    self._step_eager(B)
-                    # every warm-up run writes the K/V slot of the CURRENT position only (the one the real step
-                    # will overwrite): a run that advanced could cross into a page the row does not own yet
-                    self.ctx_lens.copy_(saved)
-            torch.cuda.current_stream().wait_stream(stream)
-            torch.cuda.synchronize()
-            g = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(g):
-                self._step_eager(B)
-            self.ctx_lens.copy_(saved)  # warm-up and capture advanced nothing the caller asked for
-            torch.cuda.synchronize()
-            self._graphs[B] = g
+            g = self._build_graph(B)
         g.replay()
         return self.next_tokens[:real]
+
+    def idle_pass(self) -> None:
+        """Expert parallelism: take part in one exchange round without any rows of one's own."""
+        self.step(0, joined=True)
 
     # --------------------------------------------------------------- prefill
     @torch.no_grad()
@@ -362,8 +443,9 @@ class DecodeEngine:
         reference's page gather for cache hits (src/inference_server/kv_cache/hf_format.py:21-45).  The K/V
         of a whole chunk are written to their page slots before the chunk's attention runs, and row i only
         looks at positions <= its own, which is the causal mask.
-        Under expert parallelism the MoE layers of a prompt pass need the same exchange on every rank, so
-        prefill is available on single-GPU engines only.
+        Under expert parallelism a chunk is one exchange round like a decode step: it is padded to the
+        exchange's fixed shape (the engine's full batch) with rows that route nowhere, and the other ranks spend
+        the round on a decode step, a chunk of their own or an idle pass.
         Returns (first generated token, last-position logits)."""
         n = len(token_ids)
         if n == 0 or cached_tokens >= n:
@@ -372,16 +454,20 @@ class DecodeEngine:
             raise ValueError("not enough pages for the prompt")
         if len(block_ids) > self.max_pages:
             raise ValueError("sequence needs more pages than the block table is wide")
-        if self.ep_state is not None:
-            raise NotImplementedError("prefill on an expert-parallel engine")
+        ep = self.ep_state is not None
+        if ep:
+            if self.scratch_block is None:
+                raise ValueError("prompt passes on an expert-parallel engine need the engine's own pools (a scratch "
+                                 "page for the padding rows)")
+            chunk = self.ep_state.T
         cfg = self.cfg
         if getattr(self, "_prefill_chunk", 0) != chunk:
             self._prefill_chunk = chunk
             self._prefill_split = ops.default_split_tokens(chunk, cfg.kv_heads, self.max_pages * PAGE)
             self._prefill_attn_ws = ops.paged_attn_workspace(chunk, cfg.q_heads, cfg.head_dim, self.max_pages, PAGE,
                                                              self._prefill_split, self.device)
-            self._prefill_moe_ws = ops.moe_fp8_workspace(chunk, cfg.experts, cfg.top_k, cfg.hidden, cfg.moe_inter,
-                                                         self.device)
+            self._prefill_moe_ws = None if ep else ops.moe_fp8_workspace(chunk, cfg.experts, cfg.top_k, cfg.hidden,
+                                                                         cfg.moe_inter, self.device)
         # consecutive prompt tokens share the table, so attention takes them two rows per CTA where it can
         pairs = ops.paged_attn_pairs_supported(cfg.q_heads, cfg.kv_heads, cfg.head_dim, PAGE, torch.bfloat16)
         row = torch.zeros(self.max_pages, dtype=torch.int32)
@@ -393,9 +479,20 @@ class DecodeEngine:
             tokens = torch.tensor(token_ids[lo:hi], device=self.device)
             pos = torch.arange(lo, hi, device=self.device, dtype=torch.int32)
             table = row.unsqueeze(0).expand(hi - lo, -1).contiguous()
+            if ep:
+                pad = chunk - (hi - lo)
+                if pad:
+                    tokens = torch.cat([tokens, tokens.new_zeros(pad)])
+                    pos = torch.cat([pos, pos.new_zeros(pad)])
+                    scratch = torch.zeros(pad, self.max_pages, dtype=torch.int32, device=self.device)
+                    scratch[:, 0] = self.scratch_block
+                    table = torch.cat([table, scratch])
+                if self.round_hook is not None:
+                    self.round_hook()
+                self.n_valid.fill_(hi - lo)
             h = self._forward(tokens, pos, table, self._prefill_attn_ws, self._prefill_moe_ws, self._prefill_split,
-                              False, pairs=pairs)
-            h_last = h[-1:]
+                              ep, pairs=pairs)
+            h_last = h[hi - lo - 1:hi - lo]
         logits = torch.matmul(h_last, self.lm_head.t())[0]
         return int(logits.argmax()), logits
 

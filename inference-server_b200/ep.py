@@ -41,14 +41,18 @@ def plan_dispatch(topk_ids: torch.Tensor, row_of_pair: torch.Tensor, expert_offs
     topk_ids [T, K] int32 (global expert ids), row_of_pair [T*K] int32 (position in the
     expert-sorted order), expert_offsets [E+1] int32.
     Returns (slot_of_pair [T*K] int64, expert_of_slot [W*capacity] int32, overflow scalar bool tensor).
-    Pairs beyond `capacity` for a destination are dropped into slot -1 and flagged."""
+    Pairs beyond `capacity` for a destination are dropped into slot -1 and flagged; pairs with expert id -1
+    (padding rows) get slot -1 without a flag."""
     e_local = num_experts // world
     flat = topk_ids.reshape(-1).long()
-    dst = flat // e_local
+    real = flat >= 0  # id -1 is "no expert" (a padding row): the pair is neither sent nor counted
+    safe = torch.where(real, flat, torch.zeros_like(flat))
+    dst = safe // e_local
     seg_start = expert_offsets.long()[dst * e_local]
     pos = row_of_pair.long() - seg_start
-    fits = pos < capacity
-    overflow = (~fits).any()
+    fits = real & (pos < capacity)
+    overflow = (real & ~fits).any()
+    flat = safe
     slot = torch.where(fits, dst * capacity + pos, torch.full_like(pos, -1))
     # fixed shapes only (the step is captured in a CUDA graph): overflowed pairs write to a spare last entry
     trash = world * capacity
@@ -191,7 +195,7 @@ class EPState:
 
 
 def ep_moe_forward(st: EPState, h, logits, w13, w13_scale, w2, w2_scale, renormalize, kernels, all_to_all,
-                   residual=None, norm_weight=None, eps: float = 1e-6):
+                   residual=None, norm_weight=None, eps: float = 1e-6, n_valid=None):
     """One expert-parallel FP8 MoE layer on this rank's tokens `h` [T, H].
 
     `w13/w2` hold only this rank's experts.  `kernels` supplies the compute steps (the ``ops`` module on a
@@ -205,15 +209,18 @@ def ep_moe_forward(st: EPState, h, logits, w13, w13_scale, w2, w2_scale, renorma
       4. all-to-all back and weighted combine in the original (token, slot) order.
     Everything has fixed shapes and no host round trip, so the layer can sit inside a captured CUDA graph.
     With a peer arena (`st.arena`) steps 2 and 4 are stores into the other ranks' memory from inside the
-    dispatch kernel and the down GEMM, separated by flag exchanges; `all_to_all` is then unused."""
+    dispatch kernel and the down GEMM, separated by flag exchanges; `all_to_all` is then unused.
+    The shapes are the same on every rank and in every pass.  `n_valid` (an int32 scalar on the device) says how
+    many leading rows of `h` are real in this pass: the router gives the others no expert, so they are neither
+    sent nor combined - a rank with a short batch, or none, still takes part in the exchange."""
     if st.arena is not None:
-        wts, slot_of_pair = p2p_dispatch(st, h, logits, renormalize, kernels)
+        wts, slot_of_pair = p2p_dispatch(st, h, logits, renormalize, kernels, n_valid)
         kernels.ep_barrier(st.peer_flags[0], st.epochs[0:1], st.rank, st.W, st.status)
         p2p_experts(st, w13, w13_scale, w2, w2_scale, kernels)
         kernels.ep_barrier(st.peer_flags[1], st.epochs[1:2], st.rank, st.W, st.status)
         return _combine(st, wts, slot_of_pair, kernels, residual, norm_weight, eps)
     T, K, W, C, El = st.T, st.K, st.W, st.C, st.e_local
-    ids, wts = kernels.moe_route(logits, K, renormalize)
+    ids, wts = kernels.moe_route(logits, K, renormalize, n_valid)
     _, slot_of_pair = kernels.moe_permute_quant_ep(ids, h, st.E, W, C, st.xq_send, st.xs_send, st.id_send, st.overflow,
                                                    perm=st.perm_send, slot_of_pair=st.slot_of_pair)
     all_to_all(st.xq_recv, st.xq_send)
@@ -242,10 +249,10 @@ def _combine(st: EPState, wts, slot_of_pair, kernels, residual, norm_weight, eps
 # stage by stage over all ranks with ep_signal / ep_wait apart (kernels that wait for each other must not
 # sit in one stream).
 
-def p2p_dispatch(st: EPState, h, logits, renormalize, kernels):
+def p2p_dispatch(st: EPState, h, logits, renormalize, kernels, n_valid=None):
     """Route, then sort + quantise + store every row, its scales and its expert id into the owner's
     receive buffers (one kernel).  Returns (routing weights, slot_of_pair)."""
-    ids, wts = kernels.moe_route(logits, st.K, renormalize)
+    ids, wts = kernels.moe_route(logits, st.K, renormalize, n_valid)
     _, slot_of_pair = kernels.moe_permute_quant_ep_p2p(ids, h, st.E, st.W, st.C, st.rank, st.peer_xq, st.peer_xs,
                                                        st.peer_id, st.overflow, perm=st.perm_send,
                                                        slot_of_pair=st.slot_of_pair)
@@ -261,3 +268,94 @@ def p2p_experts(st: EPState, w13, w13_scale, w2, w2_scale, kernels) -> None:
     hq, hs = kernels.moe_fp8_gemm_gate_up(st.xq_sorted, st.xs_sorted, w13, w13_scale, lperm)
     kernels.moe_fp8_gemm_down_p2p(hq, hs, w2, w2_scale, lperm, st.peer_y, lperm.sorted_pair_ids, st.W, st.C, st.rank,
                                   st.status)
+
+
+# --------------------------------------------------------- agreeing on exchange rounds --
+class RoundGate:
+    """Host-side agreement of the expert-parallel ranks on whether another exchange round runs.
+
+    Every MoE layer of a pass waits for the other ranks' rows, so all ranks must run the same number of
+    passes.  Data-parallel serving gives every rank its own requests: at any moment some ranks have a decode
+    step or a prompt chunk to run and others have nothing.  Before every pass each rank calls ``join``; the
+    answer is the same on all of them: if any rank has work, every rank runs exactly one pass (those without
+    work an idle pass with no rows of their own), otherwise none does.  One small all-reduce over a gloo group
+    (host memory, so it never queues behind GPU work)."""
+
+    def __init__(self, group=None):
+        import torch.distributed as dist
+
+        ranks = dist.get_process_group_ranks(group) if group is not None else None
+        self.group = dist.new_group(ranks=ranks, backend="gloo")  # collective over the default group
+
+    def join(self, have_work: bool, leaving: bool = False) -> tuple[bool, bool]:
+        """Collective.  Returns (some rank has work, some rank is leaving).  When a rank is leaving nobody runs
+        a pass: the exchange cannot complete without it."""
+        import torch.distributed as dist
+
+        t = torch.tensor([int(have_work), int(leaving)], dtype=torch.int32)
+        dist.all_reduce(t, group=self.group)
+        return bool(t[0] > 0), bool(t[1] > 0)
+
+
+class RoundKeeper:
+    """Keeps one rank in step with the exchange rounds of the others.
+
+    ``work_round`` is what a thread with a pass to run calls first (``DecodeEngine.round_hook``); a background
+    thread answers the rounds that other ranks start while this one has nothing to do, by running `idle_pass`.
+    Both take `lock` (the backend lock that the scheduler holds for its whole tick), so a rank never has two
+    threads inside the gate at once, and the order of its joins is the order of its passes."""
+
+    def __init__(self, gate: RoundGate, idle_pass, lock, idle_sleep: float = 0.002):
+        import threading
+
+        self.gate, self.idle_pass, self.lock, self.idle_sleep = gate, idle_pass, lock, idle_sleep
+        self.rounds = 0       # passes this rank has run, with or without rows of its own
+        self.idle_rounds = 0
+        self.peer_left = False
+        self._stop = threading.Event()
+        self._thread = threading.Thread(target=self._idle_loop, name="ep-round-keeper", daemon=True)
+
+    def start(self) -> "RoundKeeper":
+        self._thread.start()
+        return self
+
+    def work_round(self) -> None:
+        """Agree a round for a pass of this rank; the caller holds `lock`."""
+        if self.peer_left:
+            raise RuntimeError("a rank has left the expert-parallel group; no further exchange can complete")
+        _, left = self.gate.join(True)
+        if left:
+            self.peer_left = True
+            raise RuntimeError("a rank has left the expert-parallel group; no further exchange can complete")
+        self.rounds += 1
+
+    def _idle_loop(self) -> None:
+        import time
+
+        while not self._stop.is_set():
+            ran = False
+            with self.lock:
+                if self._stop.is_set() or self.peer_left:
+                    break
+                work, left = self.gate.join(False)
+                if left:
+                    self.peer_left = True
+                    break
+                if work:
+                    self.idle_pass()
+                    self.rounds += 1
+                    self.idle_rounds += 1
+                    ran = True
+            # out of the lock: give a thread with work the chance to take it
+            time.sleep(self.idle_sleep / 10 if ran else self.idle_sleep)
+
+    def close(self) -> None:
+        """Tell the other ranks this one is going and stop answering rounds.  Collective in effect: the others
+        see `leaving` at their next join, whoever starts it."""
+        self._stop.set()
+        with self.lock:
+            if not self.peer_left:
+                self.gate.join(False, leaving=True)
+                self.peer_left = True
+        if self._thread.is_alive():
+            self._thread.join(timeout=5)

@@ -191,16 +191,19 @@ def qk_norm_rope_append(qkv, q_norm_w, k_norm_w, cos, sin, positions, block_tabl
 # ------------------------------------------------------------------------ MoE
 
 
-def moe_route(logits: torch.Tensor, top_k: int, renormalize: bool = True):
-    """fp32 softmax top-k routing on fp32 or bf16 logits. Returns (ids [T,K] int32, weights [T,K] fp32)."""
+def moe_route(logits: torch.Tensor, top_k: int, renormalize: bool = True, num_valid: torch.Tensor | None = None):
+    """fp32 softmax top-k routing on fp32 or bf16 logits. Returns (ids [T,K] int32, weights [T,K] fp32).
+    `num_valid` (device int32 scalar): rows at or beyond it get id -1 and weight 0 (padding rows)."""
     _need(logits, "logits")
+    if num_valid is not None:
+        _need(num_valid, "num_valid", torch.int32)
     if logits.dtype not in DTYPE_CODE:
         raise ValueError(f"logits must be float32 or bfloat16, got {logits.dtype}")
     T, E = logits.shape
     ids = torch.empty(T, top_k, dtype=torch.int32, device=logits.device)
     w = torch.empty(T, top_k, dtype=torch.float32, device=logits.device)
-    rc = _lib.load().b200_moe_route(_ptr(logits), DTYPE_CODE[logits.dtype], T, E, top_k, int(renormalize), _ptr(ids),
-                                    _ptr(w), _stream())
+    rc = _lib.load().b200_moe_route(_ptr(logits), DTYPE_CODE[logits.dtype], T, E, top_k, int(renormalize),
+                                    _ptr(num_valid), _ptr(ids), _ptr(w), _stream())
     check(rc, "b200_moe_route")
     return ids, w
 

@@ -1,16 +1,16 @@
 """Per-kernel microbenchmarks of the decode path on one B200 (synthetic, seeded inputs).
 
-    python inference-server_b200/microbench.py attn            # paged decode attention, 64 sequences,
+    python microbench.py attn            # paged decode attention, 64 sequences,
                                                                # contexts U{512..8192}, groups of 8 share 1024 tokens
-    python inference-server_b200/microbench.py moe             # FP8 MoE layer, T in {1,16,64,256,1024,4096}
-    python inference-server_b200/microbench.py ep --world 8    # expert-parallel layer, ranks emulated in-process
-    python inference-server_b200/microbench.py fp8peak         # dense e4m3 GEMM rate of the library (cuBLASLt),
+    python microbench.py moe             # FP8 MoE layer, T in {1,16,64,256,1024,4096}
+    python microbench.py ep --world 8    # expert-parallel layer, ranks emulated in-process
+    python microbench.py fp8peak         # dense e4m3 GEMM rate of the library (cuBLASLt),
                                                                # the denominator for the MoE GEMM's tensor fraction
     ... attn --small / moe --small                             # few launches on a few hundred MB: sized for a profiler
 
 Every case prints one JSON line per measured point: CUDA-event time (median of --iters launches after 3 warm-ups,
 a 256 MB buffer written between launches so nothing stays in the 126 MB L2), the algorithmic bytes or flops of
-the launch and the achieved rate.  Nothing here is imported by the package; it only calls `ops`.
+the launch and the achieved rate.  It sits beside bench.py, outside the package, and only calls the package's `ops`.
 """
 from __future__ import annotations
 
@@ -23,7 +23,9 @@ import sys
 import numpy as np
 import torch
 
-sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
 ops = importlib.import_module("inference-server_b200.ops")
 quant = importlib.import_module("inference-server_b200.quant")
 ep = importlib.import_module("inference-server_b200.ep")
@@ -34,7 +36,7 @@ MOE_TOKENS_DEFAULT = "1,16,64,256,1024,4096"
 
 def measured_hbm_gbs() -> tuple[float, str]:
     """HBM copy bandwidth measured on this pool if the file is there, else the fallback figure."""
-    path = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "MEASURED_PEAKS.json")
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     try:
         with open(path) as f:
             return float(json.load(f)["hbm_gbs"]), "measured"

@@ -12,15 +12,28 @@ import torch
 from . import moe_ref
 
 
-def moe_route(logits, top_k, renormalize=True):
-    return moe_ref.route_ref(logits.float(), top_k, renormalize)
+def moe_route(logits, top_k, renormalize=True, num_valid=None):
+    ids, w = moe_ref.route_ref(logits.float(), top_k, renormalize)
+    if num_valid is not None:  # padding rows of a fixed-shape pass: no expert, no weight
+        n = int(num_valid)
+        ids[n:] = -1
+        w[n:] = 0
+    return ids, w
 
 
 def _perm(ids, num_experts):
-    r = moe_ref.permute_ref(ids, num_experts)
+    """Pairs with id -1 ("no expert") are left out: they sort behind every real pair and get row -1."""
+    flat = ids.reshape(-1)
+    real = flat >= 0
+    n_real = int(real.sum())
+    r = moe_ref.permute_ref(torch.where(real, flat, torch.full_like(flat, num_experts)).view(ids.shape), num_experts + 1)
     p = types.SimpleNamespace()
     p.sorted_pair_ids = torch.from_numpy(r["sorted_pair_ids"])
-    p.row_of_pair = torch.from_numpy(r["row_of_pair"])
+    p.row_of_pair = torch.from_numpy(r["row_of_pair"]).clone()
+    p.row_of_pair[~real] = -1
+    r["expert_offsets"] = r["expert_offsets"][: num_experts + 1]
+    r["tiles"] = r["tiles"][r["tiles"][:, 0] < num_experts] if len(r["tiles"]) else r["tiles"]
+    p.n_real = n_real
     p.expert_offsets = torch.from_numpy(r["expert_offsets"])
     tiles = torch.zeros(max(1, ids.numel() // 128 + num_experts), 4, dtype=torch.int32)
     tiles[: len(r["tiles"])] = torch.from_numpy(r["tiles"])

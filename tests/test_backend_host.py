@@ -41,6 +41,9 @@ class StubEngine:
         self.prefill_calls.append((len(token_ids), cached_tokens))
         return token_ids[-1] + 1, None
 
+    def copy_kv_tokens(self, src, dst):  # the engine's own (index arithmetic on the pools, any device)
+        return pkg("engine").DecodeEngine.copy_kv_tokens(self, src, dst)
+
 
 def make_backend(**kw):
     return pkg("backend").B200Backend(StubEngine(**kw), max_new_tokens=8)
@@ -184,3 +187,141 @@ def test_reference_cache_manager_pools_and_prefix_hits_are_used_in_place():
     cache.release(prompt_b, "b")
     # private pages went back to the reference allocator; cached prompt pages stay cached
     assert cache.block_manager.used_blocks <= used_before + 3
+
+
+# ------------------------------------------------- failure paths and bookkeeping ----
+class FailingEngine(StubEngine):
+    """Refuses every prompt pass after the pages were taken, as a device finding or a full table would."""
+
+    def prefill(self, token_ids, block_ids, cached_tokens=0):
+        raise RuntimeError("engine refused the prompt")
+
+
+def test_a_refused_prompt_leaves_no_pages_behind():
+    be = pkg("backend").B200Backend(FailingEngine(num_blocks=32), max_new_tokens=8)
+    with pytest.raises(RuntimeError, match="refused"):
+        be.prefill(list(range(40)), "s")
+    assert len(be._alloc.free) == 32
+    with pytest.raises(RuntimeError, match="refused"):
+        be.prefill_chunk(list(range(20)), None)
+    assert len(be._alloc.free) == 32
+
+
+def test_a_prompt_wider_than_the_block_table_is_refused_before_any_page_is_taken():
+    be = make_backend(num_blocks=64, max_pages=4)  # 64 tokens per sequence at most
+    with pytest.raises(ValueError, match="block table"):
+        be.prefill(list(range(60)), "s")  # 60 + 8 reserved = 68 tokens = 5 pages
+    assert len(be._alloc.free) == 64 and be.engine.prefill_calls == []
+    kv, _, _ = be.prefill_chunk(list(range(40)), None)
+    with pytest.raises(ValueError, match="block table"):
+        be.prefill_chunk(list(range(40, 60)), kv)
+    assert kv.ctx_len == 40 and len(kv.block_ids) == 3  # the earlier chunks are untouched
+
+
+def test_two_live_batches_do_not_read_each_others_table():
+    be = make_backend()
+    kv1, f1, n1 = be.prefill(list(range(5)), "a")
+    kv2, f2, n2 = be.prefill(list(range(50, 70)), "b")
+    b1 = be.splice_into_batched(None, kv1, n1)
+    b2 = be.splice_into_batched(None, kv2, n2)
+    be.decode_step_batched(torch.tensor([[f1]]), b1, None, None)
+    be.decode_step_batched(torch.tensor([[f2]]), b2, None, None)
+    # b1 is clean (nothing admitted or evicted since its last step), yet the device table holds b2's row
+    be.decode_step_batched(torch.tensor([[f1 + 1]]), b1, None, None)
+    assert be.engine.block_table[0, : len(kv1.block_ids)].tolist() == kv1.block_ids
+    assert int(be.engine.ctx_lens[0]) == 7
+
+
+def test_device_findings_surface_on_the_serving_path():
+    class Noting(StubEngine):
+        checks, bad = 0, False
+
+        def check_status(self, where):
+            self.checks += 1
+            if self.bad:
+                raise RuntimeError(f"{where}: device: block table entry outside the pool")
+
+    be = pkg("backend").B200Backend(Noting(), max_new_tokens=8)
+    be.status_check_every = 4
+    kv, first, n = be.prefill(list(range(5)), "s")
+    assert be.engine.checks == 1  # right after the prompt pass
+    batch = be.splice_into_batched(None, kv, n)
+    tok = torch.tensor([[first]])
+    for _ in range(3):
+        tok, batch = be.decode_step_batched(tok.view(1, 1), batch, None, None)
+    assert be.engine.checks == 1
+    be.engine.bad = True
+    with pytest.raises(RuntimeError, match="outside the pool"):
+        be.decode_step_batched(tok.view(1, 1), batch, None, None)
+
+
+@pytest.mark.skipif(not HAVE_REF, reason="reference checkout not present on this machine")
+def test_a_partial_block_in_the_middle_of_a_hit_is_compacted_not_dropped():
+    """The reference stores a prompt suffix in fresh blocks (cache_manager.py:82-127), so a prompt that was
+    extended twice is cached as blocks of 16 + 6 + 11 tokens.  A hit on it shares the full leading block in
+    place and copies the other 17 tokens, compacted, into the new row's own pages - none is recomputed."""
+    sys.path.insert(0, os.path.join(REF, "src"))
+    from inference_server.kv_cache.cache_manager import CacheManager
+
+    be = make_backend(num_blocks=64, max_batch=8, max_pages=16)
+    cfg = be.engine.cfg
+    cache = CacheManager(64, 16, layer_shapes=[(cfg.kv_heads, cfg.head_dim)] * cfg.layers, device="cpu",
+                         dtype=torch.bfloat16)
+    be.set_cache_adapter(cache)
+    p1 = list(range(500, 522))            # 22 tokens -> blocks of 16 + 6
+    p2 = p1 + list(range(900, 911))       # + 11 -> a third block of 11
+    p3 = p2 + [1, 2, 3, 4, 5]
+    kv1, _, _ = be.prefill(p1, "a")
+    kv2, _, _ = be.prefill(p2, "b")
+    assert be.last_cache_hit_tokens == 22 and be.engine.prefill_calls[-1] == (33, 22)
+    blocks = cache._exact_index[tuple(p2)]
+    assert [b.num_tokens_stored for b in blocks] == [16, 6, 11]
+    # make every cached token recognisable: value = 100 * block + slot, in every layer
+    for kp, vp in zip(cache.block_manager.k_pools, cache.block_manager.v_pools):
+        for b in blocks:
+            for s in range(b.num_tokens_stored):
+                kp[b.block_id, :, s, :] = 100 * b.block_id + s
+                vp[b.block_id, :, s, :] = -(100 * b.block_id + s)
+    refs_before = [b.ref_count for b in blocks]
+    kv3, _, n3 = be.prefill(p3, "c")
+    assert be.last_cache_hit_tokens == 33 and be.engine.prefill_calls[-1] == (38, 33)
+    assert kv3.block_ids[0] == blocks[0].block_id                       # the full block is shared in place
+    assert not set(kv3.block_ids[1:]) & {b.block_id for b in blocks}    # everything after it is private
+    where = [(blocks[1].block_id, s) for s in range(6)] + [(blocks[2].block_id, s) for s in range(11)]
+    kp, vp = cache.block_manager.k_pools[-1], cache.block_manager.v_pools[-1]
+    for i, (b, s) in enumerate(where):
+        pos = 16 + i
+        got_k = kp[kv3.block_ids[pos // 16], :, pos % 16, :]
+        got_v = vp[kv3.block_ids[pos // 16], :, pos % 16, :]
+        assert bool((got_k == 100 * b + s).all()) and bool((got_v == -(100 * b + s)).all())
+    # only the shared block stays acquired for the row; the copied-from blocks were let go again
+    assert blocks[0].ref_count == refs_before[0] + 1
+    assert [b.ref_count for b in blocks[1:]] == refs_before[1:]
+
+    # an exact repeat of a cached prompt recomputes only its last token
+    kv4, _, _ = be.prefill(p2, "d")
+    assert be.last_cache_hit_tokens == 32 and be.engine.prefill_calls[-1] == (33, 32)
+
+
+@pytest.mark.skipif(not HAVE_REF, reason="reference checkout not present on this machine")
+def test_a_refused_prompt_lets_go_of_its_cache_hit():
+    sys.path.insert(0, os.path.join(REF, "src"))
+    from inference_server.kv_cache.cache_manager import CacheManager
+
+    be = make_backend(num_blocks=64, max_batch=8, max_pages=16)
+    cfg = be.engine.cfg
+    cache = CacheManager(64, 16, layer_shapes=[(cfg.kv_heads, cfg.head_dim)] * cfg.layers, device="cpu",
+                         dtype=torch.bfloat16)
+    be.set_cache_adapter(cache)
+    prompt = list(range(700, 740))
+    be.prefill(prompt, "a")
+    blocks = cache._exact_index[tuple(prompt)]
+    refs, free = [b.ref_count for b in blocks], cache.block_manager.free_blocks
+
+    def refuse(*a, **k):
+        raise RuntimeError("engine refused the prompt")
+
+    be.engine.prefill = refuse
+    with pytest.raises(RuntimeError, match="refused"):
+        be.prefill(prompt + [1, 2, 3], "b")
+    assert [b.ref_count for b in blocks] == refs and cache.block_manager.free_blocks == free

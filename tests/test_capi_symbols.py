@@ -47,7 +47,7 @@ def test_host_side_calls_that_need_no_gpu():
 
 def test_null_pointer_is_rejected_on_the_host():
     lib = pkg("_lib").load()
-    rc = lib.b200_moe_route(None, 1, 4, 16, 4, 1, None, None, None)
+    rc = lib.b200_moe_route(None, 1, 4, 16, 4, 1, None, None, None, None)
     assert rc == -1 and b"null" in lib.b200_last_error_detail()
 
 

@@ -14,7 +14,7 @@ import torch.multiprocessing as mp
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
-def _worker(rank, world, port, capacity, results):
+def _worker(rank, world, port, capacity, results, valid_rows=None):
     sys.path.insert(0, ROOT)
     sys.path.insert(0, os.path.join(ROOT, "tests"))
     import importlib
@@ -36,12 +36,17 @@ def _worker(rank, world, port, capacity, results):
         el = E // world
         lo = rank * el
         st = ep.EPState(T, H, K, E, world, capacity, "cpu")
+        n = T if valid_rows is None else valid_rows[rank]  # real rows of this rank's pass; the rest is padding
         out = ep.ep_moe_forward(
             st, x, logits, w13q[lo:lo + el].view(torch.uint8), w13s[lo:lo + el], w2q[lo:lo + el].view(torch.uint8),
-            w2s[lo:lo + el], True, cpu_kernels, lambda o, i: dist.all_to_all_single(o, i))
-        ref = oracle.moe_fp8_ref(x, logits, w13q, w13s, w2q, w2s, K, True)
-        err = float((out.float() - ref.float()).abs().max() / ref.float().abs().max())
-        results[rank] = (err, bool(st.overflow.item()))
+            w2s[lo:lo + el], True, cpu_kernels, lambda o, i: dist.all_to_all_single(o, i),
+            n_valid=None if valid_rows is None else torch.tensor([n], dtype=torch.int32))
+        err = 0.0
+        if n:
+            ref = oracle.moe_fp8_ref(x[:n], logits[:n], w13q, w13s, w2q, w2s, K, True)
+            err = float((out[:n].float() - ref.float()).abs().max() / ref.float().abs().max())
+        pad_is_zero = bool((out[n:] == 0).all())
+        results[rank] = (err, bool(st.overflow.item()), pad_is_zero)
     finally:
         dist.destroy_process_group()
 
@@ -55,10 +60,89 @@ def test_two_rank_expert_parallel_layer_matches_single_process(capacity, expect_
     mp.spawn(_worker, args=(world, port, capacity, results), nprocs=world, join=True)
     assert len(results) == world
     for rank in range(world):
-        err, overflow = results[rank]
+        err, overflow, _ = results[rank]
         assert overflow == expect_overflow
         if not expect_overflow:
             assert err < 1e-2, f"rank {rank}: EP layer differs from the single-process layer by {err}"
+
+
+@pytest.mark.parametrize("valid_rows", [(24, 5), (0, 17), (0, 0)])
+def test_ranks_with_unequal_batches_share_one_fixed_shape_exchange(valid_rows):
+    """Continuous batching gives every rank its own batch size; the exchange keeps one shape and the rows a
+    rank does not have are padding that is routed nowhere.  A rank with no rows at all still serves its
+    experts to the other."""
+    world = 2
+    mgr = mp.Manager()
+    results = mgr.dict()
+    port = 29300 + (os.getpid() + sum(valid_rows) * 7) % 250
+    mp.spawn(_worker, args=(world, port, 48, results, valid_rows), nprocs=world, join=True)
+    assert len(results) == world
+    for rank in range(world):
+        err, overflow, pad_is_zero = results[rank]
+        assert not overflow and pad_is_zero
+        assert err < 1e-2, f"rank {rank}: {valid_rows[rank]} real rows differ from the single-process layer by {err}"
+
+
+def _round_worker(rank, world, port, passes, results):
+    """Every rank has its own number of passes with work, arriving at its own pace; a pass is a collective
+    (as an exchange is), so a rank that ran one more or one fewer than the others would hang the group."""
+    sys.path.insert(0, ROOT)
+    import importlib
+    import threading
+    import time
+
+    ep = importlib.import_module("inference-server_b200.ep")
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    import datetime
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=60))
+    try:
+        gate = ep.RoundGate()
+        log = []
+
+        def one_pass(kind):
+            t = torch.tensor([1 if kind == "work" else 0])
+            dist.all_reduce(t)  # stands in for the layer exchanges of one pass
+            log.append((kind, int(t)))
+
+        lock = threading.Lock()
+        keeper = ep.RoundKeeper(gate, lambda: one_pass("idle"), lock, idle_sleep=0.001).start()
+        for i in range(passes[rank]):
+            time.sleep(0.003 * (rank + 1))  # requests arrive between ticks
+            with lock:  # as the scheduler holds the backend lock for a tick
+                keeper.work_round()
+                one_pass("work")
+        # wait (on the host, without a collective: the keeper thread owns those) until every rank has done its
+        # own work; the keeper meanwhile answers the rounds the slower ranks still start
+        results[("done", rank)] = True
+        while not all(results.get(("done", r)) for r in range(world)):
+            time.sleep(0.01)
+        time.sleep(0.05)
+        with lock:
+            rounds, idle = keeper.rounds, keeper.idle_rounds
+        keeper.close()
+        # a rank that is told a peer has left refuses further rounds instead of waiting for it
+        refused = False
+        try:
+            keeper.work_round()
+        except RuntimeError:
+            refused = True
+        results[rank] = (rounds, idle, sum(1 for k, _ in log if k == "work"), refused)
+    finally:
+        dist.destroy_process_group()
+
+
+def test_round_keeper_keeps_ranks_in_step_with_unequal_work():
+    world, passes = 2, (7, 2)
+    mgr = mp.Manager()
+    results = mgr.dict()
+    port = 29700 + os.getpid() % 150
+    mp.spawn(_round_worker, args=(world, port, passes, results), nprocs=world, join=True)
+    rounds = [results[r][0] for r in range(world)]
+    assert rounds[0] == rounds[1], "ranks ran different numbers of exchange passes"
+    assert max(passes) <= rounds[0] <= sum(passes)
+    for r in range(world):
+        total, idle, worked, refused = results[r]
+        assert worked == passes[r] and idle == total - worked and refused
 
 
 def test_plan_dispatch_slots():
