@@ -26,8 +26,16 @@ One JSON line is printed by rank 0:
             device->host read of the next tokens
   roofline  paged attention kernel (the dominant kernel): algorithmic KV bytes
             per launch / measured launch time, against the measured HBM peak
+  roofline_moe  the two grouped FP8 GEMMs of one MoE layer, timed alone on the
+            step's own routing: expert weight bytes streamed / launch time
   cpu_baseline  the reference's decode step on this machine's host cores
             (oracle/ref_decode.py), a bounded sample extrapolated over layers
+  config.ep_parity (N > 1)  one MoE layer run both ways on every rank after the
+            timed region - through the expert-parallel exchange as benchmarked,
+            and as the fused single-GPU layer over all experts - must be
+            bit-equal, else the run exits non-zero
+  config.strong_scaling_tok_s (N > 1)  the same engines stepping batch/N
+            sequences per GPU (the fixed total the single-GPU line runs)
 """
 from __future__ import annotations
 
@@ -143,12 +151,113 @@ def build_workload(cfg, batch: int, gen_tokens: int, seed: int, ctx_min: int = 5
     return prompt_lens, table, total, max_pages
 
 
-def reference_arm(args, cfg, prompt_lens):
+def reference_arm(args, cfg, prompt_lens, budget_s=None):
     """The reference's own decode step on the host cores, bounded sample (see oracle/ref_decode.py)."""
     from oracle.ref_decode import time_reference_decode
 
-    r = time_reference_decode(cfg, prompt_lens, steps=max(1, args.steps), warmup=max(0, args.warmup), sample_layers=1)
-    return r
+    return time_reference_decode(cfg, prompt_lens, steps=max(1, args.steps), warmup=max(0, args.warmup), sample_layers=1,
+                                 budget_s=budget_s)
+
+
+def moe_gemm_roofline(engine, ops, cfg, B, dev, peak):
+    """The gate/up and the down grouped GEMM alone, on a routing like the step's (B tokens, random router
+    logits): each is launched once per layer on that layer's own weights (no layer's weights fit the L2, and
+    consecutive launches read different ones), between CUDA events on the launching stream.  Algorithmic bytes
+    = experts hit x 2*H*I (gate/up) or H*I (down) of e4m3 weights, which is what bounds both at decode sizes.
+    Under expert parallelism the rows are this rank's own only, so the figure describes the kernels, not the
+    exchange."""
+    g = torch.Generator(device=dev).manual_seed(4321)
+    x = torch.randn(B, cfg.hidden, generator=g, device=dev).bfloat16()
+    local = engine.layers[0].w13.shape[0]
+    logits = torch.randn(B, local, generator=g, device=dev)
+    k = min(cfg.top_k, local)
+    ids, _ = ops.moe_route(logits, k, True)
+    hit = int(torch.unique(ids).numel())
+    perm, xq, xs = ops.moe_permute_quant(ids, x, local)
+    status = torch.zeros(64, dtype=torch.int32, device=dev)
+    w0 = engine.layers[0]
+    hq, hs = ops.moe_fp8_gemm_gate_up(xq, xs, w0.w13, w0.w13_scale, perm, status)
+    y = ops.moe_fp8_gemm_down(hq, hs, w0.w2, w0.w2_scale, perm, status)
+    out = {}
+    for name, fn, per_expert in (
+            ("gate_up", lambda w: ops.moe_fp8_gemm_gate_up(xq, xs, w.w13, w.w13_scale, perm, status), 2 * cfg.hidden * cfg.moe_inter),
+            ("down", lambda w: ops.moe_fp8_gemm_down(hq, hs, w.w2, w.w2_scale, perm, status, out=y), cfg.hidden * cfg.moe_inter)):
+        for w in engine.layers[:3]:
+            fn(w)
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for w in engine.layers:
+            fn(w)
+        e1.record()
+        torch.cuda.synchronize()
+        us = e0.elapsed_time(e1) * 1e3 / len(engine.layers)
+        alg = hit * per_expert
+        out[name] = {"us_per_launch": us, "algorithmic_bytes": alg, "achieved": alg / us / 1e3, "frac": alg / us / 1e3 / peak}
+    ops.read_status(status, "MoE GEMM roofline launches")
+    out.update({"bound": "hbm", "unit": "GB/s", "peak": peak, "tokens": B, "experts_hit": hit, "experts_local": local,
+                "launches_timed": len(engine.layers)})
+    return out
+
+
+def ep_parity_check(engine, ops, cfg, B, dev, rank, world):
+    """Collective.  One MoE layer with weights drawn from a seed every rank shares: this rank's tokens go
+    through the expert-parallel exchange exactly as in the timed steps (same state, same transport) with the
+    rank's slice of the experts, and through the fused single-GPU layer over all experts.  Bit-equal or not."""
+    ep, quant = pkg("ep"), pkg("quant")
+    st = engine.ep_state
+    E, H, I = cfg.experts, cfg.hidden, cfg.moe_inter
+    g = torch.Generator(device=dev).manual_seed(777)  # the same on every rank
+    w13q = torch.empty(E, 2 * I, H, dtype=torch.float8_e4m3fn, device=dev)
+    w13s = torch.empty(E, 2 * I // 128, H // 128, dtype=torch.float32, device=dev)
+    w2q = torch.empty(E, H, I, dtype=torch.float8_e4m3fn, device=dev)
+    w2s = torch.empty(E, H // 128, I // 128, dtype=torch.float32, device=dev)
+    for e0 in range(0, E, 8):  # a few experts at a time: the fp32 originals of all of them need not fit
+        w13q[e0:e0 + 8], w13s[e0:e0 + 8] = quant.quantize_weight_blocks(
+            torch.randn(8, 2 * I, H, generator=g, device=dev) * 0.02)
+        w2q[e0:e0 + 8], w2s[e0:e0 + 8] = quant.quantize_weight_blocks(torch.randn(8, H, I, generator=g, device=dev) * 0.02)
+    el = E // world
+    mine = [t[rank * el:(rank + 1) * el].contiguous() for t in (w13q, w13s, w2q, w2s)]
+    gt = torch.Generator(device=dev).manual_seed(900 + rank)  # different tokens on every rank
+    x = torch.randn(B, H, generator=gt, device=dev).bfloat16()
+    logits = torch.randn(B, E, generator=gt, device=dev).bfloat16()
+    ref = ops.moe_fp8_forward(x, logits, w13q, w13s, w2q, w2s, cfg.top_k, cfg.norm_topk_prob)
+    a2a = lambda o, i: torch.distributed.all_to_all_single(o, i, group=st.group)
+    got = ep.ep_moe_forward(st, x, logits, *mine, cfg.norm_topk_prob, ops, a2a)
+    torch.cuda.synchronize()
+    engine.check_status("expert-parallel parity layer")
+    same = torch.tensor([int(torch.equal(got, ref))], device=dev)
+    torch.distributed.all_reduce(same, op=torch.distributed.ReduceOp.MIN)
+    worst = torch.tensor([float((got.float() - ref.float()).abs().max())], device=dev)
+    torch.distributed.all_reduce(worst, op=torch.distributed.ReduceOp.MAX)
+    return {"bit_equal": bool(same.item()), "ranks": world, "tokens_per_rank": B, "max_abs_diff": float(worst),
+            "transport": "peer memory" if st.arena is not None else "NCCL all-to-all"}
+
+
+def strong_scaling(engine, B, world, dev, steps: int = 8):
+    """Decode tokens/s with the single-GPU line's total number of sequences spread over the ranks (B / world
+    each; the other rows of the fixed-shape exchange are padding)."""
+    if engine.scratch_block is None or B % world:
+        return None
+    b = B // world
+    saved = engine.ctx_lens.clone()
+    for _ in range(3):
+        engine.step(b)
+    torch.distributed.barrier()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        engine.tokens[:b].copy_(engine.step(b))
+    e1.record()
+    torch.distributed.barrier()
+    torch.cuda.synchronize()
+    t = torch.tensor([e0.elapsed_time(e1)], device=dev, dtype=torch.float64)
+    torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
+    engine.ctx_lens.copy_(saved)
+    engine.check_status("strong-scaling steps")
+    return {"value": b * world * steps / (float(t) / 1e3), "unit": "tok/s", "sequences_total": b * world,
+            "sequences_per_gpu": b, "ms_per_step": float(t) / steps, "steps": steps}
 
 
 def main():
@@ -194,13 +303,19 @@ def main():
         if rank != 0:
             return
         torch.set_num_threads(os.cpu_count() or torch.get_num_threads())
-        steps = min(args.steps, 3)
-        warm = min(args.warmup, 1)
-        args.steps, args.warmup = steps, warm
-        r = reference_arm(args, cfg, prompt_lens)
+        # a step of this arm is a bounded sample (one of the model's layers at the full batch, about a second of
+        # host time on the benchmark machine); a slow host stops early instead of running for many minutes
+        r = reference_arm(argparse.Namespace(steps=max(1, args.steps), warmup=max(0, args.warmup)), cfg, prompt_lens,
+                          budget_s=120.0)
+        steps, warm, measured_s = r["steps_done"], r["warmup_done"], r["stepping_s"]
         line = {"impl": "reference", "metric": "decode tok/s", "value": r["tok_per_s"], "unit": "tok/s", "n_gpus": args.gpus,
-                "steps": steps, "warmup": warm, "ms_per_step": r["step_s_full"] * 1e3, "higher_is_better": True,
+                "steps": steps, "warmup": warm, "ms_per_step": r["step_s_sample"] * 1e3, "higher_is_better": True,
                 "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "config": config,
+                "timed": {"what": "ms_per_step is the measured time of one SAMPLE step (" + r["sample"].split(";")[0] + "); "
+                                  "value is the full-depth figure extrapolated from it",
+                          "measured_stepping_s": measured_s, "sample_step_ms": r["step_s_sample"] * 1e3,
+                          "layer_ms": r["layer_s"] * 1e3, "other_ms": r["other_s"] * 1e3,
+                          "extrapolated_ms_per_full_step": r["step_s_full"] * 1e3},
                 "cpu_baseline": {"value": r["tok_per_s"], "unit": "tok/s", "cores": r["threads"], "kind": "port",
                                  "sample": r["sample"]},
                 "e2e": {"value": r["tok_per_s"], "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
@@ -326,6 +441,11 @@ def main():
     peak, peak_src = measured_peak_gbs()
     achieved = alg_bytes / attn_us / 1e3  # GB/s
 
+    roofline_moe = moe_gemm_roofline(engine, ops, cfg, B, dev, peak)
+    if world > 1 and engine.ep_state is not None:
+        config["ep_parity"] = ep_parity_check(engine, ops, cfg, B, dev, rank, world)
+        config["strong_scaling_tok_s"] = strong_scaling(engine, B, world, dev)
+
     times = torch.tensor([ms, e2e_s * 1e3], device=dev, dtype=torch.float64)
     if world > 1:
         torch.distributed.all_reduce(times, op=torch.distributed.ReduceOp.MAX)
@@ -348,8 +468,12 @@ def main():
         torch.distributed.destroy_process_group()
         guard.cancel()
 
+    parity = config.get("ep_parity")
+    parity_bad = parity is not None and not parity["bit_equal"]
     if rank != 0:
         shutdown()
+        if parity_bad:
+            raise SystemExit(1)
         return
 
     line = {
@@ -365,8 +489,13 @@ def main():
                      "unit": "GB/s", "frac": achieved / peak, "traffic": alg_bytes * ATTN_TRAFFIC_PER_ALG_BYTE,
                      "algorithmic_bytes": alg_bytes, "us_per_launch": attn_us, "peak_source": peak_src,
                      "launches_timed": cfg.layers},
+        "roofline_moe": roofline_moe,
         "setup_s": setup_s,
     }
+    if parity_bad:
+        print(json.dumps(line))
+        shutdown()
+        raise SystemExit("expert-parallel MoE layer is not bit-equal to the fused single-GPU layer on every rank")
     if not args.no_cpu_baseline and world == 1:
         from oracle.ref_decode import time_reference_decode
         r = time_reference_decode(cfg, prompt_lens, steps=2, warmup=1, sample_layers=1)

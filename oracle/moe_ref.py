@@ -57,6 +57,9 @@ def quantize_weight_ref(w: torch.Tensor):
 
 
 def dequant_weight(q: torch.Tensor, scale_inv: torch.Tensor) -> torch.Tensor:
+    """w = q * scale_inv per 128x128 tile, scale_inv [..., rows/128, cols/128], as transformers
+    ``Fp8Dequantize.convert`` (integrations/finegrained_fp8.py) - pinned bit-exact on its output by
+    tests/golden/fp8_weight_dequant.npz."""
     rows, cols = q.shape[-2:]
     lead = q.shape[:-2]
     t = q.detach().cpu().float().reshape(*lead, rows // 128, 128, cols // 128, 128)
@@ -87,7 +90,7 @@ def _bf16(t: torch.Tensor) -> torch.Tensor:
 
 
 def moe_fp8_ref(x, router_logits, w13_q, w13_s, w2_q, w2_s, top_k: int, renormalize: bool = True,
-                return_parts: bool = False):
+                return_parts: bool = False, hf_rounding: bool = False):
     """The FP8 expert layer on CPU.
 
     Follows transformers ``FP8Experts.forward`` / ``fp8_grouped_mm_experts_forward``:
@@ -98,13 +101,17 @@ def moe_fp8_ref(x, router_logits, w13_q, w13_s, w2_q, w2_s, top_k: int, renormal
     equals dequant(A) @ dequant(W)^T up to fp32 rounding, which is how it is
     evaluated here.  One stated difference from that code: gate_up and h stay in
     fp32 until h is quantised (there they pass through bf16), which is the more
-    accurate of the two and what the CUDA kernel does.
+    accurate of the two and what the CUDA kernel does.  ``hf_rounding=True``
+    evaluates the other form, with every rounding point of ``FP8Experts.forward``
+    for a bf16 model: gate_up rounded to bf16 (``output_dtype=input.dtype``),
+    ``act_fn(gate) * up`` as two bf16 operations, the routing weight cast to bf16
+    and multiplied in bf16; tests bound the distance between the two forms.
     """
     ids, w = route_ref(router_logits, top_k, renormalize)
-    return moe_fp8_experts_ref(x, ids, w, w13_q, w13_s, w2_q, w2_s, return_parts)
+    return moe_fp8_experts_ref(x, ids, w, w13_q, w13_s, w2_q, w2_s, return_parts, hf_rounding)
 
 
-def moe_fp8_experts_ref(x, ids, w, w13_q, w13_s, w2_q, w2_s, return_parts: bool = False):
+def moe_fp8_experts_ref(x, ids, w, w13_q, w13_s, w2_q, w2_s, return_parts: bool = False, hf_rounding: bool = False):
     """The expert part of :func:`moe_fp8_ref` for given routing (ids int [T,K], weights fp32 [T,K]);
     this is the signature the model's experts module is called with
     (``experts(hidden_states, top_k_index, top_k_weights)``)."""
@@ -133,8 +140,10 @@ def moe_fp8_experts_ref(x, ids, w, w13_q, w13_s, w2_q, w2_s, return_parts: bool 
         a = xd[tok_of_row[lo:hi]]
         w13 = dequant_weight(w13_q[e], w13_s[e])
         gu = a @ w13.t()
+        if hf_rounding:
+            gu = _bf16(gu)
         g, u = gu[:, :inter], gu[:, inter:]
-        h = torch.nn.functional.silu(g) * u
+        h = _bf16(_bf16(torch.nn.functional.silu(g)) * u) if hf_rounding else torch.nn.functional.silu(g) * u
         hq, hs = act_quant_ref(h)
         hq_all[lo:hi], hs_all[lo:hi] = hq, hs
         h_all[lo:hi] = h
@@ -143,7 +152,10 @@ def moe_fp8_experts_ref(x, ids, w, w13_q, w13_s, w2_q, w2_s, return_parts: bool 
     rop = torch.from_numpy(perm["row_of_pair"]).long().reshape(T, top_k)
     out = torch.zeros(T, H)
     for k in range(top_k):
-        out = out + w[:, k : k + 1] * y_all[rop[:, k]]
+        if hf_rounding:
+            out = out + _bf16(y_all[rop[:, k]] * _bf16(w[:, k : k + 1]))
+        else:
+            out = out + w[:, k : k + 1] * y_all[rop[:, k]]
     out = out.to(torch.bfloat16)
     if return_parts:
         return out, dict(ids=ids, weights=w, perm=perm, xq=xq, xs=xs, h=h_all, hq=hq_all, hs=hs_all, y=y_all)

@@ -61,11 +61,14 @@ def dense_left_padded_cache(num_layers, ctx_lens, kv_heads, head_dim, dtype, see
 
 
 def time_reference_decode(cfg, ctx_lens, steps: int, warmup: int, sample_layers: int = 1,
-                          dtype=torch.bfloat16, seed: int = 0) -> dict:
+                          dtype=torch.bfloat16, seed: int = 0, budget_s: float | None = None) -> dict:
     """Times the reference decode step on the host for `sample_layers` of cfg.layers
     layers at the full batch and extrapolates the layer part to the full depth.
+    With `budget_s` the loop stops early (after at least one timed step) once that many
+    seconds of stepping have gone by; `steps_done` and `warmup_done` say what ran.
 
-    Returns dict(step_s_sample, layer_s, other_s, step_s_full, tok_per_s, threads, sample)."""
+    Returns dict(step_s_sample, layer_s, other_s, step_s_full, tok_per_s, threads, sample,
+    steps_done, warmup_done, stepping_s)."""
     from transformers import Qwen3MoeForCausalLM
 
     torch.manual_seed(seed)
@@ -87,7 +90,14 @@ def time_reference_decode(cfg, ctx_lens, steps: int, warmup: int, sample_layers:
     cur = torch.randint(0, cfg.vocab_size, (B, 1), generator=torch.Generator().manual_seed(seed))
     lens = list(ctx_lens)
     step_times, layer_times = [], []
+    t_loop = time.perf_counter()
+    warmup_done = 0
     for s in range(warmup + steps):
+        if budget_s is not None and time.perf_counter() - t_loop > budget_s and (step_times or s >= 1):
+            if step_times:
+                break
+            warmup = s  # the budget went into warm-up steps: time one step now and stop
+        warmup_done = min(s, warmup)
         mask = torch.cat([mask, torch.ones(B, 1, dtype=torch.long)], dim=1)  # scheduler.py:386-389
         pos = torch.tensor([[n] for n in lens])                              # scheduler.py:390-393
         layer_time[0] = 0.0
@@ -99,6 +109,9 @@ def time_reference_decode(cfg, ctx_lens, steps: int, warmup: int, sample_layers:
         if s >= warmup:
             step_times.append(dt)
             layer_times.append(layer_time[0] / sample_layers)
+            warmup_done = warmup
+    stepping_s = time.perf_counter() - t_loop
+    steps = len(step_times)
     for h in handles:
         h.remove()
     step_s = sum(step_times) / len(step_times)
@@ -106,7 +119,7 @@ def time_reference_decode(cfg, ctx_lens, steps: int, warmup: int, sample_layers:
     other_s = max(step_s - layer_s * sample_layers, 0.0)
     full = other_s + layer_s * cfg.layers
     return dict(step_s_sample=step_s, layer_s=layer_s, other_s=other_s, step_s_full=full, tok_per_s=B / full,
-                threads=torch.get_num_threads(),
+                threads=torch.get_num_threads(), steps_done=steps, warmup_done=warmup_done, stepping_s=stepping_s,
                 sample=f"{sample_layers} of {cfg.layers} layers at the full batch of {B} rows (dense left-padded "
                        f"{str(dtype).replace('torch.', '')} cache, S={max(ctx_lens)}), {steps} steps; step time = "
                        f"embed+norm+lm_head+argmax time + {cfg.layers} x measured layer time")

@@ -31,7 +31,7 @@ from inference_server.kv_cache.hf_format import blocks_to_dynamic_cache  # noqa:
 from inference_server.backends.torch_backend import TorchBackend  # noqa: E402
 from transformers import Qwen3MoeConfig, Qwen3MoeForCausalLM  # noqa: E402
 from transformers.models.qwen3_moe import modeling_qwen3_moe as hfm  # noqa: E402
-from transformers.integrations.finegrained_fp8 import Fp8Quantize  # noqa: E402
+from transformers.integrations.finegrained_fp8 import Fp8Dequantize, Fp8Quantize  # noqa: E402
 
 
 def save(name, **arrays):
@@ -126,6 +126,20 @@ def weight_quant_case(name, seed):
     save(name, w=w.numpy(), q=q.view(torch.uint8).numpy(), scale_inv=s.numpy())
 
 
+def weight_dequant_case(name, seed):
+    """transformers Fp8Dequantize.convert on a 2 x 3 grid of 128x128 tiles with six different scales: pins
+    which axis of scale_inv follows the rows and which the columns of the weight, and that w = q * scale_inv."""
+    g = torch.Generator().manual_seed(seed)
+    codes = torch.randint(0, 256, (1, 256, 384), generator=g, dtype=torch.int32)
+    codes = torch.where((codes & 0x7F) == 0x7F, codes & 0x80, codes).to(torch.uint8)  # no NaN encodings
+    q = codes.view(torch.float8_e4m3fn)
+    scale_inv = (torch.rand(1, 2, 3, generator=g) * 0.01 + 1e-4).float()
+    qcfg = types.SimpleNamespace(weight_block_size=(128, 128))
+    op = Fp8Dequantize(types.SimpleNamespace(quantization_config=qcfg))
+    out = op.convert({"weight$": [q], "weight_scale_inv": [scale_inv]}, full_layer_name="w")["w"]
+    save(name, q=codes.numpy(), scale_inv=scale_inv.numpy(), w=out.float().numpy())
+
+
 def tiny_model_config():
     return Qwen3MoeConfig(
         vocab_size=4096, hidden_size=512, intermediate_size=1024, num_hidden_layers=2,
@@ -214,6 +228,13 @@ def tiny_model_backend_crosscheck():
 
 
 if __name__ == "__main__":
+    only = set(sys.argv[1:])  # file names to (re)generate; none given = all
+    if only:
+        if "fp8_weight_dequant.npz" in only:
+            weight_dequant_case("fp8_weight_dequant.npz", seed=8)
+        if only - {"fp8_weight_dequant.npz"}:
+            raise SystemExit("selective generation is offered for fp8_weight_dequant.npz only; run without arguments")
+        sys.exit(0)
     attention_case("attn_d64.npz", hq=8, hkv=2, d=64, page=16, ctx_lens=[1, 16, 17, 95, 130, 64],
                    share_first_pages=3, seed=1)
     attention_case("attn_d128.npz", hq=16, hkv=2, d=128, page=16, ctx_lens=[150, 33, 129],
@@ -222,5 +243,6 @@ if __name__ == "__main__":
     router_case("route_e16k4.npz", T=64, H=32, E=16, K=4, seed=4)
     experts_case("experts_dense.npz", T=24, H=64, I=32, E=8, K=2, seed=5)
     weight_quant_case("fp8_weight_quant.npz", seed=6)
+    weight_dequant_case("fp8_weight_dequant.npz", seed=8)
     tiny_model_case("c1_tiny.npz")
     print("backend cross-check (first, next):", tiny_model_backend_crosscheck())

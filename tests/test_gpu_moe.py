@@ -234,3 +234,31 @@ def test_bad_expert_id_is_reported(ops):
     p = ops.moe_permute(ids, 16)
     with pytest.raises(Exception, match="expert id"):
         ops.read_status(p.workspace)
+
+
+def test_padding_rows_get_no_expert_and_drop_out_of_the_layer(ops):
+    """A fixed-shape step whose trailing rows are padding (expert parallelism with unequal batches per rank):
+    the router marks them with expert id -1 and weight 0, the permutation leaves them out (row -1, fewer
+    sorted rows), and nothing is flagged as an error."""
+    T, E, K, H, n_valid = 40, 16, 4, 256, 23
+    g = torch.Generator().manual_seed(9)
+    logits = torch.randn(T, E, generator=g)
+    x = torch.randn(T, H, generator=g).bfloat16()
+    nv = torch.tensor([n_valid], dtype=torch.int32, device=DEV)
+    ids, w = ops.moe_route(logits.to(DEV), K, True, num_valid=nv)
+    rid, rw = oracle.route_ref(logits[:n_valid], K, True)
+    assert torch.equal(ids[:n_valid].cpu(), rid) and bool((ids[n_valid:] == -1).all()) and bool((w[n_valid:] == 0).all())
+    p, xq, xs = ops.moe_permute_quant(ids, x.to(DEV), E)
+    ops.read_status(p.workspace, "permute with padding rows")
+    r = oracle.permute_ref(rid, E)
+    rows = n_valid * K
+    np.testing.assert_array_equal(p.row_of_pair.cpu().numpy()[:rows], r["row_of_pair"])
+    assert bool((p.row_of_pair[rows:] == -1).all())
+    np.testing.assert_array_equal(p.sorted_pair_ids.cpu().numpy()[:rows], r["sorted_pair_ids"])
+    np.testing.assert_array_equal(p.expert_offsets.cpu().numpy(), r["expert_offsets"])
+    n = int(p.num_tiles.item())
+    np.testing.assert_array_equal(p.tiles.cpu().numpy()[:n], r["tiles"])
+    q2 = ops.moe_permute(ids, E)
+    ops.read_status(q2.workspace, "permute with padding rows")
+    assert bool((q2.row_of_pair[rows:] == -1).all())
+    np.testing.assert_array_equal(q2.row_of_pair.cpu().numpy()[:rows], r["row_of_pair"])

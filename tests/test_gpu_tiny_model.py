@@ -144,3 +144,54 @@ def test_tiny_model_teacher_forced_against_reference_tokens(ops):
     assert decided_ok == decided  # every token the margin can decide is equal
     assert agree >= 115 and agree_gold >= 115
     assert all(v < 0.2 for v in gold_rel.values())
+
+
+def test_tiny_model_free_running_greedy_through_the_backend(ops):
+    """No teacher forcing: prefill, then 32 decode steps that feed the engine's own tokens back, as the
+    scheduler runs it.  The reference's fp32 tokens must be reproduced on every row up to the first step at
+    which that row's top-1/top-2 margin in the reference run falls below the logit error measured for the row
+    (bf16 activations and e4m3 experts against an fp32 model); from there on the reference token is not
+    decidable at this precision and the rows may part ways.  Prints where each row first differs."""
+    g = golden("c1_tiny.npz")
+    lens = g["prompt_lens"].tolist()
+    flat = g["prompt_flat"].tolist()
+    prompts, o = [], 0
+    for n in lens:
+        prompts.append(flat[o:o + n])
+        o += n
+    tokens = g["tokens"]                      # [33, 4]: first tokens, then 32 steps
+    margin = g["top2"][..., 0] - g["top2"][..., 1]  # [32, 4]: margin of the logits that chose tokens[s + 1]
+    model = build_models()
+    eng_mod, backend_mod = pkg("engine"), pkg("backend")
+    engine = eng_mod.engine_from_hf(model, num_blocks=128, max_batch=4, max_pages_per_seq=16, device=DEV)
+    backend = backend_mod.B200Backend(engine, max_new_tokens=40)
+    batch, cur = None, []
+    for p in prompts:
+        kv, first, n = backend.prefill(p, "s")
+        cur.append(first)
+        batch = backend.splice_into_batched(batch, kv, n)
+    mine = [list(cur)]
+    err = None
+    for s in range(32):
+        nxt, batch = backend.decode_step_batched(torch.tensor(cur).view(4, 1), batch, None, None)
+        if s == 0 and cur == tokens[0].tolist():
+            # same inputs as the reference at this step: the logit error of every row, measured
+            gl = torch.from_numpy(g["logits_step0"])
+            err = (engine.last_logits.float().cpu() - gl).abs().amax(dim=1).tolist()
+        cur = [int(t) for t in nxt]
+        mine.append(list(cur))
+    engine.check_status("free-running decode")
+    mine = np.array(mine)
+    assert err is not None, f"first tokens differ from the reference: {mine[0].tolist()} vs {tokens[0].tolist()}"
+    report = []
+    for b in range(4):
+        undecided = np.nonzero(margin[:, b] < err[b])[0]
+        limit = int(undecided[0]) if len(undecided) else 32   # decode steps 0..limit-1 are decidable
+        differs = np.nonzero(mine[:, b] != tokens[:, b])[0]
+        first_diff = int(differs[0]) - 1 if len(differs) else None  # as a decode step (entry 0 is the prefill token)
+        report.append((b, round(err[b], 4), limit, first_diff))
+        assert first_diff is None or first_diff >= limit, (
+            f"row {b}: token of decode step {first_diff} differs from the reference although every margin up to "
+            f"step {limit} exceeds the row's logit error {err[b]:.4f}")
+    print("\nconfig 1 free-running: (row, logit error at step 0, first undecidable step, first differing step) = "
+          + ", ".join(str(r) for r in report))

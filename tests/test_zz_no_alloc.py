@@ -12,7 +12,8 @@ import ctypes
 import pytest
 import torch
 
-from conftest import pkg
+from conftest import pkg, rel_err
+import oracle
 from test_gpu_attention import build_case
 
 pytestmark = pytest.mark.gpu
@@ -47,6 +48,42 @@ def test_static_scratch_entry_matches_workspace_entry_twice_in_a_row(ops):
         err = float((out.float() - ref.float()).abs().max() / ref.float().abs().max())
         assert err < 1e-2
         assert torch.equal(out, ref)
+
+
+def test_static_scratch_entry_against_the_oracle_on_a_large_batch_without_a_status_word(ops):
+    """128 rows: above the batch size at which the workspace entry point switches to another pipeline shape
+    (three shallow CTAs per SM up to 96 rows, two deeper ones above; this entry point always takes the second),
+    so here the comparison is with the CPU oracle as well, and the status word is left out (NULL is allowed:
+    findings are then not recorded)."""
+    lib = pkg("_lib").load()
+    rng = torch.Generator().manual_seed(5)
+    lens = torch.randint(1, 700, (128,), generator=rng).tolist()
+    q, kp, vp, table, ctx = build_case(128, 32, 4, 128, lens, seed=23)
+    ref = oracle.paged_attn_ref(q, kp, vp, table, ctx, 128 ** -0.5)
+    q, kp, vp, table, ctx = [t.to(DEV) for t in (q, kp, vp, table, ctx)]
+    out = torch.full_like(q, float("nan"))
+    B, Hq, D = q.shape
+    rc = lib.b200_paged_attn_decode_static(
+        q.data_ptr(), kp.data_ptr(), vp.data_ptr(), table.data_ptr(), ctx.data_ptr(), out.data_ptr(), None,
+        B, Hq, 4, D, 16, kp.shape[0], table.shape[1], ctypes.c_float(128 ** -0.5), 128,
+        torch.cuda.current_stream().cuda_stream)
+    assert rc == 0, lib.b200_last_error_detail()
+    torch.cuda.synchronize()
+    assert rel_err(out, ref) < 1e-2
+    ws = ops.paged_attn_workspace(B, Hq, D, table.shape[1], 16, 128, DEV)
+    same = ops.paged_attn_decode(q, kp, vp, table, ctx, 128 ** -0.5, 128, ws)
+    assert torch.equal(out, same)  # 128 rows take the same pipeline shape in both entry points
+
+    # a small batch goes through different pipeline shapes in the two entry points: equal within the bound
+    lens = [900, 5, 128, 33, 1500, 16, 257, 1024]
+    q, kp, vp, table, ctx = build_case(8, 32, 4, 128, lens, seed=24)
+    ref = oracle.paged_attn_ref(q, kp, vp, table, ctx, 128 ** -0.5)
+    q, kp, vp, table, ctx = [t.to(DEV) for t in (q, kp, vp, table, ctx)]
+    out = torch.full_like(q, float("nan"))
+    status = torch.zeros(64, dtype=torch.int32, device=DEV)
+    assert _call_static(lib, q, kp, vp, table, ctx, out, status, 128 ** -0.5, 256) == 0
+    ops.read_status(status, "static entry")
+    assert rel_err(out, ref) < 1e-2
 
 
 def test_static_scratch_entry_refuses_what_does_not_fit(ops):
