@@ -11,9 +11,11 @@
 // One persistent CTA per SM, 3 warpgroups (12 warps).  Warpgroup 0 holds the two
 // single-thread roles and gives most of its registers back (setmaxnreg) so that
 // the 8 promotion warps can hold 128 accumulators plus two TMEM loads in flight:
-//   warp 0      TMA producer: per 128-wide K block one A box (128 sorted rows x
-//               128 B) and two W boxes (128 rows x 128 B each) into a 4-stage
-//               ring, 128-byte swizzle, completion by mbarrier bytes.
+//   warp 0      TMA producer: per 128-wide K block one A box (the tile's sorted rows x
+//               128 B; 32, 64 or 128 rows, whichever first covers the tile, so a decode
+//               batch with a dozen rows per expert does not pull 128 through the ring)
+//               and two W boxes (128 rows x 128 B each) into a 4-stage ring, 128-byte
+//               swizzle, completion by mbarrier bytes.
 //   warp 1      MMA issuer: one thread issues 4 x tcgen05.mma (M128 N256 K32,
 //               kind::f8f6f4) per K block into one of two 256-column TMEM
 //               accumulators and commits to the stage-empty and
@@ -88,8 +90,9 @@ __device__ __forceinline__ bool tile_ok(const MoeTile& t, const GemmParams& p) {
 
 template <int MODE>
 __global__ void __launch_bounds__(kGemmThreads, 1)
-moe_fp8_gemm_kernel(const __grid_constant__ CUtensorMap a_map,
-                    const __grid_constant__ CUtensorMap b_map, const GemmParams p) {
+moe_fp8_gemm_kernel(const __grid_constant__ CUtensorMap a_map, const __grid_constant__ CUtensorMap a_map64,
+                    const __grid_constant__ CUtensorMap a_map32, const __grid_constant__ CUtensorMap b_map,
+                    const GemmParams p) {
 #ifdef B200_DEVICE_OK
   extern __shared__ uint8_t smem_raw[];
   const uint32_t ring = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -135,6 +138,8 @@ moe_fp8_gemm_kernel(const __grid_constant__ CUtensorMap a_map,
     // ------------------------------------------------------------ TMA ------
     if (lane == 0) {
       tma_prefetch_desc(&a_map);
+      tma_prefetch_desc(&a_map64);
+      tma_prefetch_desc(&a_map32);
       tma_prefetch_desc(&b_map);
       uint32_t it = 0;
       bool alive = true;
@@ -159,13 +164,17 @@ moe_fp8_gemm_kernel(const __grid_constant__ CUtensorMap a_map,
         // tiled weights: it is the contiguous 16 KiB block number (expert*sblocks + nb)*k_blocks + kb
         const int b_row0 = p.tiled ? (tile.expert * sblocks + nb0) * p.k_blocks * 128 : tile.expert * p.n_rows + nb0 * 128;
         const int b_row1 = p.tiled ? (tile.expert * sblocks + nb1) * p.k_blocks * 128 : tile.expert * p.n_rows + nb1 * 128;
+        // The A box only needs the tile's own rows.  The MMA still reads 128 rows of the stage; what an earlier
+        // tile left in the rows below the box only reaches accumulator rows that are never stored.
+        const CUtensorMap* amap = tile.rows <= 32 ? &a_map32 : (tile.rows <= 64 ? &a_map64 : &a_map);
+        const uint32_t stage_bytes = (tile.rows <= 32 ? 32u : (tile.rows <= 64 ? 64u : 128u)) * kBlockK + kBBytes;
         for (int kb = 0; kb < p.k_blocks; ++kb, ++it) {
           const uint32_t slot = it % kGemmStages, phase = (it / kGemmStages) & 1;
           alive = mbar_wait(bar_empty + 8 * slot, phase ^ 1, p.err);
           if (!alive) break;
           const uint32_t sa = ring + slot * kStageBytesG, sb = sa + kABytes;
-          mbar_arrive_expect_tx(bar_full + 8 * slot, kStageBytesG);
-          tma_load_2d(sa, &a_map, bar_full + 8 * slot, kb * kBlockK, tile.row0);
+          mbar_arrive_expect_tx(bar_full + 8 * slot, stage_bytes);
+          tma_load_2d(sa, amap, bar_full + 8 * slot, kb * kBlockK, tile.row0);
           const int bx = p.tiled ? 0 : kb * kBlockK, by = p.tiled ? kb * 128 : 0;
           tma_load_2d(sb, &b_map, bar_full + 8 * slot, bx, b_row0 + by);
           tma_load_2d(sb + kBBytes / 2, &b_map, bar_full + 8 * slot, bx, b_row1 + by);
@@ -355,15 +364,27 @@ moe_fp8_gemm_kernel(const __grid_constant__ CUtensorMap a_map,
 #endif
 }
 
+// The three A maps: boxes of 128, 64 and 32 rows over the same activation matrix.
+struct AMaps {
+  CUtensorMap m128, m64, m32;
+};
+static int make_a_maps(const void* a, int rows, int cols, AMaps* out) {
+  int rc = get_tensor_map_2d(a, rows, cols, 1, 128, 128, &out->m128);
+  if (rc) return rc;
+  rc = get_tensor_map_2d(a, rows, cols, 1, 64, 128, &out->m64);
+  if (rc) return rc;
+  return get_tensor_map_2d(a, rows, cols, 1, 32, 128, &out->m32);
+}
+
 template <int MODE>
-static int launch_gemm(const CUtensorMap& a_map, const CUtensorMap& b_map, const GemmParams& p,
+static int launch_gemm(const AMaps& a, const CUtensorMap& b_map, const GemmParams& p,
                        cudaStream_t st) {
   int rc = ensure_dynamic_smem(reinterpret_cast<const void*>(&moe_fp8_gemm_kernel<MODE>), kGemmSmem);
   if (rc) return rc;
   int grid = 148;
   rc = device_sm_count(&grid);
   if (rc) return rc;
-  moe_fp8_gemm_kernel<MODE><<<grid, kGemmThreads, kGemmSmem, st>>>(a_map, b_map, p);
+  moe_fp8_gemm_kernel<MODE><<<grid, kGemmThreads, kGemmSmem, st>>>(a.m128, a.m64, a.m32, b_map, p);
   B200_CUDA(cudaGetLastError());
   return 0;
 }
@@ -389,8 +410,9 @@ extern "C" int b200_moe_fp8_gemm_gate_up(const void* xq, const float* x_scale, c
   int rc = check_device(nullptr);
   if (rc) return rc;
   if (num_rows == 0) return 0;
-  CUtensorMap a_map, b_map;
-  rc = get_tensor_map_2d(xq, num_rows, hidden, 1, 128, 128, &a_map);
+  AMaps a_map;
+  CUtensorMap b_map;
+  rc = make_a_maps(xq, num_rows, hidden, &a_map);
   if (rc) return rc;
   B200_REQUIRE(weight_layout == 0 || weight_layout == 1, "moe_fp8_gemm_gate_up: weight_layout %d is neither 0 nor 1",
                weight_layout);
@@ -433,8 +455,9 @@ static int gemm_down_impl(const void* hq, const float* h_scale, const void* w2, 
   int rc = check_device(nullptr);
   if (rc) return rc;
   if (num_rows == 0) return 0;
-  CUtensorMap a_map, b_map;
-  rc = get_tensor_map_2d(hq, num_rows, inter, 1, 128, 128, &a_map);
+  AMaps a_map;
+  CUtensorMap b_map;
+  rc = make_a_maps(hq, num_rows, inter, &a_map);
   if (rc) return rc;
   B200_REQUIRE(weight_layout == 0 || weight_layout == 1, "moe_fp8_gemm_down: weight_layout %d is neither 0 nor 1",
                weight_layout);

@@ -53,3 +53,29 @@ def paged_attn_ref(q, k_pool, v_pool, block_table, ctx_lens, scale: float) -> to
         p = torch.softmax(s, dim=-1, dtype=torch.float32)
         out[b] = torch.einsum("hl,hld->hd", p, v)
     return out
+
+
+def paged_prefill_ref(q, k_pool, v_pool, table_row, first_pos: int, scale: float) -> torch.Tensor:
+    """Causal attention of a chunk of R consecutive prompt tokens (positions first_pos ..) over the pages of
+    their sequence, fp32, output [R, Hq, D].
+
+    This is what the reference computes for a prompt suffix on top of a cached prefix: the prefix pages are
+    gathered into a dense cache (``blocks_to_dynamic_cache``, src/inference_server/kv_cache/hf_format.py:21-45)
+    and the suffix runs through the model with a causal mask
+    (src/inference_server/backends/torch_backend.py:107-147 -> transformers ``eager_attention_forward`` with the
+    additive causal mask: token t is visible to the row of position p iff t <= p).  The K/V of the chunk itself
+    are expected in their page slots already.
+    """
+    q = q.detach().cpu().float()
+    R, Hq, D = q.shape
+    Hkv = k_pool.shape[1]
+    rep = Hq // Hkv
+    L = first_pos + R
+    ids = [int(b) for b in table_row]
+    k = gather_pages(k_pool.detach().cpu(), ids, L).float().repeat_interleave(rep, dim=0)  # [Hq, L, D]
+    v = gather_pages(v_pool.detach().cpu(), ids, L).float().repeat_interleave(rep, dim=0)
+    s = torch.einsum("rhd,hld->hrl", q, k) * scale
+    visible = torch.arange(L).view(1, 1, L) <= (first_pos + torch.arange(R)).view(1, R, 1)
+    s = s.masked_fill(~visible, float("-inf"))
+    p = torch.softmax(s, dim=-1, dtype=torch.float32)
+    return torch.einsum("hrl,hld->rhd", p, v).contiguous()

@@ -80,6 +80,38 @@ def attention_case(name, hq, hkv, d, page, ctx_lens, share_first_pages, seed):
          ctx_lens=np.array(ctx_lens, dtype=np.int32), out=out, scale=np.float32(d ** -0.5))
 
 
+def prefill_attention_case(name, hq, hkv, d, page, prefix, chunk, seed):
+    """A prompt suffix of `chunk` tokens on top of `prefix` cached tokens: pools and gather by the reference's
+    BlockManager / blocks_to_dynamic_cache, attention by transformers eager_attention_forward with the additive
+    causal mask the model builds for a suffix (row of position p sees tokens 0..p)."""
+    g = torch.Generator().manual_seed(seed)
+    L = prefix + chunk
+    n_pages = (L + page - 1) // page
+    bm = BlockManager(n_pages + 5, page, layer_shapes=[(hkv, d)], device="cpu", dtype=torch.float32)
+    bm.k_pools[0].copy_(torch.randn(bm.k_pools[0].shape, generator=g))
+    bm.v_pools[0].copy_(torch.randn(bm.v_pools[0].shape, generator=g))
+    ids = list(range(n_pages + 5))
+    random.Random(seed).shuffle(ids)
+    ids = ids[:n_pages]
+    blocks, left = [], L
+    for bid in ids:
+        blk = bm.get_block(bid)
+        blk.token_ids = list(range(min(page, left)))  # only the count matters
+        left -= page
+        blocks.append(blk)
+    cache, n = blocks_to_dynamic_cache(blocks)
+    assert n == L
+    k, v = cache.layers[0].keys, cache.layers[0].values  # [1, Hkv, L, D]
+    q = torch.randn(chunk, hq, d, generator=g)
+    pos = prefix + torch.arange(chunk)
+    mask = torch.where(torch.arange(L).view(1, L) <= pos.view(chunk, 1), 0.0, float("-inf")).view(1, 1, chunk, L)
+    module = types.SimpleNamespace(num_key_value_groups=hq // hkv, training=False)
+    o, _ = hfm.eager_attention_forward(module, q.permute(1, 0, 2).unsqueeze(0), k, v, mask, scaling=d ** -0.5)
+    save(name, q=q.numpy(), k_pool=bm.k_pools[0].numpy(), v_pool=bm.v_pools[0].numpy(),
+         table_row=np.array(ids, dtype=np.int32), first_pos=np.int32(prefix), out=o[0].numpy(),
+         scale=np.float32(d ** -0.5))
+
+
 def router_case(name, T, H, E, K, seed):
     torch.manual_seed(seed)
     cfg = types.SimpleNamespace(num_experts_per_tok=K, num_experts=E, norm_topk_prob=True, hidden_size=H)
@@ -232,13 +264,16 @@ if __name__ == "__main__":
     if only:
         if "fp8_weight_dequant.npz" in only:
             weight_dequant_case("fp8_weight_dequant.npz", seed=8)
-        if only - {"fp8_weight_dequant.npz"}:
-            raise SystemExit("selective generation is offered for fp8_weight_dequant.npz only; run without arguments")
+        if "attn_prefill_d64.npz" in only:
+            prefill_attention_case("attn_prefill_d64.npz", hq=8, hkv=2, d=64, page=16, prefix=37, chunk=45, seed=9)
+        if only - {"fp8_weight_dequant.npz", "attn_prefill_d64.npz"}:
+            raise SystemExit("selective generation is offered for the two newest fixtures only; run without arguments")
         sys.exit(0)
     attention_case("attn_d64.npz", hq=8, hkv=2, d=64, page=16, ctx_lens=[1, 16, 17, 95, 130, 64],
                    share_first_pages=3, seed=1)
     attention_case("attn_d128.npz", hq=16, hkv=2, d=128, page=16, ctx_lens=[150, 33, 129],
                    share_first_pages=2, seed=2)
+    prefill_attention_case("attn_prefill_d64.npz", hq=8, hkv=2, d=64, page=16, prefix=37, chunk=45, seed=9)
     router_case("route_e128k8.npz", T=96, H=64, E=128, K=8, seed=3)
     router_case("route_e16k4.npz", T=64, H=32, E=16, K=4, seed=4)
     experts_case("experts_dense.npz", T=24, H=64, I=32, E=8, K=2, seed=5)

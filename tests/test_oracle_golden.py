@@ -142,3 +142,18 @@ def test_fp32_until_quantised_stays_close_to_the_bf16_rounding_of_the_hf_experts
     print(f"fp32-until-quantised vs bf16-rounded: max err / max |out| = {err:.2e}, identical h codes {same_codes:.3f}")
     assert err < 4e-2
     assert same_codes > 0.9
+
+
+def test_prompt_chunk_attention_matches_hf_eager_attention_with_causal_mask():
+    """45 suffix tokens on 37 cached ones: pages gathered by the reference's blocks_to_dynamic_cache, attention
+    by transformers eager_attention_forward under the causal mask."""
+    g = golden("attn_prefill_d64.npz")
+    t = lambda k: torch.from_numpy(g[k])
+    out = oracle.paged_prefill_ref(t("q"), t("k_pool"), t("v_pool"), g["table_row"].tolist(), int(g["first_pos"]),
+                                   float(g["scale"]))
+    np.testing.assert_allclose(out.numpy(), g["out"], rtol=2e-5, atol=2e-6)
+    # and row by row it is the decode oracle at that row's length
+    row = 17
+    one = oracle.paged_attn_ref(t("q")[row:row + 1], t("k_pool"), t("v_pool"), t("table_row").view(1, -1),
+                                torch.tensor([int(g["first_pos"]) + row + 1]), float(g["scale"]))
+    np.testing.assert_allclose(out[row].numpy(), one[0].numpy(), rtol=1e-5, atol=1e-6)
