@@ -95,6 +95,25 @@ int b200_paged_attn_decode_pairs(const void* q, const void* k_pool, const void* 
                                  int max_pages_per_seq, float scale, int split_tokens, void* stream);
 
 /*
+ * Replaces, for a prompt or the uncached suffix of one: the page gather of a cached prefix into a dense
+ * cache (kv_cache/hf_format.py:21-45) and the causally masked prompt attention inside the model forward
+ * (torch_backend.py:107-147; chunked prefill: scheduler.py:312-353).  A chunk of num_tokens consecutive
+ * prompt tokens of ONE sequence, at positions first_position .., whose K/V are already in their page slots,
+ * attends to the sequence's pages in place; the row of position p sees tokens 0..p.  One CTA covers 128 rows
+ * of the score matrix (128 / group consecutive positions x the group's query heads), so a page is fetched once
+ * per 128 rows; no split over the context, no workspace.
+ *
+ *   q, out            [num_tokens, num_q_heads, head_dim] bf16
+ *   block_table_row   [max_pages_per_seq] int32: the sequence's pages
+ *   status_word       optional device int32 for device-side findings (bad block id, position past the table)
+ * bf16, page_size 16; head_dim 128 with 8 or 16 query heads per kv head, or head_dim 64 with 4.
+ */
+int b200_paged_attn_prefill(const void* q, const void* k_pool, const void* v_pool,
+                            const int32_t* block_table_row, void* out, void* status_word, int num_tokens,
+                            int first_position, int num_q_heads, int num_kv_heads, int head_dim,
+                            int page_size, int num_blocks, int max_pages_per_seq, float scale, void* stream);
+
+/*
  * Paged decode attention for callers that cannot allocate device memory.
  * No counterpart in the reference: it exists for hosts of this library that own
  * no allocator at the point of the call - a server whose device memory was
@@ -146,6 +165,44 @@ int b200_kv_append(const void* k_new, const void* v_new, void* k_pool, void* v_p
                    const int32_t* block_table, const int32_t* positions, void* status_word,
                    int batch, int num_kv_heads, int head_dim, int page_size, int num_blocks,
                    int max_pages_per_seq, int dtype, void* stream);
+
+/* ----------------------------------------------------- dense projections -- */
+
+/*
+ * Replaces: the bf16 linear layers of the model forward called at torch_backend.py:314-320 (transformers
+ * Qwen3MoeAttention q/k/v/o projections, the router's gate projection, lm_head), which the reference runs as
+ * library GEMMs.  y[m, n] = sum_k x[m, k] * w[n, k] with fp32 accumulation on the tensor cores (tcgen05).
+ * The weight tile is the M side of the MMA and the step's rows the N side, so a decode batch streams the
+ * weights once; with few weight tiles K is split over the CTAs of a thread-block cluster, whose fp32 partial
+ * tiles meet in the workspace and are summed in rank order (deterministic, no atomics).
+ *
+ *   x [num_rows, in_features] bf16,  w [out_features, in_features] bf16 (the checkpoint layout),
+ *   y [num_rows, out_features] bf16, 8-byte aligned.  in_features must be a multiple of 64; x and w 16-byte
+ *   aligned.
+ *   workspace  b200_dense_gemm_workspace_bytes(num_rows, out_features) bytes, 16-byte aligned, or NULL: the
+ *              product is then computed without a K split (slower when there are few weight tiles)
+ *   k_split    0 = chosen by the library; 1, 2, 4 or 8 = CTAs that share one weight tile
+ *   status_word  optional device int32 for a bounded wait that ran out
+ */
+size_t b200_dense_gemm_workspace_bytes(int num_rows, int out_features);
+int b200_dense_gemm_bf16(const void* x, const void* w, void* y, void* workspace, size_t workspace_bytes,
+                         void* status_word, int num_rows, int out_features, int in_features, int k_split,
+                         void* stream);
+
+/*
+ * Replaces: lm_head followed by the argmax over the vocabulary (torch_backend.py:314-321:
+ * `outputs.logits[:, -1, :].argmax(dim=-1)`).  The same GEMM with a running arg-max per row kept in registers
+ * across the vocabulary tiles; the [num_rows, vocab] logits are never written.  The largest fp32 logit wins,
+ * equal logits go to the lower token id.
+ *
+ *   x [num_rows, hidden] bf16 (final-normed hidden states), w [vocab_size, hidden] bf16,
+ *   next_tokens [num_rows] int64.  num_rows <= 256 per call; hidden a multiple of 64.
+ *   workspace  b200_lm_head_argmax_workspace_bytes() bytes, 16-byte aligned (per-CTA candidates)
+ */
+size_t b200_lm_head_argmax_workspace_bytes(void);
+int b200_lm_head_argmax(const void* x, const void* w, int64_t* next_tokens, void* workspace,
+                        size_t workspace_bytes, void* status_word, int num_rows, int vocab_size,
+                        int hidden, void* stream);
 
 /* ----------------------------------------------------- fused step glue -- */
 

@@ -26,8 +26,13 @@ SIGNATURES = {
         [c_void_p] * 7 + [c_size_t] + [c_int] * 7 + [c_float, c_int, c_int, c_void_p],
     ),
     "b200_paged_attn_decode_pairs": (c_int, [c_void_p] * 7 + [c_size_t] + [c_int] * 7 + [c_float, c_int, c_void_p]),
+    "b200_paged_attn_prefill": (c_int, [c_void_p] * 6 + [c_int] * 8 + [c_float, c_void_p]),
     "b200_paged_attn_decode_static": (c_int, [c_void_p] * 7 + [c_int] * 7 + [c_float, c_int, c_void_p]),
     "b200_kv_append": (c_int, [c_void_p] * 7 + [c_int] * 7 + [c_void_p]),
+    "b200_dense_gemm_workspace_bytes": (c_size_t, [c_int, c_int]),
+    "b200_dense_gemm_bf16": (c_int, [c_void_p] * 4 + [c_size_t, c_void_p] + [c_int] * 4 + [c_void_p]),
+    "b200_lm_head_argmax_workspace_bytes": (c_size_t, []),
+    "b200_lm_head_argmax": (c_int, [c_void_p] * 4 + [c_size_t, c_void_p] + [c_int] * 3 + [c_void_p]),
     "b200_add_rmsnorm": (c_int, [c_void_p, c_void_p, c_void_p, c_float, c_int, c_int, c_void_p, c_void_p]),
     "b200_qk_norm_rope_append": (c_int, [c_void_p] * 11 + [c_int] * 4 + [c_float] + [c_int] * 4 + [c_void_p]),
     "b200_moe_route": (c_int, [c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p]),

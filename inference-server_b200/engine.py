@@ -5,18 +5,18 @@ This is the model-forward side of the reference's hot entry
 (src/inference_server/backends/torch_backend.py:305-322), rebuilt so that a
 step reads the KV page pools in place instead of a dense left-padded cache:
 
-  per layer   fused q/k/v projection
+  per layer   fused q/k/v projection (``b200_dense_gemm_bf16``)
               -> ``b200_qk_norm_rope_append`` (per-head q/k RMSNorm, RoPE, page write)
-              -> ``b200_paged_attn_decode`` -> o projection
-              -> ``b200_add_rmsnorm`` (residual + RMSNorm) -> router projection
+              -> ``b200_paged_attn_decode`` -> o projection (``b200_dense_gemm_bf16``)
+              -> ``b200_add_rmsnorm`` (residual + RMSNorm) -> router projection (``b200_dense_gemm_bf16``)
               -> ``b200_moe_fp8_forward_add_rmsnorm`` (route, permute+quantise, two
                  grouped GEMMs, combine + residual + the next layer's input norm)
-  final       lm_head -> argmax
+  final       ``b200_lm_head_argmax`` (lm_head with the arg-max over the vocabulary in its epilogue)
 
-The element-wise glue, paged attention and the FP8 MoE layer are this package's
-CUDA kernels; the dense projections are library GEMMs (torch.matmul, bf16).  The whole step is captured once per batch
-size in a CUDA graph; block table, context lengths and input tokens live in
-static device buffers that the graph reads.
+Every kernel of the step is this package's own: the element-wise glue, paged attention, the FP8 MoE layer and
+the dense bf16 projections (tcgen05); the one library call left is the embedding row gather.  The whole step is
+captured once per batch size in a CUDA graph; block table, context lengths and input tokens live in static
+device buffers that the graph reads.
 
 Pools use the reference layout [num_blocks, n_kv_heads, 16, head_dim] per layer
 (src/inference_server/kv_cache/block_manager.py:33-49) and can be the very
@@ -143,11 +143,16 @@ class DecodeEngine:
                  embed: torch.Tensor | None = None, lm_head: torch.Tensor | None = None,
                  final_norm: torch.Tensor | None = None, k_pools=None, v_pools=None, use_graphs: bool = True,
                  split_tokens: int | None = None, ep_group=None, ep_capacity: int | None = None,
-                 ep_transport: str = "p2p", graph_buckets: bool = True):
+                 ep_transport: str = "p2p", graph_buckets: bool = True, keep_logits: bool = False):
         if not torch.cuda.is_available():
             raise RuntimeError("DecodeEngine needs a CUDA device; this path has no CPU implementation")
         self.cfg = cfg
         self.device = torch.device(device)
+        # The step picks its next tokens inside the lm_head kernel and never writes the [batch, vocab] logits.
+        # With keep_logits they are computed as well, by a second pass over lm_head, into `last_logits` (for
+        # tests and inspection; set before the first step, the graphs are captured with or without it).
+        self.keep_logits = keep_logits
+        self.last_logits = None
         self.max_batch = max_batch
         self.max_pages = max_pages_per_seq
         self.num_blocks = num_blocks
@@ -193,6 +198,10 @@ class DecodeEngine:
         self.attn_ws = ops.paged_attn_workspace(max_batch, cfg.q_heads, cfg.head_dim, max_pages_per_seq, PAGE,
                                                 self.split_tokens, self.device)
         self.moe_ws = ops.moe_fp8_workspace(max_batch, cfg.experts, cfg.top_k, cfg.hidden, cfg.moe_inter, self.device)
+        self.gemm_status = torch.zeros(64, dtype=torch.int32, device=self.device)  # dense projections, lm_head
+        widest = max((cfg.q_heads + 2 * cfg.kv_heads) * cfg.head_dim, cfg.hidden, cfg.experts)
+        self.gemm_ws = ops.dense_gemm_workspace(min(max_batch, 256), widest, self.device)  # K-split partial tiles
+        self.argmax_ws = ops.lm_head_argmax_workspace(self.device)
         self._graphs: dict[int, torch.cuda.CUDAGraph] = {}
         # rows of the current pass that are real (expert parallelism only): the router gives the rows beyond
         # it no expert, so they send nothing and receive nothing
@@ -229,20 +238,24 @@ class DecodeEngine:
             # The exchange has one shape, so there is one graph; it is built here, where every rank is (its
             # warm-up runs are real exchanges and must happen on all ranks together), with padding rows only.
             self._build_graph(self.max_batch, pad_from=0)
-        # per layer: qk_norm_rope_append, attention + split reduce, add_rmsnorm, route, rank, scatter+quant, gemm x2,
-        # combine+norm; + the first norm
-        self.kernel_launches_per_step = cfg.layers * 10 + 1
+        # per layer: qkv GEMM, qk_norm_rope_append, attention + split reduce, o GEMM, add_rmsnorm, router GEMM, route,
+        # rank, scatter+quant, expert GEMM x2, combine+norm; + the first norm, lm_head with arg-max and its fold
+        self.kernel_launches_per_step = cfg.layers * 13 + 3
         if self.ep_world > 1:
             # the local re-sort of received rows (rank + scatter + row gather), and with the peer-memory
             # transport the two flag exchanges
             self.kernel_launches_per_step += cfg.layers * (3 + (2 if ep_transport == "p2p" else 0))
 
     # ------------------------------------------------------------------ step
-    def _forward(self, tokens, pos, table, attn_ws, moe_ws, split_tokens, ep: bool, pairs: bool = False) -> torch.Tensor:
+    def _forward(self, tokens, pos, table, attn_ws, moe_ws, split_tokens, ep: bool, pairs: bool = False,
+                 chunk_of: tuple[int, int] | None = None) -> torch.Tensor:
         """The layer stack for R rows: row i is token `tokens[i]` at position `pos[i]` of the sequence whose
         pages are `table[i]`; it attends to positions 0..pos[i].  Decode passes one row per sequence; a prompt
         chunk passes one row per prompt token with the sequence's table repeated - the same kernels, reading
-        the pages in place either way.  Returns the final normed hidden states [R, hidden].
+        the pages in place either way.  `chunk_of` = (first position, rows): the first `rows` rows are
+        consecutive prompt tokens of ONE sequence starting there, and attention runs as the tiled causal kernel
+        (a page fetched once per 128 score rows) instead of one row per token.
+        Returns the final normed hidden states [R, hidden].
 
         Per layer: qkv GEMM, fused q/k norm + RoPE + page write, paged attention, o GEMM, fused
         residual+RMSNorm, router GEMM, FP8 MoE whose combine adds into the residual stream `x`
@@ -254,14 +267,20 @@ class DecodeEngine:
         x = self.embed[tokens]
         h = ops.add_rmsnorm(x, None, self.layers[0].ln1, cfg.rms_eps)
         for li, w in enumerate(self.layers):
-            qkv = torch.matmul(h, w.wqkv.t()).view(R, Hq + 2 * Hkv, D)
+            qkv = ops.dense_gemm(h, w.wqkv, status=self.gemm_status, workspace=self.gemm_ws).view(R, Hq + 2 * Hkv, D)
             q = ops.qk_norm_rope_append(qkv, w.q_norm, w.k_norm, self.cos, self.sin, pos, table, self.k_pools[li],
                                         self.v_pools[li], Hq, cfg.rms_eps, attn_ws)
-            attn = ops.paged_attn_decode(q, self.k_pools[li], self.v_pools[li], table, new_len, self.scale,
-                                         split_tokens, attn_ws, pairs=pairs)
-            o = torch.matmul(attn.view(R, Hq * D), w.wo.t())
+            if chunk_of is not None:
+                first_pos, n_real = chunk_of
+                attn = q.new_zeros(R, Hq, D) if n_real < R else torch.empty_like(q)
+                ops.paged_attn_prefill(q[:n_real], self.k_pools[li], self.v_pools[li], table[0], first_pos, self.scale,
+                                       attn_ws, out=attn[:n_real])
+            else:
+                attn = ops.paged_attn_decode(q, self.k_pools[li], self.v_pools[li], table, new_len, self.scale,
+                                             split_tokens, attn_ws, pairs=pairs)
+            o = ops.dense_gemm(attn.view(R, Hq * D), w.wo, status=self.gemm_status, workspace=self.gemm_ws)
             h2 = ops.add_rmsnorm(x, o, w.ln2, cfg.rms_eps)
-            logits = torch.matmul(h2, w.router.t())  # bf16, routed as is
+            logits = ops.dense_gemm(h2, w.router, status=self.gemm_status, workspace=self.gemm_ws)  # bf16, routed as is
             nxt = self.layers[li + 1].ln1 if li + 1 < len(self.layers) else self.final_norm
             # MoE layer; its combine also adds into the residual stream and applies the next norm
             if ep:
@@ -290,6 +309,7 @@ class DecodeEngine:
         for rows, (_, ws) in self._attn_by_rows.items():
             ops.read_status(ws, f"{where}: attention ({rows} rows)")
         ops.read_status(self.moe_ws, f"{where}: MoE")
+        ops.read_status(self.gemm_status, f"{where}: dense projections")
         for name in ("_prefill_attn_ws", "_prefill_moe_ws"):
             ws = getattr(self, name, None)
             if ws is not None:
@@ -329,8 +349,9 @@ class DecodeEngine:
         split, attn_ws = self._attn_for(B)
         h = self._forward(self.tokens[:B], self.ctx_lens[:B], self.block_table[:B], attn_ws, self.moe_ws,
                           split, self.ep_state is not None)
-        self.last_logits = torch.matmul(h, self.lm_head.t())
-        self.next_tokens[:B] = self.last_logits.argmax(dim=-1)
+        if self.keep_logits:
+            self.last_logits = ops.dense_gemm(h, self.lm_head, status=self.gemm_status)
+        ops.lm_head_argmax(h, self.lm_head, self.argmax_ws, out=self.next_tokens[:B], status=self.gemm_status)
         self.ctx_lens[:B] += 1
 
     def _ep_moe(self, h2, logits, w: LayerWeights, x, next_norm, B: int) -> torch.Tensor:
@@ -433,16 +454,17 @@ class DecodeEngine:
     # --------------------------------------------------------------- prefill
     @torch.no_grad()
     def prefill(self, token_ids: list[int], block_ids: list[int], cached_tokens: int = 0,
-                chunk: int = 256) -> tuple[int, torch.Tensor]:
+                chunk: int = 1024) -> tuple[int, torch.Tensor]:
         """Prompt pass for one sequence; writes K/V of tokens [cached_tokens, n) into `block_ids` pages.
 
-        Runs the same paged kernels as decode, in chunks of `chunk` prompt tokens: every token of a chunk is a
-        row with its own position, all rows share the sequence's block table, and attention reads the pages in
-        place (cached prefix pages included, two rows per CTA: b200_paged_attn_decode_pairs) - there is no dense
-        gather of the KV.  This replaces the
-        reference's page gather for cache hits (src/inference_server/kv_cache/hf_format.py:21-45).  The K/V
-        of a whole chunk are written to their page slots before the chunk's attention runs, and row i only
-        looks at positions <= its own, which is the causal mask.
+        Runs in chunks of `chunk` prompt tokens through the same projection, glue and MoE kernels as decode
+        (every token of a chunk is a row with its own position); attention reads the sequence's pages in place,
+        cached prefix pages included - there is no dense gather of the KV as in the reference
+        (src/inference_server/kv_cache/hf_format.py:21-45).  The K/V of a whole chunk are written to their page
+        slots before the chunk's attention runs.  Attention is the tiled causal kernel
+        (b200_paged_attn_prefill: a page fetched once per 128 score rows); for head shapes it is not built for,
+        the decode kernel with one row per token (two rows per CTA: b200_paged_attn_decode_pairs), where
+        row i only looks at positions <= its own, which is the causal mask.
         Under expert parallelism a chunk is one exchange round like a decode step: it is padded to the
         exchange's fixed shape (the engine's full batch) with rows that route nowhere, and the other ranks spend
         the round on a decode step, a chunk of their own or an idle pass.
@@ -461,15 +483,19 @@ class DecodeEngine:
                                  "page for the padding rows)")
             chunk = self.ep_state.T
         cfg = self.cfg
+        tiled = ops.paged_attn_prefill_supported(cfg.q_heads, cfg.kv_heads, cfg.head_dim, PAGE, torch.bfloat16)
         if getattr(self, "_prefill_chunk", 0) != chunk:
             self._prefill_chunk = chunk
             self._prefill_split = ops.default_split_tokens(chunk, cfg.kv_heads, self.max_pages * PAGE)
-            self._prefill_attn_ws = ops.paged_attn_workspace(chunk, cfg.q_heads, cfg.head_dim, self.max_pages, PAGE,
-                                                             self._prefill_split, self.device)
+            # the tiled kernel needs no workspace beyond a status word; the row-per-token form needs the split
+            # partials of `chunk` rows
+            self._prefill_attn_ws = torch.zeros(256, dtype=torch.uint8, device=self.device) if tiled else \
+                ops.paged_attn_workspace(chunk, cfg.q_heads, cfg.head_dim, self.max_pages, PAGE, self._prefill_split,
+                                         self.device)
             self._prefill_moe_ws = None if ep else ops.moe_fp8_workspace(chunk, cfg.experts, cfg.top_k, cfg.hidden,
                                                                          cfg.moe_inter, self.device)
-        # consecutive prompt tokens share the table, so attention takes them two rows per CTA where it can
-        pairs = ops.paged_attn_pairs_supported(cfg.q_heads, cfg.kv_heads, cfg.head_dim, PAGE, torch.bfloat16)
+        # consecutive prompt tokens share the table, so the row-per-token form takes them two rows per CTA where it can
+        pairs = not tiled and ops.paged_attn_pairs_supported(cfg.q_heads, cfg.kv_heads, cfg.head_dim, PAGE, torch.bfloat16)
         row = torch.zeros(self.max_pages, dtype=torch.int32)
         row[: len(block_ids)] = torch.tensor(block_ids, dtype=torch.int32)
         row = row.to(self.device)
@@ -491,10 +517,11 @@ class DecodeEngine:
                     self.round_hook()
                 self.n_valid.fill_(hi - lo)
             h = self._forward(tokens, pos, table, self._prefill_attn_ws, self._prefill_moe_ws, self._prefill_split,
-                              ep, pairs=pairs)
-            h_last = h[hi - lo - 1:hi - lo]
-        logits = torch.matmul(h_last, self.lm_head.t())[0]
-        return int(logits.argmax()), logits
+                              ep, pairs=pairs, chunk_of=(lo, hi - lo) if tiled else None)
+            h_last = h[hi - lo - 1:hi - lo].contiguous()
+        first = ops.lm_head_argmax(h_last, self.lm_head, self.argmax_ws, status=self.gemm_status)
+        logits = ops.dense_gemm(h_last, self.lm_head, status=self.gemm_status)[0]
+        return int(first[0]), logits
 
     # ------------------------------------------------------------- accounting
     def weight_bytes_per_step(self, experts_hit_per_layer: float | None = None) -> dict:

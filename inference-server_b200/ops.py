@@ -121,6 +121,37 @@ def paged_attn_decode(
     return out
 
 
+def paged_attn_prefill(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, table_row: torch.Tensor,
+                       first_pos: int, scale: float, status: torch.Tensor | None = None,
+                       out: torch.Tensor | None = None) -> torch.Tensor:
+    """Causal attention of a chunk of consecutive prompt tokens of one sequence over its pages.
+
+    q [R, Hq, D] (positions first_pos .. first_pos + R - 1, K/V already in their page slots); table_row
+    [max_pages] int32.  See `paged_attn_prefill_supported`."""
+    _need(q, "q", torch.bfloat16)
+    _need(k_pool, "k_pool", torch.bfloat16)
+    _need(v_pool, "v_pool", torch.bfloat16)
+    _need(table_row, "table_row", torch.int32)
+    R, Hq, D = q.shape
+    nb, Hkv, page, D2 = k_pool.shape
+    if D2 != D or v_pool.shape != k_pool.shape:
+        raise ValueError("pool shape does not match q / each other")
+    if out is None:
+        out = torch.empty_like(q)
+    rc = _lib.load().b200_paged_attn_prefill(_ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(table_row), _ptr(out),
+                                             _ptr(status), R, int(first_pos), Hq, Hkv, D, page, nb,
+                                             table_row.numel(), float(scale), _stream())
+    check(rc, "b200_paged_attn_prefill")
+    return out
+
+
+def paged_attn_prefill_supported(num_q_heads: int, num_kv_heads: int, head_dim: int, page_size: int, dtype) -> bool:
+    """Whether b200_paged_attn_prefill is built for this shape."""
+    if dtype != torch.bfloat16 or page_size != 16 or num_q_heads % num_kv_heads:
+        return False
+    return (head_dim, num_q_heads // num_kv_heads) in ((128, 8), (128, 16), (64, 4))
+
+
 def paged_attn_pairs_supported(num_q_heads: int, num_kv_heads: int, head_dim: int, page_size: int, dtype) -> bool:
     """Whether b200_paged_attn_decode_pairs is built for this shape."""
     return (dtype == torch.bfloat16 and page_size == 16 and num_q_heads % num_kv_heads == 0
@@ -144,6 +175,67 @@ def kv_append(k_new, v_new, k_pool, v_pool, block_table, positions, status: torc
         _ptr(status), B, Hkv, D, page, nb, block_table.shape[1], DTYPE_CODE[k_pool.dtype], _stream(),
     )
     check(rc, "b200_kv_append")
+
+
+# ---------------------------------------------------------- dense projections
+
+
+def dense_gemm_workspace(num_rows: int, out_features: int, device) -> torch.Tensor:
+    """Room for the fp32 partial tiles of a K-split product of up to `num_rows` x `out_features`."""
+    n = _lib.load().b200_dense_gemm_workspace_bytes(int(num_rows), int(out_features))
+    return torch.empty(max(n, 16), dtype=torch.uint8, device=device)
+
+
+def dense_gemm(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor | None = None, status: torch.Tensor | None = None,
+               k_split: int = 0, workspace: torch.Tensor | None = None) -> torch.Tensor:
+    """y = x w^T for bf16 x [M, K] and w [N, K] (fp32 accumulation, bf16 result).  Callers on a hot path pass a
+    `workspace` (dense_gemm_workspace) that they keep; without one it is allocated here when a K split is used."""
+    _need(x, "x", torch.bfloat16)
+    _need(w, "w", torch.bfloat16)
+    M, K = x.shape
+    N, K2 = w.shape
+    if K2 != K:
+        raise ValueError(f"x has {K} columns, w has {K2}")
+    if out is None:
+        out = torch.empty(M, N, dtype=torch.bfloat16, device=x.device)
+    _need(out, "out", torch.bfloat16)
+    if M == 0:
+        return out
+    if workspace is None and k_split != 1:
+        if k_split == 0 and ((N + 127) // 128) * ((M + 255) // 256) >= 128:
+            k_split = 1  # enough weight tiles to fill the GPU: the library would not split either
+        else:
+            workspace = dense_gemm_workspace(M, N, x.device)
+    rc = _lib.load().b200_dense_gemm_bf16(_ptr(x), _ptr(w), _ptr(out), _ptr(workspace),
+                                          0 if workspace is None else workspace.numel(), _ptr(status), M, N, K,
+                                          int(k_split), _stream())
+    check(rc, "b200_dense_gemm_bf16")
+    return out
+
+
+def lm_head_argmax_workspace(device) -> torch.Tensor:
+    return torch.zeros(_lib.load().b200_lm_head_argmax_workspace_bytes(), dtype=torch.uint8, device=device)
+
+
+def lm_head_argmax(x: torch.Tensor, w: torch.Tensor, workspace: torch.Tensor | None = None,
+                   out: torch.Tensor | None = None, status: torch.Tensor | None = None) -> torch.Tensor:
+    """argmax_n (x w^T)[m, n] per row without writing the logits; ties go to the lower index.  int64 [M]."""
+    _need(x, "x", torch.bfloat16)
+    _need(w, "w", torch.bfloat16)
+    M, K = x.shape
+    if w.shape[1] != K:
+        raise ValueError(f"x has {K} columns, w has {w.shape[1]}")
+    if workspace is None:
+        workspace = lm_head_argmax_workspace(x.device)
+    if out is None:
+        out = torch.empty(M, dtype=torch.int64, device=x.device)
+    _need(out, "out", torch.int64)
+    for lo in range(0, M, 256):  # the kernel keeps one running candidate per row in registers: 256 rows a call
+        hi = min(M, lo + 256)
+        rc = _lib.load().b200_lm_head_argmax(_ptr(x[lo:hi]), _ptr(w), out[lo:hi].data_ptr(), _ptr(workspace),
+                                             workspace.numel(), _ptr(status), hi - lo, w.shape[0], K, _stream())
+        check(rc, "b200_lm_head_argmax")
+    return out
 
 
 # ------------------------------------------------------------ fused step glue

@@ -6,6 +6,8 @@
     python microbench.py ep --world 8    # expert-parallel layer, ranks emulated in-process
     python microbench.py fp8peak         # dense e4m3 GEMM rate of the library (cuBLASLt),
                                                                # the denominator for the MoE GEMM's tensor fraction
+    python microbench.py dense           # the bf16 projections (q/k/v, o, router, lm_head + arg-max) at decode
+                                                               # sizes, every K split, beside the library GEMM
     ... attn --small / moe --small                             # few launches on a few hundred MB: sized for a profiler
 
 Every case prints one JSON line per measured point: CUDA-event time (median of --iters launches after 3 warm-ups,
@@ -236,6 +238,55 @@ def run_ep(args) -> None:
                       "note": "all ranks on one GPU: no NVLink time and no waiting for other ranks"}))
 
 
+# --------------------------------------------------------- dense projections --
+def run_dense(args) -> None:
+    """The step's bf16 projections at `--rows` rows: this package's tcgen05 kernel for every K split it offers,
+    and torch.matmul (cuBLAS) on the same tensors for comparison.  Bytes = the weight matrix once."""
+    M, H = args.rows, args.hidden
+    qkv_out = (args.q_heads + 2 * args.kv_heads) * args.head_dim
+    shapes = [("qkv", qkv_out, H), ("o", H, args.q_heads * args.head_dim), ("router", args.experts, H)]
+    g = torch.Generator(device=DEV).manual_seed(0)
+    timer = Timer(args.iters)
+    peak, src = measured_hbm_gbs()
+    status = torch.zeros(64, dtype=torch.int32, device=DEV)
+    for name, N, K in shapes:
+        x = torch.randn(M, K, generator=g, device=DEV).bfloat16()
+        w = (torch.randn(N, K, generator=g, device=DEV) * 0.02).bfloat16()
+        out = torch.empty(M, N, dtype=torch.bfloat16, device=DEV)
+        gws = ops.dense_gemm_workspace(M, N, DEV)
+        row = {"case": "dense", "what": name, "rows": M, "out_features": N, "in_features": K, "weight_MB": N * K * 2 / 1e6}
+        if args.small:  # one launch per shape with the library's own split, for a profiler
+            ops.dense_gemm(x, w, out, status, workspace=gws)
+            torch.cuda.synchronize()
+            print(json.dumps({**row, "case": "dense --small", "launches": 1}))
+            continue
+        for ks in (0, 1, 2, 4, 8):
+            if ks and (K // 64) % ks:
+                continue
+            med, _ = timer(lambda: ops.dense_gemm(x, w, out, status, k_split=ks, workspace=gws))
+            row["us_auto" if ks == 0 else f"us_split{ks}"] = med
+        lib, _ = timer(lambda: torch.matmul(x, w.t(), out=out))
+        row.update({"us_library": lib, "GBs_auto": N * K * 2 / row["us_auto"] / 1e3, "peak_GBs": peak, "peak_source": src})
+        print(json.dumps(row))
+    x = torch.randn(M, H, generator=g, device=DEV).bfloat16()
+    w = (torch.randn(args.vocab, H, generator=g, device=DEV) * 0.02).bfloat16()
+    ws = ops.lm_head_argmax_workspace(DEV)
+    tok = torch.empty(M, dtype=torch.int64, device=DEV)
+    if args.small:
+        ops.lm_head_argmax(x, w, ws, tok, status)
+        torch.cuda.synchronize()
+        ops.read_status(status, "dense")
+        print(json.dumps({"case": "dense --small", "what": "lm_head + arg-max", "launches": 1}))
+        return
+    med, _ = timer(lambda: ops.lm_head_argmax(x, w, ws, tok, status))
+    lib, _ = timer(lambda: torch.matmul(x, w.t()).argmax(dim=-1))
+    ops.read_status(status, "dense")
+    print(json.dumps({"case": "dense", "what": "lm_head + arg-max", "rows": M, "vocab": args.vocab, "hidden": H,
+                      "weight_MB": args.vocab * H * 2 / 1e6, "us": med, "us_library_matmul_then_argmax": lib,
+                      "GBs": args.vocab * H * 2 / med / 1e3, "frac_of_hbm_peak": args.vocab * H * 2 / med / 1e3 / peak,
+                      "peak_GBs": peak, "peak_source": src}))
+
+
 # ------------------------------------------------------------ dense FP8 peak --
 def run_fp8peak(args) -> None:
     """What the library's dense e4m3 x e4m3 -> bf16 GEMM reaches on this GPU (per-tensor scales, no block
@@ -279,6 +330,16 @@ def main() -> None:
         p.add_argument("--top-k", type=int, default=8)
         p.add_argument("--hidden", type=int, default=2048)
         p.add_argument("--inter", type=int, default=768)
+    d = sub.add_parser("dense")
+    d.add_argument("--rows", type=int, default=256)
+    d.add_argument("--hidden", type=int, default=2048)
+    d.add_argument("--q-heads", type=int, default=32)
+    d.add_argument("--kv-heads", type=int, default=4)
+    d.add_argument("--head-dim", type=int, default=128)
+    d.add_argument("--experts", type=int, default=128)
+    d.add_argument("--vocab", type=int, default=151936)
+    d.add_argument("--iters", type=int, default=20)
+    d.add_argument("--small", action="store_true", help="one launch per shape (for a profiler)")
     f = sub.add_parser("fp8peak")
     f.add_argument("--size", type=int, default=8192)
     f.add_argument("--iters", type=int, default=20)
@@ -289,7 +350,7 @@ def main() -> None:
     args = ap.parse_args()
     if not torch.cuda.is_available():
         raise SystemExit("microbench.py needs a CUDA device")
-    {"attn": run_attn, "moe": run_moe, "ep": run_ep, "fp8peak": run_fp8peak}[args.case](args)
+    {"attn": run_attn, "moe": run_moe, "ep": run_ep, "fp8peak": run_fp8peak, "dense": run_dense}[args.case](args)
 
 
 if __name__ == "__main__":

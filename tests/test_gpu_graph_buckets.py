@@ -12,7 +12,7 @@ DEV = "cuda"
 
 def make(eng_mod, buckets):
     return eng_mod.DecodeEngine(eng_mod.CONFIGS["tiny"], num_blocks=32, max_batch=8, max_pages_per_seq=4, device=DEV,
-                                seed=5, graph_buckets=buckets)
+                                seed=5, graph_buckets=buckets, keep_logits=True)
 
 
 def test_bucketed_graph_equals_exact_graph_and_keeps_off_foreign_pages(ops):

@@ -18,7 +18,7 @@ def test_hf_forward_with_plugins_matches_the_engine_step(ops):
     torch.manual_seed(0)
     cfg = hf_config(eng_mod.CONFIGS["tiny"], attn_implementation="eager", experts_implementation="eager")
     model = Qwen3MoeForCausalLM(cfg).float().eval()
-    engine = eng_mod.engine_from_hf(model, num_blocks=64, max_batch=4, max_pages_per_seq=8, device=DEV)
+    engine = eng_mod.engine_from_hf(model, num_blocks=64, max_batch=4, max_pages_per_seq=8, device=DEV, keep_logits=True)
     g = torch.Generator().manual_seed(2)
     lens = [37, 64, 90, 5]
     table = torch.arange(32, dtype=torch.int32).view(4, 8)

@@ -18,7 +18,8 @@ TOL_MODEL = 3e-2
 
 def make_engine():
     eng = pkg("engine")
-    return eng.DecodeEngine(eng.CONFIGS["tiny"], num_blocks=64, max_batch=4, max_pages_per_seq=16, device=DEV, seed=3)
+    return eng.DecodeEngine(eng.CONFIGS["tiny"], num_blocks=64, max_batch=4, max_pages_per_seq=16, device=DEV, seed=3,
+                            keep_logits=True)
 
 
 def test_chunked_prefill_equals_one_pass_and_cached_prefix_is_read_in_place(ops):

@@ -74,7 +74,7 @@ def test_tiny_model_teacher_forced_against_reference_tokens(ops):
     tokens = g["tokens"]  # [33, 4]: first tokens, then 32 steps
     model = build_models()
     eng_mod, backend_mod = pkg("engine"), pkg("backend")
-    engine = eng_mod.engine_from_hf(model, num_blocks=128, max_batch=4, max_pages_per_seq=16, device=DEV)
+    engine = eng_mod.engine_from_hf(model, num_blocks=128, max_batch=4, max_pages_per_seq=16, device=DEV, keep_logits=True)
     backend = backend_mod.B200Backend(engine, max_new_tokens=40)
 
     # ---- oracle pass on CPU (fp32, matched formats), teacher-forced with the golden tokens
@@ -163,7 +163,7 @@ def test_tiny_model_free_running_greedy_through_the_backend(ops):
     margin = g["top2"][..., 0] - g["top2"][..., 1]  # [32, 4]: margin of the logits that chose tokens[s + 1]
     model = build_models()
     eng_mod, backend_mod = pkg("engine"), pkg("backend")
-    engine = eng_mod.engine_from_hf(model, num_blocks=128, max_batch=4, max_pages_per_seq=16, device=DEV)
+    engine = eng_mod.engine_from_hf(model, num_blocks=128, max_batch=4, max_pages_per_seq=16, device=DEV, keep_logits=True)
     backend = backend_mod.B200Backend(engine, max_new_tokens=40)
     batch, cur = None, []
     for p in prompts:
