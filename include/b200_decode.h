@@ -238,6 +238,27 @@ int b200_qk_norm_rope_append(const void* qkv, const void* q_norm_weight, const v
                              int page_size, int num_blocks, int max_pages_per_seq,
                              int max_positions, void* stream);
 
+/*
+ * Replaces, in one kernel: the residual add and post-attention RMSNorm of the decoder layer, the router's
+ * linear layer (`gate`) and Qwen3MoeTopKRouter (fp32 softmax, top-k, renormalisation) of the forward called at
+ * torch_backend.py:314-320 - b200_add_rmsnorm, the router projection and b200_moe_route back to back, with the
+ * router logits kept on the chip in fp32.  A cluster of 8 CTAs owns 16 rows; each CTA takes an eighth of the
+ * hidden dimension and the partial sums of squares and partial logits meet through distributed shared memory,
+ * summed in rank order.
+ *
+ *   x [num_rows, hidden] bf16, updated in place to x + delta when delta is not NULL
+ *   normed_out [num_rows, hidden] bf16 = norm_weight * normalise(x)   (the MoE layer's input)
+ *   router_weight [num_experts, hidden] bf16
+ *   topk_ids / topk_weights  as b200_moe_route (num_valid_rows: see there)
+ *   logits_out  optional [num_rows, num_experts] fp32
+ * hidden a multiple of 512, num_experts a multiple of 16 and at most 128: b200_add_rmsnorm_route_supported.
+ */
+int b200_add_rmsnorm_route_supported(int hidden, int num_experts, int top_k);
+int b200_add_rmsnorm_route(void* x, const void* delta, const void* norm_weight, float eps,
+                           const void* router_weight, int num_rows, int hidden, int num_experts, int top_k,
+                           int renormalize, const int32_t* num_valid_rows, void* normed_out, int32_t* topk_ids,
+                           float* topk_weights, float* logits_out, void* stream);
+
 /* ------------------------------------------------------------------- MoE -- */
 
 /*
@@ -405,6 +426,19 @@ int b200_moe_fp8_forward_add_rmsnorm(const void* x, const void* router_logits, i
                                      void* workspace, size_t workspace_bytes, int num_tokens,
                                      int num_experts, int top_k, int hidden, int inter,
                                      int renormalize, int weight_layout, void* stream);
+
+/*
+ * The _add_rmsnorm form for tokens that are already routed (b200_add_rmsnorm_route, or the model's own
+ * router as the experts module of transformers is called: `experts(hidden_states, top_k_index,
+ * top_k_weights)`): permute+quantise, the two grouped GEMMs, combine + residual + norm.
+ *   topk_ids [num_tokens, top_k] int32 (-1 = no expert), topk_weights [num_tokens, top_k] fp32
+ */
+int b200_moe_fp8_routed_add_rmsnorm(const void* x, const int32_t* topk_ids, const float* topk_weights,
+                                    const void* w13, const float* w13_scale_inv, const void* w2,
+                                    const float* w2_scale_inv, void* residual, const void* norm_weight,
+                                    float eps, void* normed_out, void* workspace, size_t workspace_bytes,
+                                    int num_tokens, int num_experts, int top_k, int hidden, int inter,
+                                    int weight_layout, void* stream);
 
 /*
  * ---------------------------------------------------------------------------

@@ -33,6 +33,8 @@ SIGNATURES = {
     "b200_dense_gemm_bf16": (c_int, [c_void_p] * 4 + [c_size_t, c_void_p] + [c_int] * 4 + [c_void_p]),
     "b200_lm_head_argmax_workspace_bytes": (c_size_t, []),
     "b200_lm_head_argmax": (c_int, [c_void_p] * 4 + [c_size_t, c_void_p] + [c_int] * 3 + [c_void_p]),
+    "b200_add_rmsnorm_route_supported": (c_int, [c_int] * 3),
+    "b200_add_rmsnorm_route": (c_int, [c_void_p] * 3 + [c_float, c_void_p] + [c_int] * 5 + [c_void_p] * 6),
     "b200_add_rmsnorm": (c_int, [c_void_p, c_void_p, c_void_p, c_float, c_int, c_int, c_void_p, c_void_p]),
     "b200_qk_norm_rope_append": (c_int, [c_void_p] * 11 + [c_int] * 4 + [c_float] + [c_int] * 4 + [c_void_p]),
     "b200_moe_route": (c_int, [c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p]),
@@ -54,6 +56,8 @@ SIGNATURES = {
     "b200_moe_fp8_forward": (c_int, [c_void_p, c_void_p, c_int] + [c_void_p] * 6 + [c_size_t] + [c_int] * 7 + [c_void_p]),
     "b200_moe_fp8_forward_add_rmsnorm": (
         c_int, [c_void_p, c_void_p, c_int] + [c_void_p] * 6 + [c_float] + [c_void_p] * 2 + [c_size_t] + [c_int] * 7 + [c_void_p]),
+    "b200_moe_fp8_routed_add_rmsnorm": (
+        c_int, [c_void_p] * 9 + [c_float] + [c_void_p] * 2 + [c_size_t] + [c_int] * 6 + [c_void_p]),
     # expert parallelism over peer memory (no counterpart in the reference)
     "b200_moe_permute_quant_ep_p2p": (c_int, [c_void_p, c_void_p] + [c_int] * 7 + [c_void_p] * 11 + [c_size_t, c_void_p]),
     "b200_moe_fp8_gemm_down_p2p": (c_int, [c_void_p] * 9 + [c_int] * 8 + [c_void_p]),

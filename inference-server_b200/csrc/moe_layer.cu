@@ -59,12 +59,15 @@ extern "C" size_t b200_moe_fp8_workspace_bytes(int num_tokens, int num_experts, 
   return carve_moe(num_tokens, num_experts, top_k, hidden, inter).total;
 }
 
-static int moe_forward_impl(const void* x, const void* router_logits, int logits_dtype, const void* w13,
+// `routed_ids` / `routed_w`: routing that the caller has already done; the router step is then skipped.
+static int moe_forward_impl(const void* x, const void* router_logits, int logits_dtype, const int32_t* routed_ids,
+                            const float* routed_w, const void* w13,
                             const float* w13_scale_inv, const void* w2, const float* w2_scale_inv,
                             void* out, void* residual, const void* norm_weight, float eps, void* workspace,
                             size_t workspace_bytes, int num_tokens, int num_experts, int top_k, int hidden,
                             int inter, int renormalize, int weight_layout, void* stream) {
-  B200_REQUIRE(x && router_logits && w13 && w13_scale_inv && w2 && w2_scale_inv && out && workspace,
+  B200_REQUIRE(x && (router_logits || (routed_ids && routed_w)) && w13 && w13_scale_inv && w2 && w2_scale_inv && out &&
+                   workspace,
                "moe_fp8_forward: null pointer");
   B200_REQUIRE(num_tokens >= 0 && num_experts > 0 && top_k > 0 && hidden > 0 && inter > 0,
                "moe_fp8_forward: bad dimensions");
@@ -77,8 +80,8 @@ static int moe_forward_impl(const void* x, const void* router_logits, int logits
   }
   if (num_tokens == 0) return 0;
   uint8_t* ws = static_cast<uint8_t*>(workspace);
-  int32_t* topk_ids = reinterpret_cast<int32_t*>(ws + c.topk_ids);
-  float* topk_w = reinterpret_cast<float*>(ws + c.topk_w);
+  const int32_t* topk_ids = routed_ids ? routed_ids : reinterpret_cast<int32_t*>(ws + c.topk_ids);
+  const float* topk_w = routed_w ? routed_w : reinterpret_cast<float*>(ws + c.topk_w);
   int32_t* sorted_pair = reinterpret_cast<int32_t*>(ws + c.sorted_pair);
   int32_t* row_of_pair = reinterpret_cast<int32_t*>(ws + c.row_of_pair);
   int32_t* expert_offsets = reinterpret_cast<int32_t*>(ws + c.expert_offsets);
@@ -87,9 +90,12 @@ static int moe_forward_impl(const void* x, const void* router_logits, int logits
   void* status = ws;
   const int rows = num_tokens * top_k;
 
-  int rc = b200_moe_route(router_logits, logits_dtype, num_tokens, num_experts, top_k, renormalize, nullptr,
-                          topk_ids, topk_w, stream);
-  if (rc) return rc;
+  int rc = 0;
+  if (routed_ids == nullptr) {
+    rc = b200_moe_route(router_logits, logits_dtype, num_tokens, num_experts, top_k, renormalize, nullptr,
+                        reinterpret_cast<int32_t*>(ws + c.topk_ids), reinterpret_cast<float*>(ws + c.topk_w), stream);
+    if (rc) return rc;
+  }
   rc = b200_moe_permute_quant(topk_ids, x, num_tokens, num_experts, top_k, hidden, sorted_pair, row_of_pair,
                               expert_offsets, tiles, num_tiles, ws + c.xq, reinterpret_cast<float*>(ws + c.xs),
                               ws + c.permute_ws, b200_moe_permute_workspace_bytes(num_tokens, num_experts, top_k),
@@ -115,8 +121,8 @@ extern "C" int b200_moe_fp8_forward(const void* x, const void* router_logits, in
                                     size_t workspace_bytes, int num_tokens, int num_experts,
                                     int top_k, int hidden, int inter, int renormalize,
                                     int weight_layout, void* stream) {
-  return moe_forward_impl(x, router_logits, logits_dtype, w13, w13_scale_inv, w2, w2_scale_inv, out, nullptr,
-                          nullptr, 0.f, workspace, workspace_bytes, num_tokens, num_experts, top_k, hidden, inter,
+  return moe_forward_impl(x, router_logits, logits_dtype, nullptr, nullptr, w13, w13_scale_inv, w2, w2_scale_inv, out,
+                          nullptr, nullptr, 0.f, workspace, workspace_bytes, num_tokens, num_experts, top_k, hidden, inter,
                           renormalize, weight_layout, stream);
 }
 
@@ -128,7 +134,20 @@ extern "C" int b200_moe_fp8_forward_add_rmsnorm(const void* x, const void* route
                                                 int num_experts, int top_k, int hidden, int inter,
                                                 int renormalize, int weight_layout, void* stream) {
   B200_REQUIRE(residual && norm_weight && normed_out, "moe_fp8_forward_add_rmsnorm: null pointer");
-  return moe_forward_impl(x, router_logits, logits_dtype, w13, w13_scale_inv, w2, w2_scale_inv, normed_out,
+  return moe_forward_impl(x, router_logits, logits_dtype, nullptr, nullptr, w13, w13_scale_inv, w2, w2_scale_inv,
+                          normed_out, residual, norm_weight, eps, workspace, workspace_bytes, num_tokens, num_experts,
+                          top_k, hidden, inter, renormalize, weight_layout, stream);
+}
+
+extern "C" int b200_moe_fp8_routed_add_rmsnorm(const void* x, const int32_t* topk_ids, const float* topk_weights,
+                                               const void* w13, const float* w13_scale_inv, const void* w2,
+                                               const float* w2_scale_inv, void* residual, const void* norm_weight,
+                                               float eps, void* normed_out, void* workspace, size_t workspace_bytes,
+                                               int num_tokens, int num_experts, int top_k, int hidden, int inter,
+                                               int weight_layout, void* stream) {
+  B200_REQUIRE(topk_ids && topk_weights && residual && norm_weight && normed_out,
+               "moe_fp8_routed_add_rmsnorm: null pointer");
+  return moe_forward_impl(x, nullptr, 0, topk_ids, topk_weights, w13, w13_scale_inv, w2, w2_scale_inv, normed_out,
                           residual, norm_weight, eps, workspace, workspace_bytes, num_tokens, num_experts, top_k,
-                          hidden, inter, renormalize, weight_layout, stream);
+                          hidden, inter, 1, weight_layout, stream);
 }

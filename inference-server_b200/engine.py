@@ -199,6 +199,7 @@ class DecodeEngine:
                                                 self.split_tokens, self.device)
         self.moe_ws = ops.moe_fp8_workspace(max_batch, cfg.experts, cfg.top_k, cfg.hidden, cfg.moe_inter, self.device)
         self.gemm_status = torch.zeros(64, dtype=torch.int32, device=self.device)  # dense projections, lm_head
+        self._fused_router = ops.add_rmsnorm_route_supported(cfg.hidden, cfg.experts, cfg.top_k)
         widest = max((cfg.q_heads + 2 * cfg.kv_heads) * cfg.head_dim, cfg.hidden, cfg.experts)
         self.gemm_ws = ops.dense_gemm_workspace(min(max_batch, 256), widest, self.device)  # K-split partial tiles
         self.argmax_ws = ops.lm_head_argmax_workspace(self.device)
@@ -238,9 +239,10 @@ class DecodeEngine:
             # The exchange has one shape, so there is one graph; it is built here, where every rank is (its
             # warm-up runs are real exchanges and must happen on all ranks together), with padding rows only.
             self._build_graph(self.max_batch, pad_from=0)
-        # per layer: qkv GEMM, qk_norm_rope_append, attention + split reduce, o GEMM, add_rmsnorm, router GEMM, route,
-        # rank, scatter+quant, expert GEMM x2, combine+norm; + the first norm, lm_head with arg-max and its fold
-        self.kernel_launches_per_step = cfg.layers * 13 + 3
+        # per layer: qkv GEMM, qk_norm_rope_append, attention + split reduce, o GEMM, norm + router + top-k (one
+        # kernel; three where its shape limits do not hold), rank, scatter+quant, expert GEMM x2, combine+norm;
+        # + the first norm, lm_head with arg-max and its fold
+        self.kernel_launches_per_step = cfg.layers * (11 if self._fused_router else 13) + 3
         if self.ep_world > 1:
             # the local re-sort of received rows (rank + scatter + row gather), and with the peer-memory
             # transport the two flag exchanges
@@ -279,12 +281,22 @@ class DecodeEngine:
                 attn = ops.paged_attn_decode(q, self.k_pools[li], self.v_pools[li], table, new_len, self.scale,
                                              split_tokens, attn_ws, pairs=pairs)
             o = ops.dense_gemm(attn.view(R, Hq * D), w.wo, status=self.gemm_status, workspace=self.gemm_ws)
-            h2 = ops.add_rmsnorm(x, o, w.ln2, cfg.rms_eps)
-            logits = ops.dense_gemm(h2, w.router, status=self.gemm_status, workspace=self.gemm_ws)  # bf16, routed as is
             nxt = self.layers[li + 1].ln1 if li + 1 < len(self.layers) else self.final_norm
+            if self._fused_router:
+                # residual add + norm + router projection + top-k in one kernel; the logits stay on the chip (fp32)
+                h2, ids, wts = ops.add_rmsnorm_route(x, o, w.ln2, cfg.rms_eps, w.router, cfg.top_k, cfg.norm_topk_prob,
+                                                     self.n_valid if ep else None)
+                logits, routing = None, (ids, wts)
+            else:
+                h2 = ops.add_rmsnorm(x, o, w.ln2, cfg.rms_eps)
+                logits = ops.dense_gemm(h2, w.router, status=self.gemm_status, workspace=self.gemm_ws)  # bf16, routed as is
+                routing = None
             # MoE layer; its combine also adds into the residual stream and applies the next norm
             if ep:
-                h = self._ep_moe(h2, logits, w, x, nxt, R)  # rows >= n_valid take no part
+                h = self._ep_moe(h2, logits, w, x, nxt, R, routing)  # rows >= n_valid take no part
+            elif routing is not None:
+                h = ops.moe_fp8_forward(h2, None, w.w13, w.w13_scale, w.w2, w.w2_scale, cfg.top_k, cfg.norm_topk_prob,
+                                        moe_ws, residual=x, norm_weight=nxt, eps=cfg.rms_eps, routing=routing)
             else:
                 h = ops.moe_fp8_forward(h2, logits, w.w13, w.w13_scale, w.w2, w.w2_scale, cfg.top_k,
                                         cfg.norm_topk_prob, moe_ws, residual=x, norm_weight=nxt, eps=cfg.rms_eps)
@@ -354,7 +366,7 @@ class DecodeEngine:
         ops.lm_head_argmax(h, self.lm_head, self.argmax_ws, out=self.next_tokens[:B], status=self.gemm_status)
         self.ctx_lens[:B] += 1
 
-    def _ep_moe(self, h2, logits, w: LayerWeights, x, next_norm, B: int) -> torch.Tensor:
+    def _ep_moe(self, h2, logits, w: LayerWeights, x, next_norm, B: int, routing=None) -> torch.Tensor:
         """Expert-parallel MoE layer: dispatch and combine around the local grouped GEMMs, by NCCL all-to-all
         or, with a peer arena, by stores into the other ranks' memory.  The exchange has one fixed shape (the
         engine's full batch on every rank); a pass with fewer real rows runs it with padding rows that the
@@ -367,7 +379,7 @@ class DecodeEngine:
             raise ValueError("an expert-parallel pass runs at the exchange's full shape; pad it (see step / prefill)")
         return ep.ep_moe_forward(st, h2, logits, w.w13, w.w13_scale, w.w2, w.w2_scale, self.cfg.norm_topk_prob, ops,
                                  lambda o, i: dist.all_to_all_single(o, i, group=st.group), residual=x,
-                                 norm_weight=next_norm, eps=self.cfg.rms_eps, n_valid=self.n_valid)
+                                 norm_weight=next_norm, eps=self.cfg.rms_eps, n_valid=self.n_valid, routing=routing)
 
     GRAPH_BUCKETS = (1, 2, 4, 8, 16, 24, 32, 48, 64, 96, 128, 192, 256, 384, 512, 768, 1024)
 

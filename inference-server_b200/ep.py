@@ -195,7 +195,7 @@ class EPState:
 
 
 def ep_moe_forward(st: EPState, h, logits, w13, w13_scale, w2, w2_scale, renormalize, kernels, all_to_all,
-                   residual=None, norm_weight=None, eps: float = 1e-6, n_valid=None):
+                   residual=None, norm_weight=None, eps: float = 1e-6, n_valid=None, routing=None):
     """One expert-parallel FP8 MoE layer on this rank's tokens `h` [T, H].
 
     `w13/w2` hold only this rank's experts.  `kernels` supplies the compute steps (the ``ops`` module on a
@@ -212,15 +212,17 @@ def ep_moe_forward(st: EPState, h, logits, w13, w13_scale, w2, w2_scale, renorma
     dispatch kernel and the down GEMM, separated by flag exchanges; `all_to_all` is then unused.
     The shapes are the same on every rank and in every pass.  `n_valid` (an int32 scalar on the device) says how
     many leading rows of `h` are real in this pass: the router gives the others no expert, so they are neither
-    sent nor combined - a rank with a short batch, or none, still takes part in the exchange."""
+    sent nor combined - a rank with a short batch, or none, still takes part in the exchange.
+    `routing` = (ids, weights) when the tokens are routed already (the fused norm + router kernel, which has
+    applied `n_valid` itself); `logits` is then unused."""
     if st.arena is not None:
-        wts, slot_of_pair = p2p_dispatch(st, h, logits, renormalize, kernels, n_valid)
+        wts, slot_of_pair = p2p_dispatch(st, h, logits, renormalize, kernels, n_valid, routing)
         kernels.ep_barrier(st.peer_flags[0], st.epochs[0:1], st.rank, st.W, st.status)
         p2p_experts(st, w13, w13_scale, w2, w2_scale, kernels)
         kernels.ep_barrier(st.peer_flags[1], st.epochs[1:2], st.rank, st.W, st.status)
         return _combine(st, wts, slot_of_pair, kernels, residual, norm_weight, eps)
     T, K, W, C, El = st.T, st.K, st.W, st.C, st.e_local
-    ids, wts = kernels.moe_route(logits, K, renormalize, n_valid)
+    ids, wts = routing if routing is not None else kernels.moe_route(logits, K, renormalize, n_valid)
     _, slot_of_pair = kernels.moe_permute_quant_ep(ids, h, st.E, W, C, st.xq_send, st.xs_send, st.id_send, st.overflow,
                                                    perm=st.perm_send, slot_of_pair=st.slot_of_pair)
     all_to_all(st.xq_recv, st.xq_send)
@@ -249,10 +251,10 @@ def _combine(st: EPState, wts, slot_of_pair, kernels, residual, norm_weight, eps
 # stage by stage over all ranks with ep_signal / ep_wait apart (kernels that wait for each other must not
 # sit in one stream).
 
-def p2p_dispatch(st: EPState, h, logits, renormalize, kernels, n_valid=None):
-    """Route, then sort + quantise + store every row, its scales and its expert id into the owner's
-    receive buffers (one kernel).  Returns (routing weights, slot_of_pair)."""
-    ids, wts = kernels.moe_route(logits, st.K, renormalize, n_valid)
+def p2p_dispatch(st: EPState, h, logits, renormalize, kernels, n_valid=None, routing=None):
+    """Route (unless `routing` is given), then sort + quantise + store every row, its scales and its expert id
+    into the owner's receive buffers (one kernel).  Returns (routing weights, slot_of_pair)."""
+    ids, wts = routing if routing is not None else kernels.moe_route(logits, st.K, renormalize, n_valid)
     _, slot_of_pair = kernels.moe_permute_quant_ep_p2p(ids, h, st.E, st.W, st.C, st.rank, st.peer_xq, st.peer_xs,
                                                        st.peer_id, st.overflow, perm=st.perm_send,
                                                        slot_of_pair=st.slot_of_pair)

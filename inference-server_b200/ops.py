@@ -256,6 +256,38 @@ def add_rmsnorm(x: torch.Tensor, delta: torch.Tensor | None, weight: torch.Tenso
     return out
 
 
+def add_rmsnorm_route_supported(hidden: int, num_experts: int, top_k: int) -> bool:
+    return bool(_lib.load().b200_add_rmsnorm_route_supported(int(hidden), int(num_experts), int(top_k)))
+
+
+def add_rmsnorm_route(x: torch.Tensor, delta: torch.Tensor | None, norm_weight: torch.Tensor, eps: float,
+                      router_weight: torch.Tensor, top_k: int, renormalize: bool = True,
+                      num_valid: torch.Tensor | None = None, want_logits: bool = False):
+    """x += delta (in place); h = norm_weight * rmsnorm(x); fp32 router logits h W_r^T; top-k routing - one
+    kernel.  Returns (h bf16 [T, H], ids int32 [T, K], weights fp32 [T, K]) and, with want_logits, the fp32
+    logits [T, E] as a fourth value."""
+    _need(x, "x", torch.bfloat16)
+    _need(norm_weight, "norm_weight", torch.bfloat16)
+    _need(router_weight, "router_weight", torch.bfloat16)
+    if delta is not None:
+        _need(delta, "delta", torch.bfloat16)
+    if num_valid is not None:
+        _need(num_valid, "num_valid", torch.int32)
+    T, H = x.shape
+    E = router_weight.shape[0]
+    if router_weight.shape[1] != H:
+        raise ValueError("router_weight does not match the hidden size")
+    h = torch.empty_like(x)
+    ids = torch.empty(T, top_k, dtype=torch.int32, device=x.device)
+    w = torch.empty(T, top_k, dtype=torch.float32, device=x.device)
+    logits = torch.empty(T, E, dtype=torch.float32, device=x.device) if want_logits else None
+    rc = _lib.load().b200_add_rmsnorm_route(_ptr(x), _ptr(delta), _ptr(norm_weight), float(eps), _ptr(router_weight), T, H,
+                                            E, top_k, int(renormalize), _ptr(num_valid), _ptr(h), _ptr(ids), _ptr(w),
+                                            _ptr(logits), _stream())
+    check(rc, "b200_add_rmsnorm_route")
+    return (h, ids, w, logits) if want_logits else (h, ids, w)
+
+
 def qk_norm_rope_append(qkv, q_norm_w, k_norm_w, cos, sin, positions, block_table, k_pool, v_pool, num_q_heads,
                         eps: float, status=None, q_out=None) -> torch.Tensor:
     """Per-head q/k RMSNorm + RoPE; q returned [B, Hq, D], k and v written into their page slots."""
@@ -632,13 +664,35 @@ def moe_fp8_workspace(num_tokens, num_experts, top_k, hidden, inter, device):
 
 
 def moe_fp8_forward(x, router_logits, w13, w13_scale_inv, w2, w2_scale_inv, top_k, renormalize=True,
-                    workspace=None, out=None, residual=None, norm_weight=None, eps: float = 1e-6):
+                    workspace=None, out=None, residual=None, norm_weight=None, eps: float = 1e-6, routing=None):
     """The whole FP8 MoE layer on one stream: route, permute+quantise, two grouped GEMMs, combine.
 
     With `residual` and `norm_weight` the combine is fused with the next residual add and RMSNorm:
-    `residual` is updated in place and the returned tensor is norm_weight * rmsnorm(residual)."""
+    `residual` is updated in place and the returned tensor is norm_weight * rmsnorm(residual).
+    `routing` = (ids int32 [T, K], weights fp32 [T, K]) skips the router (tokens routed by
+    add_rmsnorm_route); `router_logits` is then unused and the residual form is required."""
     w13, w2 = _as_u8(w13), _as_u8(w2)
     _need(x, "x", torch.bfloat16)
+    if routing is not None:
+        ids, wts = routing
+        _need(ids, "routing ids", torch.int32)
+        _need(wts, "routing weights", torch.float32)
+        _need(w13, "w13", torch.uint8)
+        _need(w2, "w2", torch.uint8)
+        _need(residual, "residual", torch.bfloat16)
+        _need(norm_weight, "norm_weight", torch.bfloat16)
+        T, H = x.shape
+        E, two_i, _, layout = _weight_dims(w13)
+        if workspace is None:
+            workspace = moe_fp8_workspace(T, E, top_k, H, two_i // 2, x.device)
+        if out is None:
+            out = torch.empty_like(x)
+        rc = _lib.load().b200_moe_fp8_routed_add_rmsnorm(
+            _ptr(x), _ptr(ids), _ptr(wts), _ptr(w13), _ptr(w13_scale_inv), _ptr(w2), _ptr(w2_scale_inv), _ptr(residual),
+            _ptr(norm_weight), float(eps), _ptr(out), _ptr(workspace), workspace.numel(), T, E, top_k, H, two_i // 2,
+            layout, _stream())
+        check(rc, "b200_moe_fp8_routed_add_rmsnorm")
+        return out
     _need(router_logits, "router_logits")
     if router_logits.dtype not in DTYPE_CODE:
         raise ValueError(f"router_logits must be float32 or bfloat16, got {router_logits.dtype}")
