@@ -14,8 +14,10 @@
 //   load  = one producer warp walks the block table and brings page after page of its kv head into a
 //           ring of one-page stages: TMA boxes of 16 tokens x 128 B, 128-byte swizzle, mbarrier
 //           hand-over.
-//   math  = 4 consumer warps, 32 rows each (two m16 tiles that share every K and V fragment):
-//           S = Q K^T by mma.sync m16n8k16, causal mask by position (row of position p sees tokens
+//   math  = 8 consumer warps, one m16 tile (16 score rows) each.  Four warps with two tiles each share
+//           more K/V fragments per warp but need 255 registers and leave a scheduler with one warp:
+//           measured 25 % tensor-pipe activity, stalled on fixed-latency dependencies; eight lighter
+//           warps hide them better.  S = Q K^T by mma.sync m16n8k16, causal mask by position (row of position p sees tokens
 //           0..p), online softmax in fp32 in the log2 domain, O += P V.  No split over the context
 //           and no second pass: a row's whole context is inside one CTA.
 //   out   = normalised bf16 rows written from registers.
@@ -28,7 +30,8 @@ namespace b200 {
 
 constexpr int kPfPage = 16;
 constexpr int kPfRows = 128;        // score-matrix rows per CTA
-constexpr int kPfWarps = 4;         // consumer warps
+constexpr int kPfMt = 1;            // m16 tiles per consumer warp (they share every K and V fragment)
+constexpr int kPfWarps = kPfRows / (16 * kPfMt);  // consumer warps
 constexpr int kPfStages = 8;
 
 template <int D>
@@ -113,15 +116,15 @@ paged_attn_prefill_kernel(const __grid_constant__ CUtensorMap k_map, const __gri
   // --------------------------------------------------------------- consumers --
   const int gq = lane >> 2, tq = lane & 3;
   // this thread's four score rows: m16 tile mt, fragment rows gq and gq + 8
-  int len[2][2];        // tokens the row sees (its position + 1); rows past the chunk copy the tile's first row
-  bool real[2][2];
-  const __nv_bfloat16* qrow[2][2];
-  __nv_bfloat16* orow[2][2];
+  int len[kPfMt][2];        // tokens the row sees (its position + 1); rows past the chunk copy the tile's first row
+  bool real[kPfMt][2];
+  const __nv_bfloat16* qrow[kPfMt][2];
+  __nv_bfloat16* orow[kPfMt][2];
 #pragma unroll
-  for (int mt = 0; mt < 2; ++mt)
+  for (int mt = 0; mt < kPfMt; ++mt)
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
-      const int r = warp * 32 + mt * 16 + h * 8 + gq;  // row inside the CTA
+      const int r = warp * (16 * kPfMt) + mt * 16 + h * 8 + gq;  // row inside the CTA
       const int pos_i = i0 + r / G, head = kvh * G + r % G;
       real[mt][h] = pos_i < num_tokens;
       const int ii = real[mt][h] ? pos_i : i0;
@@ -130,9 +133,9 @@ paged_attn_prefill_kernel(const __grid_constant__ CUtensorMap k_map, const __gri
       orow[mt][h] = out + (static_cast<size_t>(ii) * num_q_heads + head) * D;
     }
 
-  uint32_t qa[2][D / 16][4];
+  uint32_t qa[kPfMt][D / 16][4];
 #pragma unroll
-  for (int mt = 0; mt < 2; ++mt)
+  for (int mt = 0; mt < kPfMt; ++mt)
 #pragma unroll
     for (int ks = 0; ks < D / 16; ++ks) {
       const int d0 = ks * 16 + 2 * tq;
@@ -144,14 +147,14 @@ paged_attn_prefill_kernel(const __grid_constant__ CUtensorMap k_map, const __gri
       qa[mt][ks][3] = __ldg(r1 + 4);
     }
 
-  float o[2][D / 8][4];
+  float o[kPfMt][D / 8][4];
 #pragma unroll
-  for (int mt = 0; mt < 2; ++mt)
+  for (int mt = 0; mt < kPfMt; ++mt)
 #pragma unroll
     for (int n = 0; n < D / 8; ++n) o[mt][n][0] = o[mt][n][1] = o[mt][n][2] = o[mt][n][3] = 0.f;
-  float mrun[2][2], lrun[2][2];
+  float mrun[kPfMt][2], lrun[kPfMt][2];
 #pragma unroll
-  for (int mt = 0; mt < 2; ++mt) {
+  for (int mt = 0; mt < kPfMt; ++mt) {
     mrun[mt][0] = mrun[mt][1] = -INFINITY;
     lrun[mt][0] = lrun[mt][1] = 0.f;
   }
@@ -169,9 +172,9 @@ paged_attn_prefill_kernel(const __grid_constant__ CUtensorMap k_map, const __gri
       const uint32_t kbase = ring + slot * Cfg::kStageBytes;
       const uint32_t vbase = kbase + Cfg::kHalves * Cfg::kBoxBytes;
 
-      float s0[2][4], s1[2][4];
+      float s0[kPfMt][4], s1[kPfMt][4];
 #pragma unroll
-      for (int mt = 0; mt < 2; ++mt)
+      for (int mt = 0; mt < kPfMt; ++mt)
 #pragma unroll
         for (int e = 0; e < 4; ++e) s0[mt][e] = s1[mt][e] = 0.f;
 #pragma unroll
@@ -180,7 +183,7 @@ paged_attn_prefill_kernel(const __grid_constant__ CUtensorMap k_map, const __gri
         uint32_t b00, b01, b10, b11;
         ldmatrix_x4(kbase + (cidx >> 3) * Cfg::kBoxBytes + swz128(k_tok, cidx & 7), b00, b01, b10, b11);
 #pragma unroll
-        for (int mt = 0; mt < 2; ++mt) {
+        for (int mt = 0; mt < kPfMt; ++mt) {
           mma_bf16_16816(s0[mt], qa[mt][ks], b00, b01);
           mma_bf16_16816(s1[mt], qa[mt][ks], b10, b11);
         }
@@ -188,10 +191,10 @@ paged_attn_prefill_kernel(const __grid_constant__ CUtensorMap k_map, const __gri
 
       const int tok0 = i * kPfPage + 2 * tq;  // token of s0[.][0]; s0[.][1] is +1, s1 is +8
       const bool edge = i * kPfPage + kPfPage > l_min;  // some row of the CTA ends inside or before this page
-      uint32_t pa[2][4];
-      float alpha[2][2];
+      uint32_t pa[kPfMt][4];
+      float alpha[kPfMt][2];
 #pragma unroll
-      for (int mt = 0; mt < 2; ++mt) {
+      for (int mt = 0; mt < kPfMt; ++mt) {
         if (edge) {
           const int la = len[mt][0], lb = len[mt][1];
           if (tok0 >= la) s0[mt][0] = -INFINITY;
@@ -226,13 +229,15 @@ paged_attn_prefill_kernel(const __grid_constant__ CUtensorMap k_map, const __gri
         pa[mt][2] = pack_bf16x2(p[0][2], p[0][3]);
         pa[mt][3] = pack_bf16x2(p[1][2], p[1][3]);
       }
-      const bool rescale = __any_sync(0xffffffffu, alpha[0][0] != 1.f || alpha[0][1] != 1.f ||
-                                                       alpha[1][0] != 1.f || alpha[1][1] != 1.f);
+      bool resc = false;
+#pragma unroll
+      for (int mt = 0; mt < kPfMt; ++mt) resc = resc || alpha[mt][0] != 1.f || alpha[mt][1] != 1.f;
+      const bool rescale = __any_sync(0xffffffffu, resc);
 #pragma unroll
       for (int np = 0; np < D / 16; ++np) {
         if (rescale) {
 #pragma unroll
-          for (int mt = 0; mt < 2; ++mt) {
+          for (int mt = 0; mt < kPfMt; ++mt) {
             o[mt][2 * np][0] *= alpha[mt][0];
             o[mt][2 * np][1] *= alpha[mt][0];
             o[mt][2 * np + 1][0] *= alpha[mt][0];
@@ -247,7 +252,7 @@ paged_attn_prefill_kernel(const __grid_constant__ CUtensorMap k_map, const __gri
         uint32_t v0, v1, v2, v3;
         ldmatrix_x4_trans(vbase + (cidx >> 3) * Cfg::kBoxBytes + swz128(v_tok, cidx & 7), v0, v1, v2, v3);
 #pragma unroll
-        for (int mt = 0; mt < 2; ++mt) {
+        for (int mt = 0; mt < kPfMt; ++mt) {
           mma_bf16_16816(o[mt][2 * np], pa[mt], v0, v1);
           mma_bf16_16816(o[mt][2 * np + 1], pa[mt], v2, v3);
         }
@@ -259,7 +264,7 @@ paged_attn_prefill_kernel(const __grid_constant__ CUtensorMap k_map, const __gri
   if (!alive) return;
 
 #pragma unroll
-  for (int mt = 0; mt < 2; ++mt)
+  for (int mt = 0; mt < kPfMt; ++mt)
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
       float l = lrun[mt][h];

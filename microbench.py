@@ -6,6 +6,8 @@
     python microbench.py ep --world 8    # expert-parallel layer, ranks emulated in-process
     python microbench.py fp8peak         # dense e4m3 GEMM rate of the library (cuBLASLt),
                                                                # the denominator for the MoE GEMM's tensor fraction
+    python microbench.py prefill         # tiled causal prompt attention: a chunk of 1024 tokens at several
+                                                               # depths of one sequence, beside the row-per-token form
     python microbench.py dense           # the bf16 projections (q/k/v, o, router, lm_head + arg-max) at decode
                                                                # sizes, every K split, beside the library GEMM
     ... attn --small / moe --small                             # few launches on a few hundred MB: sized for a profiler
@@ -238,6 +240,45 @@ def run_ep(args) -> None:
                       "note": "all ranks on one GPU: no NVLink time and no waiting for other ranks"}))
 
 
+# ----------------------------------------------------------- prompt attention --
+def run_prefill(args) -> None:
+    """b200_paged_attn_prefill on a chunk of `--chunk` consecutive prompt tokens whose sequence already holds
+    `first` tokens, for several `first`; flops = 4 * Hq * D * unmasked (query, key) pairs.  Beside it the decode
+    kernel's row-per-token form (two rows per CTA) on the same rows."""
+    hq, hkv, d, chunk = args.q_heads, args.kv_heads, args.head_dim, args.chunk
+    firsts = [int(f) for f in args.first.split(",")]
+    total = max(firsts) + chunk
+    n_pages = (total + PAGE - 1) // PAGE
+    g = torch.Generator(device=DEV).manual_seed(0)
+    kp = torch.randn(n_pages + 8, hkv, PAGE, d, generator=g, device=DEV).bfloat16()
+    vp = torch.randn(n_pages + 8, hkv, PAGE, d, generator=g, device=DEV).bfloat16()
+    q = torch.randn(chunk, hq, d, generator=g, device=DEV).bfloat16()
+    row = torch.randperm(n_pages + 8, generator=torch.Generator().manual_seed(0))[:n_pages].to(torch.int32).to(DEV)
+    status = torch.zeros(64, dtype=torch.int32, device=DEV)
+    out = torch.empty_like(q)
+    if args.small:
+        for _ in range(3):
+            ops.paged_attn_prefill(q, kp, vp, row, firsts[0], d ** -0.5, status, out)
+        torch.cuda.synchronize()
+        ops.read_status(status, "prefill attention")
+        print(json.dumps({"case": "prefill --small", "launches": 3, "chunk": chunk, "first_position": firsts[0]}))
+        return
+    timer = Timer(args.iters)
+    table = row.view(1, -1).expand(chunk, -1).contiguous()
+    for first in firsts:
+        med, mn = timer(lambda: ops.paged_attn_prefill(q, kp, vp, row, first, d ** -0.5, status, out))
+        pairs = chunk * first + chunk * (chunk + 1) // 2
+        flops = 4 * hq * d * pairs
+        lens = torch.arange(first + 1, first + chunk + 1, dtype=torch.int32, device=DEV)
+        st = ops.default_split_tokens(chunk, hkv, table.shape[1] * PAGE)
+        ws = ops.paged_attn_workspace(chunk, hq, d, table.shape[1], PAGE, st, DEV)
+        rows_med, _ = timer(lambda: ops.paged_attn_decode(q, kp, vp, table, lens, d ** -0.5, st, ws, out, pairs=True))
+        print(json.dumps({"case": "prefill", "chunk": chunk, "first_position": first, "q_heads": hq, "kv_heads": hkv,
+                          "us_median": med, "us_min": mn, "GFLOP": flops / 1e9, "TFLOPs": flops / med / 1e6,
+                          "row_per_token_form_us": rows_med}))
+    ops.read_status(status, "prefill attention")
+
+
 # --------------------------------------------------------- dense projections --
 def run_dense(args) -> None:
     """The step's bf16 projections at `--rows` rows: this package's tcgen05 kernel for every K split it offers,
@@ -330,6 +371,14 @@ def main() -> None:
         p.add_argument("--top-k", type=int, default=8)
         p.add_argument("--hidden", type=int, default=2048)
         p.add_argument("--inter", type=int, default=768)
+    pf = sub.add_parser("prefill")
+    pf.add_argument("--chunk", type=int, default=1024)
+    pf.add_argument("--first", default="0,1024,7168", help="tokens already in the sequence, comma separated")
+    pf.add_argument("--q-heads", type=int, default=32)
+    pf.add_argument("--kv-heads", type=int, default=4)
+    pf.add_argument("--head-dim", type=int, default=128)
+    pf.add_argument("--iters", type=int, default=10)
+    pf.add_argument("--small", action="store_true", help="three launches (for a profiler)")
     d = sub.add_parser("dense")
     d.add_argument("--rows", type=int, default=256)
     d.add_argument("--hidden", type=int, default=2048)
@@ -350,7 +399,7 @@ def main() -> None:
     args = ap.parse_args()
     if not torch.cuda.is_available():
         raise SystemExit("microbench.py needs a CUDA device")
-    {"attn": run_attn, "moe": run_moe, "ep": run_ep, "fp8peak": run_fp8peak, "dense": run_dense}[args.case](args)
+    {"attn": run_attn, "moe": run_moe, "ep": run_ep, "fp8peak": run_fp8peak, "dense": run_dense, "prefill": run_prefill}[args.case](args)
 
 
 if __name__ == "__main__":

@@ -325,3 +325,36 @@ def test_a_refused_prompt_lets_go_of_its_cache_hit():
     with pytest.raises(RuntimeError, match="refused"):
         be.prefill(prompt + [1, 2, 3], "b")
     assert [b.ref_count for b in blocks] == refs and cache.block_manager.free_blocks == free
+
+
+def test_load_model_reads_a_checkpoint_as_the_reference_does(tmp_path, monkeypatch):
+    """load_model(path) follows TorchBackend.load_model (torch_backend.py:33-53): from_pretrained in bf16, EOS ids
+    from the model config (a list or a single id).  The conversion to run-time formats needs a GPU, so the engine
+    constructor is replaced by one that records what it was handed."""
+    from transformers import Qwen3MoeConfig, Qwen3MoeForCausalLM
+
+    cfg = Qwen3MoeConfig(vocab_size=128, hidden_size=64, intermediate_size=128, num_hidden_layers=1,
+                         num_attention_heads=4, num_key_value_heads=2, head_dim=16, num_experts=4,
+                         num_experts_per_tok=2, moe_intermediate_size=32, decoder_sparse_step=1, mlp_only_layers=[],
+                         eos_token_id=[5, 7], tie_word_embeddings=False)
+    torch.manual_seed(0)
+    Qwen3MoeForCausalLM(cfg).save_pretrained(tmp_path)
+    seen = {}
+
+    def fake_engine(model, num_blocks, max_batch, max_pages_per_seq):
+        seen["dtype"] = next(model.parameters()).dtype
+        seen["layers"] = len(model.model.layers)
+        seen["experts"] = tuple(model.model.layers[0].mlp.experts.gate_up_proj.shape)
+        return StubEngine(num_blocks=num_blocks, max_batch=max_batch, max_pages=max_pages_per_seq)
+
+    be_cls = pkg("backend").B200Backend
+    monkeypatch.setattr(be_cls, "_engine_from_model", staticmethod(fake_engine))
+    be = be_cls(max_new_tokens=8)
+    be.load_model(str(tmp_path), num_blocks=40, max_batch=4, max_pages_per_seq=8)
+    assert seen == {"dtype": torch.bfloat16, "layers": 1, "experts": (4, 64, 64)}
+    assert be._eos_ids == {5, 7} and be.is_eos(7) and not be.is_eos(6)
+    assert be.engine.num_blocks == 40 and len(be._alloc.free) == 40
+    kv, first, n = be.prefill([1, 2, 3], "s")  # the loaded backend serves requests
+    assert n == 3 and first == 4
+    with pytest.raises(Exception):
+        be.load_model(str(tmp_path / "missing"))
