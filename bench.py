@@ -136,9 +136,31 @@ class ClockSampler:
         return out
 
 
-def build_workload(cfg, batch: int, gen_tokens: int, seed: int, ctx_min: int = 512, ctx_max: int = 4096):
+def balanced_share(lens: list[int], world: int, rank: int, batch: int) -> list[int]:
+    """The sequences a load-aware request router would give this rank: longest first, each to the rank with
+    the fewest context tokens so far that still has room (every rank ends with `batch` sequences)."""
+    sums, counts, mine = [0] * world, [0] * world, []
+    for L in sorted(lens, reverse=True):
+        r = min((r for r in range(world) if counts[r] < batch), key=lambda r: (sums[r], r))
+        sums[r] += L
+        counts[r] += 1
+        if r == rank:
+            mine.append(L)
+    return mine
+
+
+def build_workload(cfg, batch: int, gen_tokens: int, seed: int, ctx_min: int = 512, ctx_max: int = 4096,
+                   world: int = 1, rank: int = 0, balance: bool = False):
+    """Prompt lengths and a shuffled block table for this rank.  With `balance` (expert parallelism: the ranks
+    meet at two flag exchanges per layer, so every layer waits for the rank with the most context to read) the
+    world * batch prompt lengths are drawn from one seed and dealt to the ranks as a load-aware router would."""
     rng = np.random.default_rng(seed)
-    prompt_lens = rng.integers(ctx_min, ctx_max + 1, size=batch).tolist()
+    if balance and world > 1:
+        everyone = np.random.default_rng(12345).integers(ctx_min, ctx_max + 1, size=batch * world).tolist()
+        prompt_lens = balanced_share(everyone, world, rank, batch)
+        rng.shuffle(prompt_lens)
+    else:
+        prompt_lens = rng.integers(ctx_min, ctx_max + 1, size=batch).tolist()
     pages = [(L + gen_tokens + PAGE - 1) // PAGE for L in prompt_lens]
     max_pages = max(pages)
     total = sum(pages) + 64
@@ -415,6 +437,9 @@ def main():
                     help="with --ep: NCCL all-to-all, or stores into the peers' mapped receive buffers")
     ap.add_argument("--ep", action="store_true",
                     help="N > 1: data-parallel attention + expert-parallel MoE (the default for N > 1)")
+    ap.add_argument("--no-balance", action="store_true",
+                    help="N > 1 with expert parallelism: every rank draws its own prompt lengths instead of getting a "
+                         "load-balanced share of one common draw")
     ap.add_argument("--replicas", action="store_true",
                     help="N > 1: N independent data-parallel engines with all experts each, no data-path exchange")
     args = ap.parse_args()
@@ -425,8 +450,10 @@ def main():
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     cfg = pkg("engine").CONFIGS[args.model]
+    balance = world > 1 and args.ep and not args.no_balance
     prompt_lens, table, num_blocks, max_pages = build_workload(cfg, args.batch, args.gen_tokens, seed=rank,
-                                                               ctx_min=args.ctx_min, ctx_max=args.ctx_max)
+                                                               ctx_min=args.ctx_min, ctx_max=args.ctx_max, world=world,
+                                                               rank=rank, balance=balance)
     which = {"qwen3-30b-a3b": "BASELINE config 4", "qwen3-235b-a22b": "BASELINE config 5 shape"}.get(args.model, "parity shape")
     config = {"workload": f"{args.model} continuous-batching decode, {args.batch} sequences/GPU, prompts "
                           f"U{{{args.ctx_min}..{args.ctx_max}}}, page {PAGE}, FP8 experts ({which})",
@@ -434,6 +461,9 @@ def main():
               "parallelism": (f"dp{world} attention + ep{world} MoE ({'NCCL all-to-all' if args.ep_transport == 'nccl' else 'peer-memory stores + flag exchange'})"
                                if world > 1 and args.ep
                               else f"dp{world} (replicas: disjoint request batches, no data-path collective)"),
+              "requests": ("one common draw of prompt lengths dealt to the ranks by context load, as a load-aware "
+                           "router would (longest first to the least loaded rank)" if balance else
+                           "every rank draws its own prompt lengths"),
               "kv": "synthetic N(0,1) pages at the prompt lengths; prefill not timed",
               "l2": "each step streams tens of GB of KV pages and expert weights, far more than the 126 MB L2"}
 

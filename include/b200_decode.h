@@ -190,6 +190,26 @@ int b200_dense_gemm_bf16(const void* x, const void* w, void* y, void* workspace,
                          void* stream);
 
 /*
+ * Replaces, in one kernel: the fused q/k/v projection of an attention block and what follows it before the
+ * attention itself - per-head RMSNorm of q and k, rotary embedding, and the write of this step's K and V into
+ * their page slots (transformers Qwen3MoeAttention.forward up to the attention call, with the decode-time form of
+ * the page write at kv_cache/cache_manager.py:185-214): b200_dense_gemm_bf16 with the work of
+ * b200_qk_norm_rope_append in its epilogue.  A weight tile is one head (head_dim 128); the tile's bf16 result is
+ * normalised, rotated and stored from shared memory, so the [rows, heads, 128] projection output never goes to
+ * global memory.  Same results, bit for bit, as the two separate calls (the projection without a K split).
+ *
+ *   x [num_rows, in_features] bf16; wqkv [(Hq + 2 Hkv) * 128, in_features] bf16: q heads, k heads, v heads
+ *   other arguments as b200_qk_norm_rope_append
+ */
+int b200_qkv_rope_append_supported(int head_dim, int in_features);
+int b200_qkv_rope_append_gemm(const void* x, const void* wqkv, const void* q_norm_weight,
+                              const void* k_norm_weight, const void* cos_table, const void* sin_table,
+                              const int32_t* positions, const int32_t* block_table, void* q_out, void* k_pool,
+                              void* v_pool, void* status_word, int num_rows, int num_q_heads, int num_kv_heads,
+                              int head_dim, int in_features, float eps, int page_size, int num_blocks,
+                              int max_pages_per_seq, int max_positions, void* stream);
+
+/*
  * Replaces: lm_head followed by the argmax over the vocabulary (torch_backend.py:314-321:
  * `outputs.logits[:, -1, :].argmax(dim=-1)`).  The same GEMM with a running arg-max per row kept in registers
  * across the vocabulary tiles; the [num_rows, vocab] logits are never written.  The largest fp32 logit wins,

@@ -31,6 +31,8 @@ SIGNATURES = {
     "b200_kv_append": (c_int, [c_void_p] * 7 + [c_int] * 7 + [c_void_p]),
     "b200_dense_gemm_workspace_bytes": (c_size_t, [c_int, c_int]),
     "b200_dense_gemm_bf16": (c_int, [c_void_p] * 4 + [c_size_t, c_void_p] + [c_int] * 4 + [c_void_p]),
+    "b200_qkv_rope_append_supported": (c_int, [c_int, c_int]),
+    "b200_qkv_rope_append_gemm": (c_int, [c_void_p] * 12 + [c_int] * 5 + [c_float] + [c_int] * 4 + [c_void_p]),
     "b200_lm_head_argmax_workspace_bytes": (c_size_t, []),
     "b200_lm_head_argmax": (c_int, [c_void_p] * 4 + [c_size_t, c_void_p] + [c_int] * 3 + [c_void_p]),
     "b200_add_rmsnorm_route_supported": (c_int, [c_int] * 3),

@@ -58,14 +58,17 @@ constexpr int kDenseXBytesMax = 256 * 128;        // largest X box of a stage
 constexpr int kDenseThreads = 10 * 32;           // TMA warp, MMA warp, 8 epilogue warps
 constexpr int kDenseMaxRows = 256;                // rows of X per MMA (its N)
 
-enum : int { kEpiStore = 0, kEpiArgmax = 1 };
+enum : int { kEpiStore = 0, kEpiArgmax = 1, kEpiQkvRope = 2 };
+constexpr int kQkvStageBytes = kDenseMaxRows * 128 * 2;  // kEpiQkvRope: one head of up to 256 rows, bf16
 
-template <int A_TILES>
+template <int A_TILES, int EPI = kEpiStore>
 struct DenseCfg {
-  static constexpr int kStages = A_TILES == 1 ? 4 : 3;
+  // the q/k/v epilogue keeps a bf16 copy of one head's tile beside the ring and gives a stage for it
+  static constexpr int kStages = (A_TILES == 1 && EPI != kEpiQkvRope) ? 4 : 3;
   static constexpr int kStageBytes = A_TILES * kDenseWBytes + kDenseXBytesMax;
-  static constexpr int kRingBytes = kStages * kStageBytes;  // 192 KiB either way
-  static constexpr int kSmemBytes = kRingBytes + 1024 /* alignment */ + 256 /* barriers, tmem base */;
+  static constexpr int kRingBytes = kStages * kStageBytes;  // 192 KiB, or 144 KiB + 64 KiB of head tile
+  static constexpr int kExtraBytes = EPI == kEpiQkvRope ? kQkvStageBytes : 0;
+  static constexpr int kSmemBytes = kRingBytes + kExtraBytes + 1024 /* alignment */ + 256 /* barriers, tmem base */;
 };
 
 struct DenseParams {
@@ -73,6 +76,19 @@ struct DenseParams {
   float* part_val;    // kEpiArgmax: [grid * 4, 256] candidates per TMEM lane quarter
   int* part_idx;
   float* exchange;    // kEpiStore, split K: [tile][finishing CTA][source CTA][rows_per][128] fp32
+  // kEpiQkvRope: the q/k/v projection of heads of 128 with per-head RMSNorm, RoPE and the page write in its
+  // epilogue (what b200_qk_norm_rope_append does after a plain projection)
+  const __nv_bfloat16* q_norm_w;
+  const __nv_bfloat16* k_norm_w;
+  const __nv_bfloat16* cos_t;
+  const __nv_bfloat16* sin_t;
+  const int* positions;
+  const int* block_table;
+  __nv_bfloat16* q_out;
+  __nv_bfloat16* k_pool;
+  __nv_bfloat16* v_pool;
+  float eps;
+  int hq, hkv, page, num_blocks, max_pages, max_pos;
   int* err;
   int M, N, K;
   int m_tiles;        // ceil(M / xbox)
@@ -125,15 +141,15 @@ __global__ void __launch_bounds__(kDenseThreads, 1)
 dense_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant__ CUtensorMap x_map,
                   const DenseParams p) {
 #ifdef B200_DEVICE_OK
-  using Cfg = DenseCfg<A_TILES>;
+  using Cfg = DenseCfg<A_TILES, EPI>;
   constexpr int kStages = Cfg::kStages;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t ring = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* ring_ptr = smem_raw + (ring - smem_u32(smem_raw));
-  const uint32_t bars = ring + Cfg::kRingBytes;
+  const uint32_t bars = ring + Cfg::kRingBytes + Cfg::kExtraBytes;
   const uint32_t bar_full = bars, bar_empty = bars + 8 * kStages;
   const uint32_t bar_tfull = bars + 16 * kStages, bar_tempty = bar_tfull + 16;
-  uint32_t* tmem_base_sm = reinterpret_cast<uint32_t*>(ring_ptr + Cfg::kRingBytes + 16 * kStages + 32);
+  uint32_t* tmem_base_sm = reinterpret_cast<uint32_t*>(ring_ptr + Cfg::kRingBytes + Cfg::kExtraBytes + 16 * kStages + 32);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   // accumulator buffers: one W tile -> two buffers of 256 columns that alternate between work items;
@@ -245,15 +261,45 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_consta
       const int tile = w / ks;
       const int nt = tile / p.m_tiles, mt = tile - nt * p.m_tiles;
       const uint32_t buf = item % kBufs, aphase = (item / kBufs) & 1;
+      const int m0 = mt * p.xbox;
+      // kEpiQkvRope: position and page of the rows this warp will finish (lane i: row (warp - 2) + 8 i of the
+      // tile), fetched while the MMAs of the item are still running; -1 = not a row, or reported as bad
+      int row_pos = -1, row_page = -1;
+      if (EPI == kEpiQkvRope) {
+        const int r = (warp - 2) + 8 * lane, m = m0 + r;
+        if (r < p.xbox && m < p.M) {
+          const int ps = p.positions[m];
+          if (ps < 0 || ps >= p.max_pos || ps >= p.max_pages * p.page) {
+            set_error(p.err, kErrDevBadCtxLen);
+          } else {
+            row_pos = ps;
+            if (nt >= p.hq) {  // k and v heads go to the page of that position
+              const int id = p.block_table[static_cast<size_t>(m) * p.max_pages + ps / p.page];
+              if (id < 0 || id >= p.num_blocks) set_error(p.err, kErrDevBadBlockId);
+              else row_page = id;
+            }
+          }
+        }
+      }
       alive = mbar_wait(bar_tfull + 8 * buf, aphase, p.err);
       if (!alive) break;
       tc_fence_after();
-      const int m0 = mt * p.xbox;
 #pragma unroll
       for (int a = 0; a < A_TILES; ++a) {
         const int n = (nt * A_TILES + a) * 128 + t;
         const uint32_t t0 = lane_addr + (A_TILES == 1 ? buf : static_cast<uint32_t>(a)) * kDenseMaxRows;
-        if (EPI == kEpiStore) {
+        if (EPI == kEpiQkvRope) {
+          // the tile is one head (128 features) of up to 256 rows: a bf16 copy goes to shared memory as
+          // [row][feature] - the projection's output is bf16 in the model, so this rounding is the model's
+          __nv_bfloat16* head = reinterpret_cast<__nv_bfloat16*>(ring_ptr + Cfg::kRingBytes);
+          for (int c = half; c < chunks; c += 2) {
+            uint32_t v[32];
+            tmem_ld32(t0 + c * 32, v);
+            tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) head[(c * 32 + i) * 128 + t] = __float2bfloat16(__uint_as_float(v[i]));
+          }
+        } else if (EPI == kEpiStore) {
           for (int c = half; c < chunks; c += 2) {
             uint32_t v[32];
             tmem_ld32(t0 + c * 32, v);
@@ -283,10 +329,87 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_consta
           }
         }
       }
-      // everything this thread needs from the accumulator is in registers
+      // everything this thread needs from the accumulator is in registers (or shared memory)
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(bar_tempty + 8 * buf);
+      if (EPI == kEpiQkvRope) {
+        // ---- per row of X: RMSNorm over the head (q and k), RoPE (rotate-half), then q to its output row
+        // and k / v into their page slot; warp e takes rows e, e + 8, ...; lane l holds d = l + 32 j.  Position
+        // and page of every row were fetched before the accumulator was awaited (lane i: the warp's i-th row), and
+        // the rows go four at a time so that their cos/sin loads are in flight together: done one row after the
+        // other, the dependent loads of 16-32 rows per warp cost more than the separate kernel they replace.
+        asm volatile("bar.sync 1, 256;" ::: "memory");  // the eight epilogue warps: the head tile is complete
+        const __nv_bfloat16* head = reinterpret_cast<const __nv_bfloat16*>(ring_ptr + Cfg::kRingBytes);
+        const int h = nt;  // weight tile = head: q heads, then k heads, then v heads
+        const bool is_q = h < p.hq, is_k = !is_q && h < p.hq + p.hkv;
+        const __nv_bfloat16* nw = is_q ? p.q_norm_w : p.k_norm_w;
+        float nwf[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) nwf[j] = (is_q || is_k) ? __bfloat162float(nw[lane + 32 * j]) : 1.f;
+        const int my_rows = p.xbox / 8;  // rows this warp handles: 4..32
+        for (int i0 = 0; i0 < my_rows; i0 += 4) {
+          int pos[4], dstoff_ok[4];
+          __nv_bfloat16* dst[4];
+          float v[4][4], cs[4][4], sn[4][4];
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            const int i = i0 + u;
+            pos[u] = __shfl_sync(0xffffffffu, row_pos, i & 31);
+            const int id = __shfl_sync(0xffffffffu, row_page, i & 31);
+            const int r = (warp - 2) + 8 * i, m = m0 + r;
+            dstoff_ok[u] = i < my_rows && pos[u] >= 0 && (is_q || id >= 0);
+            if (dstoff_ok[u]) {
+#pragma unroll
+              for (int j = 0; j < 4; ++j) v[u][j] = __bfloat162float(head[r * 128 + lane + 32 * j]);
+              if (is_q || is_k) {
+                const __nv_bfloat16* c = p.cos_t + static_cast<size_t>(pos[u]) * 128;
+                const __nv_bfloat16* sp = p.sin_t + static_cast<size_t>(pos[u]) * 128;
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                  cs[u][j] = __bfloat162float(c[lane + 32 * j]);
+                  sn[u][j] = __bfloat162float(sp[lane + 32 * j]);
+                }
+              }
+              if (is_q) {
+                dst[u] = p.q_out + (static_cast<size_t>(m) * p.hq + h) * 128;
+              } else {
+                const int kvh = is_k ? h - p.hq : h - p.hq - p.hkv;
+                __nv_bfloat16* pool = is_k ? p.k_pool : p.v_pool;
+                dst[u] = pool + ((static_cast<size_t>(id) * p.hkv + kvh) * p.page + pos[u] % p.page) * 128;
+              }
+            }
+          }
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            if (!dstoff_ok[u]) continue;  // uniform across the warp
+            if (is_q || is_k) {
+              float ss = 0.f;
+#pragma unroll
+              for (int j = 0; j < 4; ++j) ss += v[u][j] * v[u][j];
+              ss = warp_sum(ss);
+              const float inv = rsqrtf(ss / 128.f + p.eps);
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                const float nrm = __bfloat162float(__float2bfloat16(v[u][j] * inv));
+                v[u][j] = __bfloat162float(__float2bfloat16(nwf[j] * nrm));
+              }
+              float rot[4];
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                const int jp = (j + 2) & 3;  // partner element d +- 64 lives in the same lane
+                const float other = j < 2 ? -v[u][jp] : v[u][jp];
+                rot[j] = v[u][j] * cs[u][j] + other * sn[u][j];
+              }
+#pragma unroll
+              for (int j = 0; j < 4; ++j) v[u][j] = rot[j];
+            }
+#pragma unroll
+            for (int j = 0; j < 4; ++j) dst[u][lane + 32 * j] = __float2bfloat16(v[u][j]);
+          }
+        }
+        asm volatile("bar.sync 1, 256;" ::: "memory");  // the head tile may be overwritten by the next item
+      }
     }
     if (EPI == kEpiArgmax) {
       // one warp-wide maximum per row of X, once: lane l ends up with the winners of rows l, l+32, l+64, l+96
@@ -538,7 +661,7 @@ static int plan_dense(int M, int n_tiles, int k_blocks, int sms, size_t workspac
 template <int A_TILES, int EPI>
 static int launch_dense(const CUtensorMap& w_map, const CUtensorMap& x_map, const DenseParams& p, int grid,
                         cudaStream_t st) {
-  using Cfg = DenseCfg<A_TILES>;
+  using Cfg = DenseCfg<A_TILES, EPI>;
   const void* fn = reinterpret_cast<const void*>(&dense_gemm_kernel<A_TILES, EPI>);
   int rc = ensure_dynamic_smem(fn, Cfg::kSmemBytes);
   if (rc) return rc;
@@ -622,6 +745,79 @@ extern "C" int b200_dense_gemm_bf16(const void* x, const void* w, void* y, void*
   // with a cluster every CTA has exactly one work item; without, a CTA walks items persistently
   const int grid = p.ksplit > 1 ? items : (items < sms ? items : sms);
   return launch_dense<1, kEpiStore>(w_map, x_map, p, grid, as_stream(stream));
+}
+
+extern "C" int b200_qkv_rope_append_supported(int head_dim, int in_features) {
+  return head_dim == 128 && in_features > 0 && in_features % kDenseBlockK == 0;
+}
+
+extern "C" int b200_qkv_rope_append_gemm(const void* x, const void* wqkv, const void* q_norm_weight,
+                                         const void* k_norm_weight, const void* cos_table, const void* sin_table,
+                                         const int32_t* positions, const int32_t* block_table, void* q_out,
+                                         void* k_pool, void* v_pool, void* status_word, int num_rows,
+                                         int num_q_heads, int num_kv_heads, int head_dim, int in_features, float eps,
+                                         int page_size, int num_blocks, int max_pages_per_seq, int max_positions,
+                                         void* stream) {
+  const int heads = num_q_heads + 2 * num_kv_heads;
+  int rc = dense_args_ok(x, wqkv, num_rows, heads * head_dim, in_features, "qkv_rope_append_gemm");
+  if (rc) return rc;
+  B200_REQUIRE(q_norm_weight && k_norm_weight && cos_table && sin_table && positions && block_table && q_out && k_pool &&
+                   v_pool,
+               "qkv_rope_append_gemm: null pointer");
+  B200_REQUIRE(b200_qkv_rope_append_supported(head_dim, in_features),
+               "qkv_rope_append_gemm: head_dim %d must be 128 (one head per weight tile)", head_dim);
+  B200_REQUIRE(num_q_heads > 0 && num_kv_heads > 0 && page_size > 0 && num_blocks > 0 && max_pages_per_seq > 0 &&
+                   max_positions > 0,
+               "qkv_rope_append_gemm: non-positive dimension");
+  rc = check_device(nullptr);
+  if (rc) return rc;
+  int sms = 148;
+  rc = device_sm_count(&sms);
+  if (rc) return rc;
+  DenseParams p{};
+  p.err = static_cast<int*>(status_word);
+  p.M = num_rows;
+  p.N = heads * head_dim;
+  p.K = in_features;
+  p.n_tiles = heads;
+  p.ksplit = 1;
+  // rows per item: the width that needs the fewest waves of CTAs, then the least data per CTA
+  p.xbox = pick_xbox(num_rows);
+  {
+    double best = 1e30;
+    for (int xbox = p.xbox; xbox >= 32; xbox >>= 1) {
+      const int items = heads * ((num_rows + xbox - 1) / xbox);
+      const double cost = static_cast<double>((items + sms - 1) / sms) * (128.0 + xbox) + xbox * 0.25;
+      if (cost < best) {
+        best = cost;
+        p.xbox = xbox;
+      }
+    }
+  }
+  p.m_tiles = (num_rows + p.xbox - 1) / p.xbox;
+  p.q_norm_w = static_cast<const __nv_bfloat16*>(q_norm_weight);
+  p.k_norm_w = static_cast<const __nv_bfloat16*>(k_norm_weight);
+  p.cos_t = static_cast<const __nv_bfloat16*>(cos_table);
+  p.sin_t = static_cast<const __nv_bfloat16*>(sin_table);
+  p.positions = positions;
+  p.block_table = block_table;
+  p.q_out = static_cast<__nv_bfloat16*>(q_out);
+  p.k_pool = static_cast<__nv_bfloat16*>(k_pool);
+  p.v_pool = static_cast<__nv_bfloat16*>(v_pool);
+  p.eps = eps;
+  p.hq = num_q_heads;
+  p.hkv = num_kv_heads;
+  p.page = page_size;
+  p.num_blocks = num_blocks;
+  p.max_pages = max_pages_per_seq;
+  p.max_pos = max_positions;
+  CUtensorMap w_map, x_map;
+  rc = get_tensor_map_2d(wqkv, p.N, in_features, 2, 128, 64, &w_map);
+  if (rc) return rc;
+  rc = get_tensor_map_2d(x, num_rows, in_features, 2, p.xbox, 64, &x_map);
+  if (rc) return rc;
+  const int items = p.n_tiles * p.m_tiles;
+  return launch_dense<1, kEpiQkvRope>(w_map, x_map, p, items < sms ? items : sms, as_stream(stream));
 }
 
 extern "C" size_t b200_lm_head_argmax_workspace_bytes(void) {

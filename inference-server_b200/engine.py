@@ -200,6 +200,7 @@ class DecodeEngine:
         self.moe_ws = ops.moe_fp8_workspace(max_batch, cfg.experts, cfg.top_k, cfg.hidden, cfg.moe_inter, self.device)
         self.gemm_status = torch.zeros(64, dtype=torch.int32, device=self.device)  # dense projections, lm_head
         self._fused_router = ops.add_rmsnorm_route_supported(cfg.hidden, cfg.experts, cfg.top_k)
+        self._fused_qkv = ops.qkv_rope_append_supported(cfg.head_dim, cfg.hidden)
         widest = max((cfg.q_heads + 2 * cfg.kv_heads) * cfg.head_dim, cfg.hidden, cfg.experts)
         self.gemm_ws = ops.dense_gemm_workspace(min(max_batch, 256), widest, self.device)  # K-split partial tiles
         self.argmax_ws = ops.lm_head_argmax_workspace(self.device)
@@ -239,10 +240,11 @@ class DecodeEngine:
             # The exchange has one shape, so there is one graph; it is built here, where every rank is (its
             # warm-up runs are real exchanges and must happen on all ranks together), with padding rows only.
             self._build_graph(self.max_batch, pad_from=0)
-        # per layer: qkv GEMM, qk_norm_rope_append, attention + split reduce, o GEMM, norm + router + top-k (one
+        # per layer: qkv GEMM with norm/RoPE/page write (two kernels for head sizes other than 128), attention +
+        # split reduce, o GEMM, norm + router + top-k (one
         # kernel; three where its shape limits do not hold), rank, scatter+quant, expert GEMM x2, combine+norm;
         # + the first norm, lm_head with arg-max and its fold
-        self.kernel_launches_per_step = cfg.layers * (11 if self._fused_router else 13) + 3
+        self.kernel_launches_per_step = cfg.layers * ((11 if self._fused_router else 13) - (1 if self._fused_qkv else 0)) + 3
         if self.ep_world > 1:
             # the local re-sort of received rows (rank + scatter + row gather), and with the peer-memory
             # transport the two flag exchanges
@@ -269,9 +271,14 @@ class DecodeEngine:
         x = self.embed[tokens]
         h = ops.add_rmsnorm(x, None, self.layers[0].ln1, cfg.rms_eps)
         for li, w in enumerate(self.layers):
-            qkv = ops.dense_gemm(h, w.wqkv, status=self.gemm_status, workspace=self.gemm_ws).view(R, Hq + 2 * Hkv, D)
-            q = ops.qk_norm_rope_append(qkv, w.q_norm, w.k_norm, self.cos, self.sin, pos, table, self.k_pools[li],
-                                        self.v_pools[li], Hq, cfg.rms_eps, attn_ws)
+            if self._fused_qkv:
+                # projection with q/k norm, RoPE and the K/V page write in its epilogue
+                q = ops.qkv_rope_append_gemm(h, w.wqkv, w.q_norm, w.k_norm, self.cos, self.sin, pos, table,
+                                             self.k_pools[li], self.v_pools[li], Hq, cfg.rms_eps, self.gemm_status)
+            else:
+                qkv = ops.dense_gemm(h, w.wqkv, status=self.gemm_status, workspace=self.gemm_ws).view(R, Hq + 2 * Hkv, D)
+                q = ops.qk_norm_rope_append(qkv, w.q_norm, w.k_norm, self.cos, self.sin, pos, table, self.k_pools[li],
+                                            self.v_pools[li], Hq, cfg.rms_eps, attn_ws)
             if chunk_of is not None:
                 first_pos, n_real = chunk_of
                 attn = q.new_zeros(R, Hq, D) if n_real < R else torch.empty_like(q)

@@ -213,6 +213,38 @@ def dense_gemm(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor | None = None
     return out
 
 
+def qkv_rope_append_supported(head_dim: int, in_features: int) -> bool:
+    return bool(_lib.load().b200_qkv_rope_append_supported(int(head_dim), int(in_features)))
+
+
+def qkv_rope_append_gemm(x, wqkv, q_norm_w, k_norm_w, cos, sin, positions, block_table, k_pool, v_pool, num_q_heads,
+                         eps: float, status=None, q_out=None) -> torch.Tensor:
+    """The q/k/v projection with per-head q/k RMSNorm, RoPE and the K/V page write in its epilogue: q returned
+    [rows, Hq, 128], k and v written into their page slots.  dense_gemm + qk_norm_rope_append in one kernel."""
+    _need(x, "x", torch.bfloat16)
+    _need(wqkv, "wqkv", torch.bfloat16)
+    _need(cos, "cos", torch.bfloat16)
+    _need(sin, "sin", torch.bfloat16)
+    _need(positions, "positions", torch.int32)
+    _need(block_table, "block_table", torch.int32)
+    _need(k_pool, "k_pool", torch.bfloat16)
+    _need(v_pool, "v_pool", torch.bfloat16)
+    R, K = x.shape
+    nb, Hkv, page, D = k_pool.shape
+    if wqkv.shape != ((num_q_heads + 2 * Hkv) * D, K):
+        raise ValueError("wqkv does not match the heads and the input width")
+    if q_out is None:
+        q_out = torch.empty(R, num_q_heads, D, dtype=torch.bfloat16, device=x.device)
+    if R == 0:
+        return q_out
+    rc = _lib.load().b200_qkv_rope_append_gemm(
+        _ptr(x), _ptr(wqkv), _ptr(q_norm_w), _ptr(k_norm_w), _ptr(cos), _ptr(sin), _ptr(positions), _ptr(block_table),
+        _ptr(q_out), _ptr(k_pool), _ptr(v_pool), _ptr(status), R, num_q_heads, Hkv, D, K, float(eps), page, nb,
+        block_table.shape[1], cos.shape[0], _stream())
+    check(rc, "b200_qkv_rope_append_gemm")
+    return q_out
+
+
 def lm_head_argmax_workspace(device) -> torch.Tensor:
     return torch.zeros(_lib.load().b200_lm_head_argmax_workspace_bytes(), dtype=torch.uint8, device=device)
 

@@ -102,3 +102,50 @@ def test_lm_head_argmax_agrees_with_argmax_of_the_written_logits(ops):
     picked = logits[torch.arange(64, device=DEV), tok]
     # the written logits are rounded to bf16, which creates ties that the fp32 comparison does not see
     assert bool((picked == logits.max(dim=1).values).all())
+
+
+@pytest.mark.parametrize("R,hq,hkv,K", [(256, 32, 4, 2048), (1, 32, 4, 2048), (37, 64, 4, 4096), (300, 8, 2, 512)])
+def test_qkv_projection_with_norm_rope_and_page_write_equals_the_two_kernels(ops, R, hq, hkv, K):
+    """b200_qkv_rope_append_gemm against b200_dense_gemm_bf16 (no K split) + b200_qk_norm_rope_append: the query
+    rows and every page of both pools must come out bit for bit the same."""
+    D, page, max_pages = 128, 16, 6
+    assert ops.qkv_rope_append_supported(D, K)
+    g = torch.Generator().manual_seed(R + K)
+    x = torch.randn(R, K, generator=g).bfloat16().to(DEV)
+    w = (torch.randn((hq + 2 * hkv) * D, K, generator=g) * 0.03).bfloat16().to(DEV)
+    qn = (1 + 0.1 * torch.randn(D, generator=g)).bfloat16().to(DEV)
+    kn = (1 + 0.1 * torch.randn(D, generator=g)).bfloat16().to(DEV)
+    ang = torch.arange(max_pages * page, dtype=torch.float32)[:, None] / (1e6 ** (torch.arange(0, D, 2) / D))[None, :]
+    emb = torch.cat([ang, ang], dim=-1)
+    cos, sin = emb.cos().bfloat16().to(DEV), emb.sin().bfloat16().to(DEV)
+    pos = torch.randint(0, max_pages * page, (R,), generator=g).to(torch.int32).to(DEV)
+    nb = R * max_pages + 3
+    table = torch.randperm(nb, generator=g)[: R * max_pages].view(R, max_pages).to(torch.int32).to(DEV)
+    pools = [torch.randn(nb, hkv, page, D, generator=g).bfloat16().to(DEV) for _ in range(2)]
+    k1, v1, k2, v2 = pools[0].clone(), pools[1].clone(), pools[0].clone(), pools[1].clone()
+    status = torch.zeros(64, dtype=torch.int32, device=DEV)
+    q1 = ops.qkv_rope_append_gemm(x, w, qn, kn, cos, sin, pos, table, k1, v1, hq, 1e-6, status)
+    ops.read_status(status, "qkv_rope_append_gemm")
+    qkv = ops.dense_gemm(x, w, k_split=1).view(R, hq + 2 * hkv, D)
+    q2 = ops.qk_norm_rope_append(qkv, qn, kn, cos, sin, pos, table, k2, v2, hq, 1e-6, status)
+    ops.read_status(status, "qk_norm_rope_append")
+    assert torch.equal(q1, q2)
+    assert torch.equal(k1, k2) and torch.equal(v1, v2)
+    assert not torch.equal(k1, pools[0])  # something was written
+
+
+def test_qkv_projection_epilogue_reports_bad_positions_and_pages(ops):
+    R, hq, hkv, K, D = 4, 32, 4, 2048, 128
+    g = torch.Generator().manual_seed(0)
+    x = torch.randn(R, K, generator=g).bfloat16().to(DEV)
+    w = (torch.randn((hq + 2 * hkv) * D, K, generator=g) * 0.03).bfloat16().to(DEV)
+    one = torch.ones(D, dtype=torch.bfloat16, device=DEV)
+    cs = torch.ones(64, D, dtype=torch.bfloat16, device=DEV)
+    pool = torch.zeros(8, hkv, 16, D, dtype=torch.bfloat16, device=DEV)
+    table = torch.zeros(R, 4, dtype=torch.int32, device=DEV)
+    table[2, 0] = 99  # outside the pool
+    pos = torch.tensor([0, 1, 2, 3], dtype=torch.int32, device=DEV)
+    status = torch.zeros(64, dtype=torch.int32, device=DEV)
+    ops.qkv_rope_append_gemm(x, w, one, one, cs, cs, pos, table, pool, pool.clone(), hq, 1e-6, status)
+    with pytest.raises(Exception, match="block table entry"):
+        ops.read_status(status, "qkv_rope_append_gemm")
