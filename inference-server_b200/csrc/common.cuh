@@ -56,6 +56,22 @@ __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
 }
 
+// Programmatic dependent launch.  grid_dep_wait(): hold until every kernel this one depends on has completed and
+// its writes are visible (returns at once when the kernel was launched the ordinary way).  Every thread calls it
+// before its first access to global memory and before any return, so that "this grid has completed" always
+// implies "everything before it in the stream has completed".  grid_dep_launch(): the kernel after this one may
+// have its blocks placed (they hold at their own grid_dep_wait()) once every block of this grid has said so.
+__device__ __forceinline__ void grid_dep_wait() {
+#ifdef B200_DEVICE_OK
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+#endif
+}
+__device__ __forceinline__ void grid_dep_launch() {
+#ifdef B200_DEVICE_OK
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+#endif
+}
+
 __device__ __forceinline__ void set_error(int* err, int code) {
   if (err != nullptr) atomicCAS(err, 0, code);
 }

@@ -177,6 +177,10 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_consta
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_base_sm;
+  // Everything above is this CTA's own set-up; X (and the buffers the epilogues write) belong to the kernels
+  // before this one.
+  grid_dep_wait();
+  grid_dep_launch();
 
   const int ks = p.ksplit;
   const int kb_per = p.K / kDenseBlockK / ks;  // K blocks of one work item
@@ -540,6 +544,8 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_consta
 __global__ void __launch_bounds__(128)
 argmax_fold_kernel(const float* __restrict__ part_val, const int* __restrict__ part_idx, int parts, int M,
                    long long* __restrict__ out) {
+  grid_dep_wait();
+  grid_dep_launch();
   const int m = blockIdx.x * 4 + (threadIdx.x >> 5);
   const int lane = threadIdx.x & 31;
   if (m >= M) return;
@@ -666,8 +672,13 @@ static int launch_dense(const CUtensorMap& w_map, const CUtensorMap& x_map, cons
   int rc = ensure_dynamic_smem(fn, Cfg::kSmemBytes);
   if (rc) return rc;
   cudaLaunchConfig_t cfg;
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
   cluster_launch_config(&cfg, attr, grid, Cfg::kSmemBytes, p.ksplit, st);
+  if (overlapped_launch_enabled()) {  // the kernel holds at grid_dep_wait() after its set-up
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.numAttrs = 2;
+  }
   B200_CUDA(cudaLaunchKernelEx(&cfg, dense_gemm_kernel<A_TILES, EPI>, w_map, x_map, p));
   return 0;
 }
@@ -863,8 +874,7 @@ extern "C" int b200_lm_head_argmax(const void* x, const void* w, int64_t* next_t
   if (rc) return rc;
   rc = launch_dense<2, kEpiArgmax>(w_map, x_map, p, grid, as_stream(stream));
   if (rc) return rc;
-  argmax_fold_kernel<<<(num_rows + 3) / 4, 128, 0, as_stream(stream)>>>(p.part_val, p.part_idx, grid * 4, num_rows,
-                                                                       reinterpret_cast<long long*>(next_tokens));
-  B200_CUDA(cudaGetLastError());
+  B200_CUDA(launch_overlapped(argmax_fold_kernel, dim3((num_rows + 3) / 4), dim3(128), 0, as_stream(stream), p.part_val,
+                              p.part_idx, grid * 4, num_rows, reinterpret_cast<long long*>(next_tokens)));
   return 0;
 }

@@ -3,6 +3,7 @@
 
 #include <stdarg.h>
 #include <stdio.h>
+#include <stdlib.h>
 #include <string.h>
 
 #include <mutex>
@@ -72,6 +73,14 @@ int check_device(int* device_out) {
   }
   if (device_out) *device_out = f.device;
   return 0;
+}
+
+bool overlapped_launch_enabled() {
+  static const bool enabled = [] {
+    const char* v = getenv("B200_SERIAL_LAUNCH");
+    return !(v && v[0] != '\0' && v[0] != '0');
+  }();
+  return enabled;
 }
 
 int device_sm_count(int* out) {

@@ -35,6 +35,31 @@ const char* get_detail();
 
 inline cudaStream_t as_stream(void* s) { return reinterpret_cast<cudaStream_t>(s); }
 
+// True unless the environment variable B200_SERIAL_LAUNCH is set to a non-zero value (read once).
+bool overlapped_launch_enabled();
+
+// Launches a kernel that begins with grid_dep_wait() (common.cuh) as a programmatic dependent of the kernel before
+// it in the stream: its blocks may be placed on the multiprocessors while that kernel drains and they hold at
+// grid_dep_wait() until it has completed and its writes are visible, which takes the launch latency and the
+// block placement off the critical path between two kernels.  Captured into a CUDA graph the edge becomes a
+// programmatic dependency.  Only for kernels whose every thread executes grid_dep_wait() before it touches
+// global memory or returns.
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_overlapped(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st,
+                                     Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = overlapped_launch_enabled() ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 }  // namespace b200
 
 #define B200_REQUIRE(cond, ...)            \

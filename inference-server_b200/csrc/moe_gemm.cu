@@ -124,6 +124,9 @@ moe_fp8_gemm_kernel(const __grid_constant__ CUtensorMap a_map, const __grid_cons
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_base_sm;
+  // Set-up done; the tile list, the activations and their scales come from the kernels before this one.
+  grid_dep_wait();
+  grid_dep_launch();
 
   int listed = *p.num_tiles;
   if (listed < 0 || listed > p.max_tiles) {
@@ -384,7 +387,8 @@ static int launch_gemm(const AMaps& a, const CUtensorMap& b_map, const GemmParam
   int grid = 148;
   rc = device_sm_count(&grid);
   if (rc) return rc;
-  moe_fp8_gemm_kernel<MODE><<<grid, kGemmThreads, kGemmSmem, st>>>(a.m128, a.m64, a.m32, b_map, p);
+  B200_CUDA(launch_overlapped(moe_fp8_gemm_kernel<MODE>, dim3(grid), dim3(kGemmThreads), kGemmSmem, st, a.m128, a.m64,
+                              a.m32, b_map, p));
   B200_CUDA(cudaGetLastError());
   return 0;
 }

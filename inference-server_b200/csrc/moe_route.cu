@@ -106,6 +106,8 @@ __global__ void __launch_bounds__(kRankThreads)
 moe_rank_kernel(const int* __restrict__ topk_ids, int n_pairs, int* __restrict__ rank,
                 int* __restrict__ counts) {
   __shared__ int part[kRankThreads];
+  grid_dep_wait();
+  grid_dep_launch();
   const int e = blockIdx.x, tid = threadIdx.x;
   const int chunk = (n_pairs + kRankThreads - 1) / kRankThreads;
   const int lo = min(n_pairs, tid * chunk), hi = min(n_pairs, lo + chunk);
@@ -321,6 +323,8 @@ __global__ void moe_scatter_quant_kernel(const __nv_bfloat16* __restrict__ x, co
                                          int* __restrict__ slot_of_pair, int* __restrict__ expert_of_slot,
                                          int* __restrict__ overflow, const EpPeers peers) {
   extern __shared__ int sm[];  // cnt[E], off[E+1], ntile[E], toff[E+1], warp_tot[32], dst[K]
+  grid_dep_wait();
+  grid_dep_launch();
   const bool p2p = peers.xq[0] != nullptr;
   int* cnt = sm;
   int* off = cnt + E;
@@ -465,6 +469,8 @@ __global__ void moe_combine_add_rmsnorm_kernel(const __nv_bfloat16* __restrict__
                                                const __nv_bfloat16* __restrict__ weight, float eps,
                                                __nv_bfloat16* __restrict__ out) {
   __shared__ float red[32];
+  grid_dep_wait();
+  grid_dep_launch();
   const int t = blockIdx.x, tid = threadIdx.x;
   float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
   for (int k = 0; k < K; ++k) {
@@ -623,15 +629,14 @@ static int permute_quant_impl(const int32_t* topk_ids, const void* x, int num_to
   int* err = reinterpret_cast<int*>(p);
   int* counts = reinterpret_cast<int*>(p + 256);
   int* rank = reinterpret_cast<int*>(p + 256 + ((static_cast<size_t>(num_experts) * 4 + 255) & ~size_t(255)));
-  moe_rank_kernel<<<num_experts, kRankThreads, 0, st>>>(topk_ids, num_tokens * top_k, rank, counts);
-  B200_CUDA(cudaGetLastError());
+  B200_CUDA(launch_overlapped(moe_rank_kernel, dim3(num_experts), dim3(kRankThreads), 0, st, topk_ids,
+                              num_tokens * top_k, rank, counts));
   const size_t smem = (4 * static_cast<size_t>(num_experts) + 2 + 32 + top_k) * sizeof(int);
-  moe_scatter_quant_kernel<<<num_tokens, hidden / 8, smem, st>>>(
-      static_cast<const __nv_bfloat16*>(x), topk_ids, rank, counts, num_experts, top_k, hidden, 128,
-      sorted_pair_ids, row_of_pair, expert_offsets, static_cast<MoeTile*>(tiles), num_tiles,
-      static_cast<uint8_t*>(xq), x_scale, err, ep_world, ep_capacity, slot_of_pair, expert_of_slot, overflow,
-      peers);
-  B200_CUDA(cudaGetLastError());
+  B200_CUDA(launch_overlapped(moe_scatter_quant_kernel, dim3(num_tokens), dim3(hidden / 8), smem, st,
+                              static_cast<const __nv_bfloat16*>(x), topk_ids, rank, counts, num_experts, top_k, hidden,
+                              128, sorted_pair_ids, row_of_pair, expert_offsets, static_cast<MoeTile*>(tiles),
+                              num_tiles, static_cast<uint8_t*>(xq), x_scale, err, ep_world, ep_capacity, slot_of_pair,
+                              expert_of_slot, overflow, peers));
   return 0;
 }
 
@@ -729,11 +734,10 @@ extern "C" int b200_moe_combine_add_rmsnorm(const void* y_sorted, const int32_t*
   int rc = check_device(nullptr);
   if (rc) return rc;
   if (num_tokens == 0) return 0;
-  moe_combine_add_rmsnorm_kernel<<<num_tokens, hidden / 8, 0, as_stream(stream)>>>(
-      static_cast<const __nv_bfloat16*>(y_sorted), row_of_pair, topk_weights, hidden, top_k,
-      static_cast<__nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(weight), eps,
-      static_cast<__nv_bfloat16*>(out));
-  B200_CUDA(cudaGetLastError());
+  B200_CUDA(launch_overlapped(moe_combine_add_rmsnorm_kernel, dim3(num_tokens), dim3(hidden / 8), 0, as_stream(stream),
+                              static_cast<const __nv_bfloat16*>(y_sorted), row_of_pair, topk_weights, hidden, top_k,
+                              static_cast<__nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(weight), eps,
+                              static_cast<__nv_bfloat16*>(out)));
   return 0;
 }
 

@@ -70,6 +70,8 @@ paged_attn_decode_kernel(const __grid_constant__ CUtensorMap k_map,
                          int* __restrict__ err, int batch, int num_q_heads, int num_blocks, int max_pages,
                          int split_tokens, int max_splits, float scale_log2) {
 #ifdef B200_DEVICE_OK
+  grid_dep_wait();    // the context lengths, the query rows and the new K/V rows come from the kernels before
+  grid_dep_launch();
   using Cfg = AttnCfg<D, HKV, STAGES, CTAS>;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t ring = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -369,6 +371,8 @@ __global__ void __launch_bounds__(128)
 paged_attn_reduce_kernel(const float* __restrict__ part_o, const float2* __restrict__ part_ml,
                          const int* __restrict__ ctx_lens, __nv_bfloat16* __restrict__ out,
                          int rows_total, int num_q_heads, int max_splits, int split_tokens, int max_ctx) {
+  grid_dep_wait();
+  grid_dep_launch();
   const int row = blockIdx.x * 4 + (threadIdx.x >> 5);
   const int lane = threadIdx.x & 31;
   if (row >= rows_total) return;
@@ -586,17 +590,15 @@ static int launch_main(const void* q, const void* k_pool, const void* v_pool,
   if (rc) return rc;
   dim3 grid(PAIRS ? (batch + 1) / 2 : batch, max_splits);
   const float scale_log2 = scale * 1.4426950408889634f;
-  paged_attn_decode_kernel<D, HKV, STAGES, CTAS, PAIRS><<<grid, Cfg::kThreads, Cfg::kSmemBytes, stream>>>(
-      kmap, vmap, static_cast<const __nv_bfloat16*>(q), block_table, ctx_lens, w.o, w.ml,
-      static_cast<__nv_bfloat16*>(out), w.err, batch, hq, num_blocks, max_pages, split_tokens, max_splits,
-      scale_log2);
-  B200_CUDA(cudaGetLastError());
+  B200_CUDA(launch_overlapped(paged_attn_decode_kernel<D, HKV, STAGES, CTAS, PAIRS>, grid, dim3(Cfg::kThreads),
+                              Cfg::kSmemBytes, stream, kmap, vmap, static_cast<const __nv_bfloat16*>(q), block_table,
+                              ctx_lens, w.o, w.ml, static_cast<__nv_bfloat16*>(out), w.err, batch, hq, num_blocks,
+                              max_pages, split_tokens, max_splits, scale_log2));
   if (max_splits > 1) {
     const int rows = batch * hq;
-    paged_attn_reduce_kernel<D><<<(rows + 3) / 4, 128, 0, stream>>>(
-        w.o, w.ml, ctx_lens, static_cast<__nv_bfloat16*>(out), rows, hq, max_splits, split_tokens,
-        max_pages * kPage);
-    B200_CUDA(cudaGetLastError());
+    B200_CUDA(launch_overlapped(paged_attn_reduce_kernel<D>, dim3((rows + 3) / 4), dim3(128), 0, stream, w.o, w.ml,
+                                ctx_lens, static_cast<__nv_bfloat16*>(out), rows, hq, max_splits, split_tokens,
+                                max_pages * kPage));
   }
   return 0;
 }

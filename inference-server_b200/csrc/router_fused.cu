@@ -94,6 +94,9 @@ add_rmsnorm_route_kernel(const RouterFusedParams p) {
     }
     asm volatile("cp.async.commit_group;" ::: "memory");
   }
+  // The router matrix is a weight; the rows come from the kernels before this one.
+  grid_dep_wait();
+  grid_dep_launch();
 
   // ---- residual add, partial sums of squares: warp w owns rows 2w and 2w + 1
 #pragma unroll
@@ -333,13 +336,15 @@ extern "C" int b200_add_rmsnorm_route(void* x, const void* delta, const void* no
   cfg.blockDim = dim3(kRfThreads);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = as_stream(stream);
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeClusterDimension;
   attr[0].val.clusterDim.x = kRfCluster;
   attr[0].val.clusterDim.y = 1;
   attr[0].val.clusterDim.z = 1;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = 1;
+  cfg.numAttrs = overlapped_launch_enabled() ? 2 : 1;
   B200_CUDA(cudaLaunchKernelEx(&cfg, add_rmsnorm_route_kernel, p));
   return 0;
 }
