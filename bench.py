@@ -364,6 +364,91 @@ def prefill_phase(args, cfg, dev, rank, world):
     print(json.dumps(line))
 
 
+def mixed_phase(args, cfg, dev, engine, table, prompt_lens, spare_blocks, config):
+    """`--phase mixed`: every pass is a decode step of the whole batch AND a prompt chunk of --chunk-tokens tokens
+    of one more sequence (outside the headline metric).  Timed three ways on the same engine: the merged pass
+    (DecodeEngine.mixed_step), and the reference's order - the chunk's own pass, then the decode step from its
+    graph.  value = tokens (decode rows + chunk tokens) per second of the merged pass; e2e = the same through
+    B200Backend.decode_step_with_prefill_chunk with host token buffers."""
+    backend_mod = pkg("backend")
+    B, n = args.batch, args.chunk_tokens
+    g = torch.Generator().manual_seed(7)
+    chunk = torch.randint(0, cfg.vocab_size, (n,), generator=g).tolist()
+    first_pos = args.chunk_first
+    pages = (first_pos + n + PAGE - 1) // PAGE
+    if pages > len(spare_blocks) or pages > engine.max_pages:
+        raise SystemExit(f"--chunk-first {first_pos} + --chunk-tokens {n} need {pages} pages; {len(spare_blocks)} spare, "
+                         f"table {engine.max_pages} wide")
+    blocks = spare_blocks[:pages]
+
+    def timed(fn, reps):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(reps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / reps
+
+    def merged():
+        engine.tokens[:B].copy_(engine.mixed_step(B, chunk, blocks, first_pos)[0])
+
+    def chunk_alone():
+        engine.prefill([0] * first_pos + chunk, blocks, cached_tokens=first_pos, chunk=n)
+
+    def step_alone():
+        engine.tokens[:B].copy_(engine.step(B))
+
+    with ClockSampler(dev.index or 0) as clocks:
+        step_alone()  # builds the graph
+        ms_chunk = timed(chunk_alone, args.steps)
+        ms_step = timed(step_alone, args.steps)
+        clocks.mark()
+        ms_merged = timed(merged, args.steps)
+    engine.check_status("mixed passes")
+    backend = backend_mod.B200Backend(engine, max_new_tokens=0)
+    ctx_now = engine.ctx_lens[:B].cpu().tolist()
+    batch = backend_mod.PagedBatch(rows=[backend_mod.SeqKV(block_ids=table[b][table[b] >= 0].tolist()[:(prompt_lens[b] + args.gen_tokens + PAGE - 1) // PAGE],
+                                                           ctx_len=ctx_now[b]) for b in range(B)])
+    backend._alloc.free = []  # every page is spoken for: the rows own theirs, the chunk's sequence is handed its pages
+    tok_host = torch.randint(0, cfg.vocab_size, (B, 1)).pin_memory()
+
+    def api_pass():
+        partial = backend_mod.SeqKV(block_ids=list(blocks), ctx_len=first_pos)
+        return backend.decode_step_with_prefill_chunk(tok_host, batch, chunk, partial)
+
+    for _ in range(3):
+        api_pass()
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        nxt = api_pass()[0]
+        tok_host.copy_(nxt.view(B, 1))
+    torch.cuda.synchronize()
+    e2e_s = time.perf_counter() - t0
+    tokens = B + n
+    config = dict(config)
+    config["workload"] = (f"{args.model}: decode step of {B} sequences (prompts U{{{args.ctx_min}..{args.ctx_max}}}) merged with a "
+                          f"{n}-token prompt chunk of one more sequence at position {first_pos}, page {PAGE} "
+                          "(outside the headline decode metric)")
+    config["mixed"] = {"merged_pass_ms": ms_merged, "chunk_pass_alone_ms": ms_chunk, "decode_step_alone_ms": ms_step,
+                       "two_passes_ms": ms_chunk + ms_step, "merged_over_two_passes": ms_merged / (ms_chunk + ms_step),
+                       "decode_rows": B, "chunk_tokens": n, "chunk_first_position": first_pos,
+                       "note": "merged and chunk passes are launched eagerly; the decode step alone replays its CUDA graph"}
+    per_layer = (11 if engine._fused_router else 13) - (1 if engine._fused_qkv else 0) + 1  # + the chunk's attention
+    line = {"metric": "decode+prefill tok/s", "value": tokens / (ms_merged / 1e3), "unit": "tok/s", "n_gpus": 1,
+            "steps": args.steps, "warmup": 3, "ms_per_step": ms_merged, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "fp8 experts (e4m3, fp32 accumulate) + bf16 attention/dense", "data": "synthetic",
+            "config": config,
+            "e2e": {"value": tokens * args.steps / e2e_s, "unit": "tok/s", "h2d_bytes_per_step": (B + n) * 8,
+                    "d2h_bytes_per_step": B * 8 + 8, "api": "B200Backend.decode_step_with_prefill_chunk"},
+            "gpu_launches": (cfg.layers * per_layer + 4) * args.steps, "clocks": clocks.summary(), "roofline": None}
+    print(json.dumps(line))
+
+
 def cpu_op_baselines():
     """The op-level oracles of BASELINE configs 2 and 3 timed on the host cores (median of three runs each, a
     bounded sample: config 2 at its full size, config 3 at 256 tokens), in bytes/s on the same algorithmic-bytes
@@ -429,9 +514,12 @@ def main():
     ap.add_argument("--ctx-min", type=int, default=512, help="shortest prompt (tokens)")
     ap.add_argument("--ctx-max", type=int, default=4096, help="longest prompt (tokens)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--phase", default="decode", choices=["decode", "prefill"],
-                    help="decode (the headline metric) or prefill: prompt passes of --prompt-tokens tokens, one GPU")
+    ap.add_argument("--phase", default="decode", choices=["decode", "prefill", "mixed"],
+                    help="decode (the headline metric); prefill: prompt passes of --prompt-tokens tokens, one GPU; "
+                         "mixed: decode steps that each carry a prompt chunk of --chunk-tokens tokens, one GPU")
     ap.add_argument("--prompt-tokens", type=int, default=2048)
+    ap.add_argument("--chunk-tokens", type=int, default=1024, help="--phase mixed: prompt tokens riding along per step")
+    ap.add_argument("--chunk-first", type=int, default=1024, help="--phase mixed: position of the chunk's first token")
     ap.add_argument("--split-tokens", type=int, default=0, help="attention KV split size (0 = the library default)")
     ap.add_argument("--ep-transport", default="p2p", choices=["nccl", "p2p"],
                     help="with --ep: NCCL all-to-all, or stores into the peers' mapped receive buffers")
@@ -519,6 +607,14 @@ def main():
             config["parallelism"] = (f"dp{world} (replicas: disjoint request batches, no data-path collective; "
                                      f"peer memory unavailable: {'; '.join(probe.failures)[:200]})")
         del probe
+    spare_blocks = []
+    if args.phase == "mixed":
+        if world > 1:
+            raise SystemExit("--phase mixed measures one GPU")
+        extra = (args.chunk_first + args.chunk_tokens + PAGE - 1) // PAGE
+        spare_blocks = list(range(num_blocks, num_blocks + extra))  # pages of the sequence whose prompt is being chunked
+        num_blocks += extra
+        max_pages = max(max_pages, extra)
     t_setup = time.time()
     ep_group = torch.distributed.group.WORLD if world > 1 and args.ep else None
     engine = eng_mod.DecodeEngine(cfg, num_blocks=num_blocks, max_batch=args.batch, max_pages_per_seq=max_pages,
@@ -533,12 +629,16 @@ def main():
     for li in range(1, cfg.layers):
         engine.k_pools[li].copy_(engine.k_pools[0])
         engine.v_pools[li].copy_(engine.v_pools[0])
-    engine.block_table.copy_(torch.from_numpy(table))
+    engine.block_table[:, : table.shape[1]].copy_(torch.from_numpy(table))
     engine.ctx_lens.copy_(torch.tensor(prompt_lens, dtype=torch.int32))
     engine.tokens.copy_(torch.randint(0, cfg.vocab_size, (args.batch,), generator=torch.Generator().manual_seed(rank)))
     B = args.batch
     torch.cuda.synchronize()
     setup_s = time.time() - t_setup
+
+    if args.phase == "mixed":
+        mixed_phase(args, cfg, dev, engine, table, prompt_lens, spare_blocks, config)
+        return
 
     def barrier():
         if world > 1:

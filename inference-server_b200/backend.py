@@ -470,6 +470,48 @@ class B200Backend:
             self._check_status("decode_step_batched")
         return out, batch
 
+    def decode_step_with_prefill_chunk(self, current_tokens, batched_kv, chunk_token_ids: list[int], partial_kv,
+                                       attention_mask=None, position_ids=None):
+        """decode_step_batched and prefill_chunk as ONE pass over the model (base.py:89-99 and :71-78 together;
+        the reference's scheduler runs them one after the other, scheduler.py:312-353 and :379-402, and its
+        design notes name the merged pass as "Version B", docs/arch-scheduler.html:269-270).  The weights are
+        streamed once for the decode rows and the chunk's tokens.
+        Returns (next_tokens [B] on the host, batched_kv, kv, token after the chunk, new_len) - the two calls'
+        results side by side.  If the pass cannot run, the pages taken for the chunk go back and neither the
+        batch nor the partial KV has advanced."""
+        eng = self.engine
+        batch: PagedBatch = batched_kv
+        kv = partial_kv if partial_kv is not None else SeqKV(block_ids=[], ctx_len=0)
+        new_len = kv.ctx_len + len(chunk_token_ids)
+        total_pages = (new_len + self.max_new_tokens + PAGE - 1) // PAGE
+        if total_pages > eng.max_pages:
+            raise ValueError(f"{new_len} tokens plus {self.max_new_tokens} reserved need {total_pages} pages; "
+                             f"the block table is {eng.max_pages} wide")
+        for row in batch.rows:
+            if row.ctx_len + 1 > len(row.block_ids) * PAGE:
+                ids, handles = self._take_pages(1)
+                row.block_ids += ids
+                row.private_blocks += handles
+                batch.dirty = True
+        ids, handles = self._take_pages(total_pages - len(kv.block_ids))
+        try:
+            B = self._sync_table(batch)
+            tok = current_tokens.reshape(-1).to(torch.int64)
+            eng.tokens[:B].copy_(tok, non_blocking=True)
+            nxt, last, _ = eng.mixed_step(B, list(chunk_token_ids), kv.block_ids + ids, kv.ctx_len)
+            out = nxt.to("cpu")
+            self._check_status("decode_step_with_prefill_chunk")
+        except BaseException:
+            self._give_back(handles)
+            batch.dirty = True  # the device lengths may have moved; re-upload them from the rows next time
+            raise
+        for row in batch.rows:
+            row.ctx_len += 1
+        kv.block_ids += ids
+        kv.private_blocks += handles
+        kv.ctx_len = new_len
+        return out, batch, kv, last, new_len
+
     # ------------------------------------------- legacy whole-request entry points
     def generate(self, token_ids: list[int], max_tokens: int, template_prefix_len: int = 0,
                  session_id: str = "default") -> list[int]:

@@ -252,13 +252,17 @@ class DecodeEngine:
 
     # ------------------------------------------------------------------ step
     def _forward(self, tokens, pos, table, attn_ws, moe_ws, split_tokens, ep: bool, pairs: bool = False,
-                 chunk_of: tuple[int, int] | None = None) -> torch.Tensor:
+                 chunk_of: tuple[int, int] | None = None, decode_attn: tuple[int, torch.Tensor] | None = None
+                 ) -> torch.Tensor:
         """The layer stack for R rows: row i is token `tokens[i]` at position `pos[i]` of the sequence whose
         pages are `table[i]`; it attends to positions 0..pos[i].  Decode passes one row per sequence; a prompt
         chunk passes one row per prompt token with the sequence's table repeated - the same kernels, reading
         the pages in place either way.  `chunk_of` = (first position, rows): the first `rows` rows are
         consecutive prompt tokens of ONE sequence starting there, and attention runs as the tiled causal kernel
-        (a page fetched once per 128 score rows) instead of one row per token.
+        (a page fetched once per 128 score rows) instead of one row per token.  The rows after the chunk are
+        padding (expert parallelism) unless `decode_attn` = (split_tokens, workspace) is given: then they are
+        decode rows of other sequences, each with its own table row and position, and the decode kernel runs for
+        them beside the chunk's (a mixed pass).
         Returns the final normed hidden states [R, hidden].
 
         Per layer: qkv GEMM, fused q/k norm + RoPE + page write, paged attention, o GEMM, fused
@@ -281,9 +285,13 @@ class DecodeEngine:
                                             self.v_pools[li], Hq, cfg.rms_eps, attn_ws)
             if chunk_of is not None:
                 first_pos, n_real = chunk_of
-                attn = q.new_zeros(R, Hq, D) if n_real < R else torch.empty_like(q)
+                attn = q.new_zeros(R, Hq, D) if n_real < R and decode_attn is None else torch.empty_like(q)
                 ops.paged_attn_prefill(q[:n_real], self.k_pools[li], self.v_pools[li], table[0], first_pos, self.scale,
                                        attn_ws, out=attn[:n_real])
+                if decode_attn is not None and n_real < R:
+                    ops.paged_attn_decode(q[n_real:], self.k_pools[li], self.v_pools[li], table[n_real:],
+                                          new_len[n_real:], self.scale, decode_attn[0], decode_attn[1],
+                                          out=attn[n_real:])
             else:
                 attn = ops.paged_attn_decode(q, self.k_pools[li], self.v_pools[li], table, new_len, self.scale,
                                              split_tokens, attn_ws, pairs=pairs)
@@ -329,10 +337,11 @@ class DecodeEngine:
             ops.read_status(ws, f"{where}: attention ({rows} rows)")
         ops.read_status(self.moe_ws, f"{where}: MoE")
         ops.read_status(self.gemm_status, f"{where}: dense projections")
-        for name in ("_prefill_attn_ws", "_prefill_moe_ws"):
+        for name, what in (("_prefill_attn_ws", "prompt pass (attention)"), ("_prefill_moe_ws", "prompt pass (MoE)"),
+                           ("_mixed_attn_ws", "mixed pass (prompt attention)"), ("_mixed_moe_ws", "mixed pass (MoE)")):
             ws = getattr(self, name, None)
             if ws is not None:
-                ops.read_status(ws, f"{where}: prompt pass ({name[9:-3]})")
+                ops.read_status(ws, f"{where}: {what}")
         st = self.ep_state
         if st is not None:
             if getattr(st, "arena", None) is not None:
@@ -541,6 +550,57 @@ class DecodeEngine:
         first = ops.lm_head_argmax(h_last, self.lm_head, self.argmax_ws, status=self.gemm_status)
         logits = ops.dense_gemm(h_last, self.lm_head, status=self.gemm_status)[0]
         return int(first[0]), logits
+
+    @torch.no_grad()
+    def mixed_step(self, B: int, chunk_token_ids: list[int], block_ids: list[int], first_pos: int,
+                   want_first: bool = True) -> tuple[torch.Tensor, int | None, torch.Tensor | None]:
+        """One pass that is a decode step for rows [0, B) of the static state AND a prompt chunk of one other
+        sequence: its tokens `chunk_token_ids` sit at positions first_pos.. of the sequence whose pages are
+        `block_ids` (earlier positions already written).  The reference runs the two as separate forwards
+        (src/inference_server/scheduler.py:312-353 then :379-402) and names the merged form as the next step
+        (docs/arch-scheduler.html:269-270); merged, the projections' and the experts' weights are streamed once
+        for both, which is most of what a decode step costs.  The chunk's rows come first; every kernel but
+        attention treats the rows alike, and attention runs as the tiled causal kernel for the chunk and the
+        decode kernel for the rest.
+        Returns (next tokens of the B decode rows (device), token after the chunk's last position, its logits);
+        the last two are None unless `want_first`.  Advances ctx_lens of the decode rows by one."""
+        n = len(chunk_token_ids)
+        if self.ep_state is not None:
+            raise ValueError("mixed passes are not built for expert-parallel engines: run the chunk and the step as "
+                             "two rounds")
+        if n == 0 or B < 1 or B > self.max_batch:
+            raise ValueError(f"mixed pass needs a chunk and 1..{self.max_batch} decode rows (got {n} and {B})")
+        if len(block_ids) * PAGE < first_pos + n or len(block_ids) > self.max_pages:
+            raise ValueError("the chunk's sequence needs more pages than it was given or than the block table is wide")
+        cfg = self.cfg
+        if not ops.paged_attn_prefill_supported(cfg.q_heads, cfg.kv_heads, cfg.head_dim, PAGE, torch.bfloat16):
+            raise ValueError("mixed passes need the tiled prompt-attention kernel, which is not built for this head shape")
+        R = n + B
+        if getattr(self, "_mixed_rows", 0) < R:
+            self._mixed_rows = max(R, 2 * getattr(self, "_mixed_rows", 0))
+            self._mixed_moe_ws = ops.moe_fp8_workspace(self._mixed_rows, cfg.experts, cfg.top_k, cfg.hidden,
+                                                       cfg.moe_inter, self.device)
+            self._mixed_attn_ws = torch.zeros(256, dtype=torch.uint8, device=self.device)  # status word only
+        row = torch.zeros(self.max_pages, dtype=torch.int32)
+        row[: len(block_ids)] = torch.tensor(block_ids, dtype=torch.int32)
+        row = row.to(self.device)
+        tokens = torch.cat([torch.tensor(chunk_token_ids, device=self.device), self.tokens[:B]])
+        pos = torch.cat([torch.arange(first_pos, first_pos + n, device=self.device, dtype=torch.int32), self.ctx_lens[:B]])
+        table = torch.cat([row.unsqueeze(0).expand(n, -1), self.block_table[:B]])
+        h = self._forward(tokens, pos, table, self._mixed_attn_ws, self._mixed_moe_ws, 0, False, chunk_of=(first_pos, n),
+                          decode_attn=self._attn_for(B))
+        first = logits = None
+        if want_first:
+            # the chunk's last row and the decode rows are neighbours: lm_head is streamed once for both
+            nxt = ops.lm_head_argmax(h[n - 1:], self.lm_head, self.argmax_ws, status=self.gemm_status)
+            self.next_tokens[:B].copy_(nxt[1:])
+            first = int(nxt[0])
+        else:
+            ops.lm_head_argmax(h[n:], self.lm_head, self.argmax_ws, out=self.next_tokens[:B], status=self.gemm_status)
+        if want_first:
+            logits = ops.dense_gemm(h[n - 1:n], self.lm_head, status=self.gemm_status)[0]
+        self.ctx_lens[:B] += 1
+        return self.next_tokens[:B], first, logits
 
     # ------------------------------------------------------------- accounting
     def weight_bytes_per_step(self, experts_hit_per_layer: float | None = None) -> dict:

@@ -358,3 +358,66 @@ def test_load_model_reads_a_checkpoint_as_the_reference_does(tmp_path, monkeypat
     assert n == 3 and first == 4
     with pytest.raises(Exception):
         be.load_model(str(tmp_path / "missing"))
+
+
+class MixedStub(StubEngine):
+    """StubEngine with the merged pass: decode rows as in step(), chunk's next token = last token + 1."""
+
+    def __init__(self, **kw):
+        super().__init__(**kw)
+        self.mixed_calls, self.fail = [], False
+
+    def mixed_step(self, B, chunk_token_ids, block_ids, first_pos, want_first=True):
+        if self.fail:
+            raise RuntimeError("engine refused the mixed pass")
+        assert len(block_ids) * 16 >= first_pos + len(chunk_token_ids)
+        self.mixed_calls.append((B, len(chunk_token_ids), first_pos))
+        return self.step(B), chunk_token_ids[-1] + 1, None
+
+
+def test_merged_decode_and_prompt_chunk_equals_the_two_calls():
+    """decode_step_with_prefill_chunk leaves the batch, the partial KV and the allocator exactly where
+    prefill_chunk followed by decode_step_batched leaves them (the reference's order, scheduler.py:312-402)."""
+    prompts = [list(range(100, 120)), list(range(300, 333))]
+    new = list(range(500, 540))
+
+    def serve(merged):
+        be = pkg("backend").B200Backend(MixedStub(), max_new_tokens=8)
+        batch, toks = None, []
+        for i, p in enumerate(prompts):
+            kv, first, n = be.prefill(p, f"s{i}")
+            batch = be.splice_into_batched(batch, kv, n)
+            toks.append(first)
+        tok = torch.tensor(toks).view(-1, 1)
+        partial, outs = None, []
+        for lo in range(0, len(new), 16):
+            piece = new[lo:lo + 16]
+            if merged:
+                nxt, batch, partial, last, n = be.decode_step_with_prefill_chunk(tok, batch, piece, partial)
+            else:
+                partial, last, n = be.prefill_chunk(piece, partial)
+                nxt, batch = be.decode_step_batched(tok, batch, None, None)
+            outs.append((nxt.tolist(), last, n))
+            tok = nxt.view(-1, 1)
+        state = ([(r.block_ids, r.ctx_len) for r in batch.rows], partial.block_ids, partial.ctx_len,
+                 sorted(be._alloc.free))
+        return outs, state, be
+
+    outs_a, state_a, _ = serve(False)
+    outs_b, state_b, be = serve(True)
+    assert outs_a == outs_b and state_a == state_b
+    assert be.engine.mixed_calls == [(2, 16, 0), (2, 16, 16), (2, 8, 32)]
+
+
+def test_a_refused_merged_pass_gives_the_chunks_pages_back():
+    be = pkg("backend").B200Backend(MixedStub(num_blocks=32), max_new_tokens=8)
+    kv, first, n = be.prefill(list(range(5)), "s")
+    batch = be.splice_into_batched(None, kv, n)
+    free = len(be._alloc.free)
+    be.engine.fail = True
+    with pytest.raises(RuntimeError, match="refused"):
+        be.decode_step_with_prefill_chunk(torch.tensor([[first]]), batch, list(range(20)), None)
+    assert len(be._alloc.free) == free and batch.rows[0].ctx_len == n
+    be.engine.fail = False
+    nxt, batch, partial, last, m = be.decode_step_with_prefill_chunk(torch.tensor([[first]]), batch, list(range(20)), None)
+    assert int(nxt[0]) == first + 1 and last == 20 and m == 20 and batch.rows[0].ctx_len == n + 1

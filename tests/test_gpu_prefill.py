@@ -55,3 +55,54 @@ def test_prefill_then_decode_matches_prefill_of_the_longer_prompt(ops):
     tok2, logits2 = engine.prefill(prompt + [first], list(range(40, 48)))
     assert rel_err(dec_logits, logits2) < TOL_MODEL
     assert int(nxt[0]) == tok2 or float(torch.topk(logits2.float(), 2).values.diff().abs()) < 0.05
+
+
+def test_merged_decode_step_and_prompt_chunk_equals_the_two_passes(ops):
+    """One pass over the model for the decode rows and a prompt chunk of another sequence gives what the
+    chunk's pass followed by the decode step gives: tokens, the chunk's pages, the decode rows' new K/V and
+    the logits of the step after (which reads everything the merged pass wrote)."""
+    g = torch.Generator().manual_seed(5)
+    prompts = [torch.randint(0, 4096, (n,), generator=g).tolist() for n in (37, 90)]
+    new = torch.randint(0, 4096, (75,), generator=g).tolist()
+    forced = [torch.randint(0, 4096, (2,), generator=g) for _ in range(3)] + [torch.randint(0, 4096, (3,), generator=g)]
+
+    def serve(merged):
+        engine = make_engine()
+        backend = pkg("backend").B200Backend(engine, max_new_tokens=16)
+        batch = None
+        for i, p in enumerate(prompts):
+            kv, first, n = backend.prefill(p, f"s{i}")
+            batch = backend.splice_into_batched(batch, kv, n)
+        partial, trace = None, []
+        for step, lo in enumerate(range(0, len(new), 32)):  # chunks of 32, 32 and 11 tokens
+            piece = new[lo:lo + 32]
+            tok = forced[step].view(-1, 1)  # the same input tokens either way, whatever the step before gave
+            if merged:
+                nxt, batch, partial, last, n = backend.decode_step_with_prefill_chunk(tok, batch, piece, partial)
+            else:
+                partial, last, n = backend.prefill_chunk(piece, partial)
+                nxt, batch = backend.decode_step_batched(tok, batch, None, None)
+            trace.append((nxt.tolist(), last, n))
+        # the new sequence joins the batch; one more step reads every page written above
+        batch = backend.splice_into_batched(batch, partial, partial.ctx_len)
+        nxt, batch = backend.decode_step_batched(forced[3].view(-1, 1), batch, None, None)
+        engine.check_status("merged pass test")
+        pages = partial.block_ids[: (len(new) + 15) // 16]
+        return trace, nxt.tolist(), engine.last_logits.float().clone(), [p[pages].float().clone() for p in engine.k_pools], \
+            [p[pages].float().clone() for p in engine.v_pools], partial.block_ids
+
+    tr_a, nxt_a, logits_a, k_a, v_a, ids_a = serve(False)
+    tr_b, nxt_b, logits_b, k_b, v_b, ids_b = serve(True)
+    assert ids_a == ids_b and [t[2] for t in tr_a] == [t[2] for t in tr_b]
+    for a, b in zip(k_a + v_a, k_b + v_b):
+        assert rel_err(b, a) < TOL_MODEL
+    assert rel_err(logits_b, logits_a) < TOL_MODEL
+    # tokens: equal wherever the two-pass logits decide clearly (the merged pass has other GEMM shapes, i.e.
+    # other bf16 rounding points, as with any re-chunking above)
+    top2 = torch.topk(logits_a, 2, dim=-1).values
+    clear = (top2[:, 0] - top2[:, 1]) > 0.05
+    for i in range(len(nxt_a)):
+        assert nxt_a[i] == nxt_b[i] or not bool(clear[i])
+    flat_a = [t for a in tr_a for t in a[0] + [a[1]]]
+    flat_b = [t for b in tr_b for t in b[0] + [b[1]]]
+    assert sum(x == y for x, y in zip(flat_a, flat_b)) >= len(flat_a) - 2, (tr_a, tr_b)  # 9 tokens, near-ties aside
