@@ -16,7 +16,7 @@ ROOT_DIR = os.path.dirname(PKG_DIR)
 CSRC = os.path.join(PKG_DIR, "csrc")
 INCLUDE = os.path.join(ROOT_DIR, "include")
 LIB_PATH = os.path.join(PKG_DIR, "libb200decode.so")
-SOURCES = ["host.cu", "paged_attn.cu", "paged_prefill.cu", "decode_glue.cu", "dense_gemm.cu", "router_fused.cu", "moe_route.cu", "moe_gemm.cu",
+SOURCES = ["host.cu", "paged_attn.cu", "paged_prefill.cu", "paged_prefill_tc.cu", "decode_glue.cu", "dense_gemm.cu", "router_fused.cu", "moe_route.cu", "moe_gemm.cu",
            "moe_layer.cu", "ep_p2p.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",

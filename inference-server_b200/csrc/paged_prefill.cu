@@ -23,6 +23,8 @@
 //   out   = normalised bf16 rows written from registers.
 // Heavy tiles (late positions, long context) are issued first.
 
+#include <stdlib.h>
+
 #include "common.cuh"
 #include "host.h"
 
@@ -303,6 +305,20 @@ static int launch_prefill(const void* q, const void* k_pool, const void* v_pool,
   return 0;
 }
 
+// paged_prefill_tc.cu
+int launch_prefill_tc(const void* q, const void* k_pool, const void* v_pool, const int* table_row, void* out, int* err,
+                      int num_tokens, int first_pos, int hq, int hkv, int num_blocks, float scale, cudaStream_t st);
+
+// The tcgen05 kernel serves head_dim 128 unless the environment variable B200_PREFILL_MMA_SYNC is set to a
+// non-zero value (read once), which keeps every shape on the mma.sync kernel of this file.
+static bool prefill_tc_enabled() {
+  static const bool enabled = [] {
+    const char* v = getenv("B200_PREFILL_MMA_SYNC");
+    return !(v && v[0] != '\0' && v[0] != '0');
+  }();
+  return enabled;
+}
+
 }  // namespace b200
 
 using namespace b200;
@@ -335,6 +351,10 @@ extern "C" int b200_paged_attn_prefill(const void* q, const void* k_pool, const 
   int* err = static_cast<int*>(status_word);
 #define B200_PF_ARGS q, k_pool, v_pool, block_table_row, out, err, num_tokens, first_position, num_q_heads, \
                      num_kv_heads, num_blocks, max_pages_per_seq, scale, st
+  if (head_dim == 128 && prefill_tc_enabled() &&
+      ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(out)) & 15) == 0)
+    return launch_prefill_tc(q, k_pool, v_pool, block_table_row, out, err, num_tokens, first_position, num_q_heads,
+                             num_kv_heads, num_blocks, scale, st);
   if (head_dim == 128 && group == 8) return launch_prefill<128, 8>(B200_PF_ARGS);
   if (head_dim == 128) return launch_prefill<128, 16>(B200_PF_ARGS);
   return launch_prefill<64, 4>(B200_PF_ARGS);
