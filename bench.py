@@ -348,7 +348,8 @@ def prefill_phase(args, cfg, dev, rank, world):
                 peak, src = float(json.load(f)["bf16_tflops_sustained"]), "measured (MEASURED_PEAKS.json bf16_tflops_sustained)"
         except Exception:
             peak, src = 1400.0, "fallback (1.4 PFLOP/s sustained)"
-        roof = {"kernel": "paged_attn_prefill_kernel (mma.sync)", "bound": "tensor", "achieved": flops / us / 1e6, "peak": peak,
+        tc = cfg.head_dim == 128 and os.environ.get("B200_PREFILL_MMA_SYNC", "0") in ("", "0")
+        roof = {"kernel": "paged_attn_prefill_tc_kernel (tcgen05, TMEM accumulators)" if tc else "paged_attn_prefill_kernel (mma.sync)", "bound": "tensor", "achieved": flops / us / 1e6, "peak": peak,
                 "unit": "TFLOP/s", "frac": flops / us / 1e6 / peak, "traffic": None, "flops": flops, "us_per_launch": us,
                 "chunk": chunk, "first_position": first_pos, "peak_source": src, "launches_timed": cfg.layers}
     line = {"metric": "prefill tok/s", "value": args.steps * n / (ms / 1e3), "unit": "tok/s", "n_gpus": 1, "steps": args.steps,

@@ -9,26 +9,32 @@
 //            the context up to its last position.  Heavy tiles (late positions) are issued first.
 //   warp 0   TMA producer: the Q tile once (boxes of G rows x 128 B), then per key tile the 8 K pages and
 //            the 8 V pages of the kv head (boxes of 16 tokens x 128 B, two column halves each) into two
-//            two-stage rings, 128-byte swizzle, mbarrier hand-over.
-//   warp 1   MMA issuer (one thread): S = Q K^T as 8 x tcgen05.mma M128 N128 K16 (kind::f16, bf16, both
-//            operands K-major) into one of two S accumulators in TMEM; O += P V as 8 x M128 N128 K16 with
-//            P (bf16, written by the softmax warps) as the K-major A operand and V as an MN-major B operand
-//            straight from its page layout [key][head_dim].  S of tile j+1 is issued before P V of tile j,
-//            so the tensor pipe works on the next scores while the softmax warps are busy with these.
-//   warps 2-9  softmax: a thread owns one score row and 64 of the tile's 128 key columns (two threads per
-//            row; TMEM lanes are bound to warp_id % 4, so warps w and w+4 see the same rows).  tcgen05.ld
-//            of its half row, causal mask by position, row max exchanged with the partner through shared
-//            memory, p = exp2((s - m) * scale) in fp32, P stored as bf16 into the swizzled A-operand tile.
-//            The running max is lazy: O (in TMEM) and the running sum are rescaled only when a row's
-//            max grew by more than 2^8 since the last rescale (any row of the warp: the whole warp
-//            rescales, through tcgen05.ld / tcgen05.st); until then p is taken against the older max,
-//            which is exact after the final division by the sum taken against the same max.
+//            two-stage rings, 128-byte swizzle, mbarrier hand-over.  The 16 boxes of a tile are issued by 16
+//            lanes side by side.
+//   warp 1   score issuer (one thread): S = Q K^T as 8 x tcgen05.mma M128 N128 K16 (kind::f16, bf16, both
+//            operands K-major) into one of two S accumulators in TMEM, as far ahead as those allow.
+//   warp 2   P V issuer (one thread): O += P V as 2 x 4 tcgen05.mma M128 N128 K16, P (bf16, written by the
+//            softmax warps) as the K-major A operand and V as an MN-major B operand straight from its page
+//            layout [key][head_dim].  A thread gets a tcgen05.mma on its way about every 95 cycles whatever
+//            its N (measured), which is why the two products have an issuer each, and the P tile is handed
+//            over in two halves of 64 keys so that the first half's product starts while the second half's
+//            exponentials are still being taken.
+//   warps 3-10  softmax: a thread owns one score row and 64 of the tile's 128 key columns (two threads per
+//            row; TMEM lanes are bound to warp_id % 4, so warps w and w+4 of these see the same rows and
+//            meet on a 64-thread named barrier).  tcgen05.ld of its half row, causal mask by position, row
+//            max exchanged with the partner through shared memory, p = exp2((s - m) * scale) in fp32, P
+//            stored as bf16 into its half of the swizzled A-operand tile once the product that read that
+//            half for the tile before has finished.  The running max is lazy: O (in TMEM) and the running
+//            sum are rescaled only when a row's max grew by more than 2^8 since the last rescale (any row
+//            of the warp: the whole warp rescales, through tcgen05.ld / tcgen05.st, after both products of
+//            the tile before have finished); until then p is taken against the older max, which is exact
+//            after the final division by the sum taken against the same max.
 //   out      O / l as bf16, each thread 128 contiguous bytes of its row.
 //
 // TMEM: S0 columns 0-127, S1 128-255, O 256-383 (512 allocated).  Shared memory: Q 32 KiB, P 32 KiB,
 // K ring 2 x 32 KiB, V ring 2 x 32 KiB.  Every mbarrier wait is bounded; a wait that runs out records
-// kErrDevWaitTimeout and the thread stops waiting but keeps the loop structure (the named barrier between the
-// softmax warps is still met by all of them), so the kernel ends.
+// kErrDevWaitTimeout and the thread stops waiting but keeps the loop structure (the named barriers between
+// partner warps are still met), so the kernel ends.
 
 #include "common.cuh"
 #include "host.h"
@@ -38,11 +44,12 @@ namespace b200 {
 constexpr int kTcPage = 16;
 constexpr int kTcRows = 128;                 // score rows per CTA = M of the MMAs
 constexpr int kTcKeys = 128;                 // keys per tile = N of S, K of P V
+constexpr int kTcPages = kTcKeys / kTcPage;
 constexpr int kTcD = 128;
 constexpr int kTcHalfBytes = 128 * 128;      // 128 rows x 64 bf16: one swizzled column half of a tile
 constexpr int kTcTileBytes = 2 * kTcHalfBytes;
 constexpr int kTcSoftmaxWarps = 8;
-constexpr int kTcThreads = (2 + kTcSoftmaxWarps) * 32;
+constexpr int kTcThreads = (3 + kTcSoftmaxWarps) * 32;
 constexpr int kTcSmemTiles = 6;              // Q, P, K0, K1, V0, V1
 constexpr int kTcExtraBytes = 256 /* barriers, tmem base */ + 2 * 2 * kTcRows * 4 /* max exchange */ +
                               2 * kTcRows * 4 /* sum exchange */;
@@ -94,6 +101,16 @@ __device__ __forceinline__ float fast_exp2(float x) {
   return y;
 }
 
+// The two warps that own the same 32 score rows (warp w and w + 4 of the softmax warps) meet here.
+__device__ __forceinline__ void pair_barrier(int quarter) {
+  switch (quarter) {
+    case 0: asm volatile("bar.sync 1, 64;" ::: "memory"); break;
+    case 1: asm volatile("bar.sync 2, 64;" ::: "memory"); break;
+    case 2: asm volatile("bar.sync 3, 64;" ::: "memory"); break;
+    default: asm volatile("bar.sync 4, 64;" ::: "memory"); break;
+  }
+}
+
 // G: query heads per kv head (8 or 16).
 template <int G>
 __global__ void __launch_bounds__(kTcThreads, 1)
@@ -113,10 +130,14 @@ paged_attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __
   const uint32_t bar_kfull = bars + 8, bar_kempty = bars + 24;   // [2] each
   const uint32_t bar_vfull = bars + 40, bar_vempty = bars + 56;  // [2] each
   const uint32_t bar_sfull = bars + 72, bar_sempty = bars + 88;  // [2] each: S accumulator written / read
-  const uint32_t bar_pfull = bars + 104;                         // P tile written (and O rescaled)
-  const uint32_t bar_odone = bars + 112;                         // P V of a tile finished
+  const uint32_t bar_pfull = bars + 104;                         // [2] a 64-key half of the P tile written
+  const uint32_t bar_odone = bars + 120;                         // [2] the product over that half finished
+  // [2, by tile parity] every softmax warp is past its rescale of O.  Two of them because a warp that needs no
+  // rescale can get here for tile j + 1 before a warp of another quarter has arrived for tile j; it cannot get
+  // to tile j + 2 before that (its P half waits for the product of tile j, which waits for this barrier).
+  const uint32_t bar_rescaled = bars + 136;
   uint8_t* extra = base_ptr + kTcSmemTiles * kTcTileBytes;
-  uint32_t* tmem_base_sm = reinterpret_cast<uint32_t*>(extra + 128);
+  uint32_t* tmem_base_sm = reinterpret_cast<uint32_t*>(extra + 192);
   float* mx_sm = reinterpret_cast<float*>(extra + 256);          // [2 tiles][2 halves][128 rows]
   float* l_sm = mx_sm + 2 * 2 * kTcRows;                         // [2 halves][128 rows]
 
@@ -135,9 +156,11 @@ paged_attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __
       mbar_init(bar_vempty + 8 * s, 1);
       mbar_init(bar_sfull + 8 * s, 1);
       mbar_init(bar_sempty + 8 * s, kTcSoftmaxWarps);
+      mbar_init(bar_pfull + 8 * s, kTcSoftmaxWarps / 2);
+      mbar_init(bar_odone + 8 * s, 1);
     }
-    mbar_init(bar_pfull, kTcSoftmaxWarps);
-    mbar_init(bar_odone, 1);
+    mbar_init(bar_rescaled, kTcSoftmaxWarps);
+    mbar_init(bar_rescaled + 8, kTcSoftmaxWarps);
     fence_mbar_init();
     fence_proxy_async();
   }
@@ -160,101 +183,98 @@ paged_attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __
 
   if (warp == 0) {
     // ------------------------------------------------------------ TMA ------
-    if (lane == 0) {
-      mbar_arrive_expect_tx(bar_q, kTcTileBytes);
+    // Lanes 0-15 each own one box of a tile: page lane >> 1, column half lane & 1.
+    if (lane == 0) mbar_arrive_expect_tx(bar_q, kTcTileBytes);
+    __syncwarp();
+    for (int i = lane; i < 2 * QT; i += 32) {
+      const int tl = i >> 1, hf = i & 1;
+      tma_load_2d(q_sm + hf * kTcHalfBytes + tl * G * 128, &q_map, bar_q, hf * 64,
+                  (t0 + tl) * num_q_heads + h * G);  // rows past the chunk are filled with zeros
+    }
+    const int pg = (lane >> 1) & 7, hf = lane & 1;
+    bool alive = true;
 #pragma unroll 1
-      for (int tl = 0; tl < QT; ++tl)
-#pragma unroll
-        for (int hf = 0; hf < 2; ++hf)
-          tma_load_2d(q_sm + hf * kTcHalfBytes + tl * G * 128, &q_map, bar_q, hf * 64,
-                      (t0 + tl) * num_q_heads + h * G);  // rows past the chunk are filled with zeros
-      bool alive = true;
-#pragma unroll 1
-      for (int j = 0; j < n_tiles && alive; ++j) {
-        const int st = j & 1;
-        const uint32_t ph = (j >> 1) & 1;
-        int rows[8];
-#pragma unroll
-        for (int pg = 0; pg < 8; ++pg) {
-          // pages past the tile's last position hold nothing this CTA may read; the last valid page stands in so
-          // that every stage is the same number of bytes and holds finite numbers (their scores are masked)
-          int page = __ldg(table_row + min(j * 8 + pg, last_page));
-          if (page < 0 || page >= num_blocks) {
-            set_error(err, kErrDevBadBlockId);
-            page = 0;
-          }
-          rows[pg] = (page * num_kv_heads + h) * kTcPage;
-        }
-        alive = mbar_wait(bar_kempty + 8 * st, ph ^ 1, err);
-        if (!alive) break;
-        mbar_arrive_expect_tx(bar_kfull + 8 * st, kTcTileBytes);
-#pragma unroll
-        for (int pg = 0; pg < 8; ++pg)
-#pragma unroll
-          for (int hf = 0; hf < 2; ++hf)
-            tma_load_2d(k_sm + st * kTcTileBytes + hf * kTcHalfBytes + pg * (kTcPage * 128), &k_map,
-                        bar_kfull + 8 * st, hf * 64, rows[pg]);
-        alive = mbar_wait(bar_vempty + 8 * st, ph ^ 1, err);
-        if (!alive) break;
-        mbar_arrive_expect_tx(bar_vfull + 8 * st, kTcTileBytes);
-#pragma unroll
-        for (int pg = 0; pg < 8; ++pg)
-#pragma unroll
-          for (int hf = 0; hf < 2; ++hf)
-            tma_load_2d(v_sm + st * kTcTileBytes + hf * kTcHalfBytes + pg * (kTcPage * 128), &v_map,
-                        bar_vfull + 8 * st, hf * 64, rows[pg]);
+    for (int j = 0; j < n_tiles; ++j) {
+      const int st = j & 1;
+      const uint32_t ph = (j >> 1) & 1;
+      // pages past the tile's last position hold nothing this CTA may read; the last valid page stands in so that
+      // every stage is the same number of bytes and holds finite numbers (their scores are masked)
+      int page = __ldg(table_row + min(j * kTcPages + pg, last_page));
+      if (page < 0 || page >= num_blocks) {
+        set_error(err, kErrDevBadBlockId);
+        page = 0;
       }
+      const int row = (page * num_kv_heads + h) * kTcPage;
+      const uint32_t dst = st * kTcTileBytes + hf * kTcHalfBytes + pg * (kTcPage * 128);
+      if (alive) alive = mbar_wait(bar_kempty + 8 * st, ph ^ 1, err);
+      if (!__all_sync(0xffffffffu, alive)) break;
+      if (lane == 0) mbar_arrive_expect_tx(bar_kfull + 8 * st, kTcTileBytes);
+      __syncwarp();
+      if (lane < 16) tma_load_2d(k_sm + dst, &k_map, bar_kfull + 8 * st, hf * 64, row);
+      if (alive) alive = mbar_wait(bar_vempty + 8 * st, ph ^ 1, err);
+      if (!__all_sync(0xffffffffu, alive)) break;
+      if (lane == 0) mbar_arrive_expect_tx(bar_vfull + 8 * st, kTcTileBytes);
+      __syncwarp();
+      if (lane < 16) tma_load_2d(v_sm + dst, &v_map, bar_vfull + 8 * st, hf * 64, row);
     }
   } else if (warp == 1) {
-    // ------------------------------------------------------------ MMA ------
+    // ---------------------------------------------------- S = Q K^T ------
     if (lane == 0) {
-      constexpr uint32_t idesc_s = tc_idesc_bf16(kTcRows, kTcKeys, 0);  // S = Q K^T: B = K, K-major
-      constexpr uint32_t idesc_o = tc_idesc_bf16(kTcRows, kTcD, 1);     // O += P V: B = V, MN-major
-      const uint32_t tmem_o = tmem_base + 2 * kTcKeys;
+      constexpr uint32_t idesc_s = tc_idesc_bf16(kTcRows, kTcKeys, 0);  // B = K, K-major
       bool alive = mbar_wait(bar_q, 0, err);
-      auto issue_s = [&](int j) {  // scores of key tile j into S accumulator j & 1
-        const int st = j & 1;
-        const uint32_t ph = (j >> 1) & 1;
-        if (!mbar_wait(bar_kfull + 8 * st, ph, err)) return false;
-        if (!mbar_wait(bar_sempty + 8 * st, ph ^ 1, err)) return false;  // the softmax warps have read tile j - 2
+      const uint64_t a0 = umma_desc_k128(q_sm);
+#pragma unroll 1
+      for (int t = 0; t < n_tiles && alive; ++t) {
+        const int st = t & 1;
+        const uint32_t ph = (t >> 1) & 1;
+        alive = mbar_wait(bar_kfull + 8 * st, ph, err);
+        if (!alive) break;
+        alive = mbar_wait(bar_sempty + 8 * st, ph ^ 1, err);  // the softmax warps have read tile t - 2
+        if (!alive) break;
         tc_fence_after();
-        const uint64_t a0 = umma_desc_k128(q_sm), b0 = umma_desc_k128(k_sm + st * kTcTileBytes);
+        const uint64_t b0 = umma_desc_k128(k_sm + st * kTcTileBytes);
 #pragma unroll
-        for (int k = 0; k < 8; ++k) {
+        for (int k = 0; k < 8; ++k) {  // 16 of the 128 head dimensions each
           const uint32_t off = ((k >> 2) * kTcHalfBytes + (k & 3) * 32) >> 4;
           tc_mma_f16(tmem_base + st * kTcKeys, a0 + off, b0 + off, idesc_s, k > 0 ? 1u : 0u);
         }
         tc_commit(bar_sfull + 8 * st);
         tc_commit(bar_kempty + 8 * st);
-        return true;
-      };
-      if (alive) alive = issue_s(0);
+      }
+    }
+  } else if (warp == 2) {
+    // ---------------------------------------------------- O += P V ------
+    if (lane == 0) {
+      constexpr uint32_t idesc_o = tc_idesc_bf16(kTcRows, kTcD, 1);  // B = V, MN-major
+      const uint32_t tmem_o = tmem_base + 2 * kTcKeys;
+      bool alive = true;
 #pragma unroll 1
       for (int j = 0; j < n_tiles && alive; ++j) {
-        if (j + 1 < n_tiles) {
-          alive = issue_s(j + 1);
-          if (!alive) break;
-        }
         const int st = j & 1;
         alive = mbar_wait(bar_vfull + 8 * st, (j >> 1) & 1, err);
         if (!alive) break;
-        alive = mbar_wait(bar_pfull, j & 1, err);
+        alive = mbar_wait(bar_rescaled + 8 * (j & 1), (j >> 1) & 1, err);  // nobody is rewriting O any more
         if (!alive) break;
-        tc_fence_after();
-        const uint64_t a0 = umma_desc_k128(p_sm);
 #pragma unroll
-        for (int kk = 0; kk < 8; ++kk) {  // 16 keys each
-          const uint32_t aoff = ((kk >> 2) * kTcHalfBytes + (kk & 3) * 32) >> 4;
-          const uint64_t b = umma_desc_mn128(v_sm + st * kTcTileBytes + kk * (16 * 128), kTcHalfBytes, 1024);
-          tc_mma_f16(tmem_o, a0 + aoff, b, idesc_o, (j > 0 || kk > 0) ? 1u : 0u);
+        for (int half = 0; half < 2; ++half) {
+          alive = mbar_wait(bar_pfull + 8 * half, j & 1, err);
+          if (!alive) break;
+          tc_fence_after();
+          const uint64_t a0 = umma_desc_k128(p_sm + half * kTcHalfBytes);
+#pragma unroll
+          for (int kk = 0; kk < 4; ++kk) {  // 16 keys each
+            const uint64_t b = umma_desc_mn128(v_sm + st * kTcTileBytes + (half * 4 + kk) * (16 * 128), kTcHalfBytes, 1024);
+            tc_mma_f16(tmem_o, a0 + ((kk * 32) >> 4), b, idesc_o, (j > 0 || half > 0 || kk > 0) ? 1u : 0u);
+          }
+          tc_commit(bar_odone + 8 * half);
         }
-        tc_commit(bar_odone);
+        if (!alive) break;
         tc_commit(bar_vempty + 8 * st);
       }
     }
   } else {
     // -------------------------------------------------------- softmax ------
-    const int sw = warp - 2;                 // 0..7
+    const int sw = warp - 3;                 // 0..7
     const int hf = sw >> 2;                  // which 64 of the tile's 128 key columns (and of O's 128 columns)
     const int quarter = warp & 3;            // TMEM lanes this warp may touch
     const int r = quarter * 32 + lane;       // score row
@@ -263,6 +283,7 @@ paged_attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __
     const int tl = r / G;
     const bool real = t0 + tl < num_tokens;
     const int pos = first_pos + min(t0 + tl, t_end - 1);  // the last key this row may see
+    uint8_t* p_half = base_ptr + kTcTileBytes + hf * kTcHalfBytes;
     float m_run = -INFINITY, l_run = 0.f;
     bool alive = true;
 #pragma unroll 1
@@ -283,29 +304,31 @@ paged_attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __
       if (lane == 0) mbar_arrive(bar_sempty + 8 * buf);  // this S accumulator may be overwritten
       float s[64];
       const int kbase = j * kTcKeys + hf * 64;
-      float mx = -INFINITY;
+      float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
       if (kbase + 63 > pos) {  // the causal edge runs through this half row
 #pragma unroll
         for (int c = 0; c < 64; ++c) {
           s[c] = kbase + c > pos ? -INFINITY : __uint_as_float(raw[c]);
-          mx = fmaxf(mx, s[c]);
+          mx4[c & 3] = fmaxf(mx4[c & 3], s[c]);
         }
       } else {
 #pragma unroll
         for (int c = 0; c < 64; ++c) {
           s[c] = __uint_as_float(raw[c]);
-          mx = fmaxf(mx, s[c]);
+          mx4[c & 3] = fmaxf(mx4[c & 3], s[c]);
         }
       }
+      const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
       float* mxb = mx_sm + buf * 2 * kTcRows;
       mxb[hf * kTcRows + r] = mx;
-      asm volatile("bar.sync 1, 256;" ::: "memory");  // the eight softmax warps; every one of them gets here
+      pair_barrier(quarter);
       const float m_new = fmaxf(m_run, fmaxf(mx, mxb[(hf ^ 1) * kTcRows + r]));
-      // P of the tile before must have been consumed (P V finished) before P is overwritten or O is touched
-      if (j > 0 && alive) alive = mbar_wait(bar_odone, (j - 1) & 1, err);
       const bool need = (m_new - m_run) * scale_log2 > kTcRescaleLog2;  // true on the first tile (m_run = -inf)
       if (__any_sync(0xffffffffu, need)) {
         if (j > 0) {
+          // O may be touched once both products of the tile before have finished
+          if (alive) alive = mbar_wait(bar_odone + 8 * (hf ^ 1), (j - 1) & 1, err);
+          if (alive) alive = mbar_wait(bar_odone + 8 * hf, (j - 1) & 1, err);
           const float alpha = fast_exp2((m_run - m_new) * scale_log2);
           l_run *= alpha;
           tc_fence_after();
@@ -322,34 +345,37 @@ paged_attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __
         }
         m_run = m_new;
       }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_rescaled + 8 * buf);
+      // this half of the P tile was last read by the product of the tile before
+      if (j > 0 && alive) alive = mbar_wait(bar_odone + 8 * hf, (j - 1) & 1, err);
       const float mb = m_run * scale_log2;
-      float sum = 0.f;
+      float sum4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
       for (int ch = 0; ch < 8; ++ch) {
         float p[8];
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          p[i] = fast_exp2(fmaf(s[ch * 8 + i], scale_log2, -mb));
-          sum += p[i];
-        }
+        for (int i = 0; i < 8; ++i) p[i] = fast_exp2(fmaf(s[ch * 8 + i], scale_log2, -mb));
+        sum4[ch & 3] += ((p[0] + p[1]) + (p[2] + p[3])) + ((p[4] + p[5]) + (p[6] + p[7]));
         uint4 w;
         w.x = pack_bf16x2(p[0], p[1]);
         w.y = pack_bf16x2(p[2], p[3]);
         w.z = pack_bf16x2(p[4], p[5]);
         w.w = pack_bf16x2(p[6], p[7]);
-        *reinterpret_cast<uint4*>(base_ptr + kTcTileBytes + hf * kTcHalfBytes + swz128(r, ch)) = w;
+        *reinterpret_cast<uint4*>(p_half + swz128(r, ch)) = w;
       }
-      l_run += sum;
+      l_run += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
       fence_proxy_async();  // the tensor core reads P through the async proxy
-      tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(bar_pfull);
+      if (lane == 0) mbar_arrive(bar_pfull + 8 * hf);
     }
-    // ---- epilogue: O / l
-    if (alive) alive = mbar_wait(bar_odone, (n_tiles - 1) & 1, err);
+    // ---- epilogue: O / l, once both products of the last tile have finished
+    if (alive) alive = mbar_wait(bar_odone + 8 * (hf ^ 1), (n_tiles - 1) & 1, err);
+    if (alive) alive = mbar_wait(bar_odone + 8 * hf, (n_tiles - 1) & 1, err);
     tc_fence_after();
     l_sm[hf * kTcRows + r] = l_run;
-    asm volatile("bar.sync 1, 256;" ::: "memory");
+    pair_barrier(quarter);
     const float inv = 1.f / (l_run + l_sm[(hf ^ 1) * kTcRows + r]);
     __nv_bfloat16* orow = out + (static_cast<size_t>(t0 + tl) * num_q_heads + h * G + (r - tl * G)) * kTcD + hf * 64;
 #pragma unroll
