@@ -439,7 +439,7 @@ def mixed_phase(args, cfg, dev, engine, table, prompt_lens, spare_blocks, config
                        "two_passes_ms": ms_chunk + ms_step, "merged_over_two_passes": ms_merged / (ms_chunk + ms_step),
                        "decode_rows": B, "chunk_tokens": n, "chunk_first_position": first_pos,
                        "note": "merged and chunk passes are launched eagerly; the decode step alone replays its CUDA graph"}
-    per_layer = (11 if engine._fused_router else 13) - (1 if engine._fused_qkv else 0) + 1  # + the chunk's attention
+    per_layer = (engine.kernel_launches_per_step - 3) // cfg.layers + 1  # the decode step's kernels + the chunk's attention
     line = {"metric": "decode+prefill tok/s", "value": tokens / (ms_merged / 1e3), "unit": "tok/s", "n_gpus": 1,
             "steps": args.steps, "warmup": 3, "ms_per_step": ms_merged, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "fp8 experts (e4m3, fp32 accumulate) + bf16 attention/dense", "data": "synthetic",

@@ -107,6 +107,9 @@ int b200_paged_attn_decode_pairs(const void* q, const void* k_pool, const void* 
  *   block_table_row   [max_pages_per_seq] int32: the sequence's pages
  *   status_word       optional device int32 for device-side findings (bad block id, position past the table)
  * bf16, page_size 16; head_dim 128 with 8 or 16 query heads per kv head, or head_dim 64 with 4.
+ * head_dim 128 (q and out 16-byte aligned) runs on the tcgen05 tensor cores with the scores and the output
+ * accumulated in TMEM; the other shapes, and every shape when the environment variable B200_PREFILL_MMA_SYNC is
+ * set to a non-zero value, on the mma.sync kernel.
  */
 int b200_paged_attn_prefill(const void* q, const void* k_pool, const void* v_pool,
                             const int32_t* block_table_row, void* out, void* status_word, int num_tokens,
