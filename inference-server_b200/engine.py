@@ -496,7 +496,7 @@ class DecodeEngine:
         Under expert parallelism a chunk is one exchange round like a decode step: it is padded to the
         exchange's fixed shape (the engine's full batch) with rows that route nowhere, and the other ranks spend
         the round on a decode step, a chunk of their own or an idle pass.
-        Returns (first generated token, last-position logits)."""
+        Returns (first generated token, last-position logits - None unless the engine was built with keep_logits)."""
         n = len(token_ids)
         if n == 0 or cached_tokens >= n:
             raise ValueError("prefill needs at least one uncached token")
@@ -548,7 +548,8 @@ class DecodeEngine:
                               ep, pairs=pairs, chunk_of=(lo, hi - lo) if tiled else None)
             h_last = h[hi - lo - 1:hi - lo].contiguous()
         first = ops.lm_head_argmax(h_last, self.lm_head, self.argmax_ws, status=self.gemm_status)
-        logits = ops.dense_gemm(h_last, self.lm_head, status=self.gemm_status)[0]
+        # the logits cost a second pass over lm_head: only for engines built to keep them (tests, debugging)
+        logits = ops.dense_gemm(h_last, self.lm_head, status=self.gemm_status)[0] if self.keep_logits else None
         return int(first[0]), logits
 
     @torch.no_grad()
@@ -563,7 +564,8 @@ class DecodeEngine:
         attention treats the rows alike, and attention runs as the tiled causal kernel for the chunk and the
         decode kernel for the rest.
         Returns (next tokens of the B decode rows (device), token after the chunk's last position, its logits);
-        the last two are None unless `want_first`.  Advances ctx_lens of the decode rows by one."""
+        the last two are None unless `want_first` (the logits also unless the engine was built with keep_logits).
+        Advances ctx_lens of the decode rows by one."""
         n = len(chunk_token_ids)
         if self.ep_state is not None:
             raise ValueError("mixed passes are not built for expert-parallel engines: run the chunk and the step as "
@@ -597,7 +599,7 @@ class DecodeEngine:
             first = int(nxt[0])
         else:
             ops.lm_head_argmax(h[n:], self.lm_head, self.argmax_ws, out=self.next_tokens[:B], status=self.gemm_status)
-        if want_first:
+        if want_first and self.keep_logits:
             logits = ops.dense_gemm(h[n - 1:n], self.lm_head, status=self.gemm_status)[0]
         self.ctx_lens[:B] += 1
         return self.next_tokens[:B], first, logits
