@@ -47,6 +47,8 @@
 
 #include <mutex>
 
+#include <stdlib.h>
+
 #include "common.cuh"
 #include "host.h"
 
@@ -94,7 +96,8 @@ struct DenseParams {
   int m_tiles;        // ceil(M / xbox)
   int n_tiles;        // ceil(N / (128 * A_TILES))
   int ksplit;         // CTAs of a cluster that share one tile (1 = no cluster)
-  int xbox;           // rows of X per work item = rows of the X box = N of the MMA: 32, 64, 128 or 256
+  int xbox;           // rows of X per work item = rows of the X box = N of the MMA: a multiple of 32 up to 256
+                      // (a power of two wherever K is split)
 };
 
 // Instruction descriptor: bf16 x bf16 -> f32, both operands K-major.
@@ -796,7 +799,7 @@ extern "C" int b200_qkv_rope_append_gemm(const void* x, const void* wqkv, const 
   p.xbox = pick_xbox(num_rows);
   {
     double best = 1e30;
-    for (int xbox = p.xbox; xbox >= 32; xbox >>= 1) {
+    for (int xbox = p.xbox; xbox >= 32; xbox -= 32) {  // any multiple of 32 here: this epilogue has no K split
       const int items = heads * ((num_rows + xbox - 1) / xbox);
       const double cost = static_cast<double>((items + sms - 1) / sms) * (128.0 + xbox) + xbox * 0.25;
       if (cost < best) {
