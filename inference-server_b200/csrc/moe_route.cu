@@ -472,22 +472,40 @@ __global__ void moe_combine_add_rmsnorm_kernel(const __nv_bfloat16* __restrict__
   grid_dep_wait();
   grid_dep_launch();
   const int t = blockIdx.x, tid = threadIdx.x;
-  float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-  for (int k = 0; k < K; ++k) {
-    const int row = row_of_pair[static_cast<size_t>(t) * K + k];
-    if (row < 0) continue;  // a pair without a result row (dropped by the expert-parallel capacity) adds nothing
-    const float w = topk_w[static_cast<size_t>(t) * K + k];
-    const uint4 raw = *reinterpret_cast<const uint4*>(y + static_cast<size_t>(row) * H + tid * 8);
-    const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
-#pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      const float2 p = __bfloat1622float2(h2[j]);
-      acc[2 * j] += w * p.x;
-      acc[2 * j + 1] += w * p.y;
-    }
-  }
+  // The kernel is a chain of dependent loads (pair -> result row -> its values) on a few KiB per CTA, so it is
+  // bound by memory latency: everything that does not depend on another load is asked for at once - the
+  // residual row and the norm weights here, then up to eight row numbers, then those rows together.  The sums
+  // are taken in pair order as before.
   const size_t base = static_cast<size_t>(t) * H + tid * 8;
   uint4 xr = *reinterpret_cast<const uint4*>(x + base);
+  const uint4 wraw = *reinterpret_cast<const uint4*>(weight + tid * 8);
+  float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+  for (int k0 = 0; k0 < K; k0 += 8) {
+    int rows[8];
+    float ws[8];
+    uint4 raws[8];
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      const bool in = k0 + u < K;
+      // a pair without a result row (dropped by the expert-parallel capacity) has row -1 and adds nothing
+      rows[u] = in ? row_of_pair[static_cast<size_t>(t) * K + k0 + u] : -1;
+      ws[u] = in ? topk_w[static_cast<size_t>(t) * K + k0 + u] : 0.f;
+    }
+#pragma unroll
+    for (int u = 0; u < 8; ++u)
+      if (rows[u] >= 0) raws[u] = *reinterpret_cast<const uint4*>(y + static_cast<size_t>(rows[u]) * H + tid * 8);
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      if (rows[u] < 0) continue;
+      const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&raws[u]);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 p = __bfloat1622float2(h2[j]);
+        acc[2 * j] += ws[u] * p.x;
+        acc[2 * j + 1] += ws[u] * p.y;
+      }
+    }
+  }
   __nv_bfloat162* x2 = reinterpret_cast<__nv_bfloat162*>(&xr);
   float f[8], ss = 0.f;
 #pragma unroll
@@ -505,7 +523,6 @@ __global__ void moe_combine_add_rmsnorm_kernel(const __nv_bfloat16* __restrict__
   float tot = (tid & 31) < (blockDim.x + 31) / 32 ? red[tid & 31] : 0.f;
   tot = warp_sum(tot);
   const float inv = rsqrtf(tot / static_cast<float>(H) + eps);
-  const uint4 wraw = *reinterpret_cast<const uint4*>(weight + tid * 8);
   const __nv_bfloat162* w2 = reinterpret_cast<const __nv_bfloat162*>(&wraw);
   uint4 o;
   __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&o);

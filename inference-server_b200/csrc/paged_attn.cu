@@ -382,13 +382,22 @@ paged_attn_reduce_kernel(const float* __restrict__ part_o, const float2* __restr
   const int n = (L + split_tokens - 1) / split_tokens;
   if (n <= 1) return;
   const size_t base = static_cast<size_t>(row) * max_splits;
+  constexpr int V = D / 32;  // floats per lane
+  // The first eight partial rows (all of them at the usual split counts) are asked for before anything else:
+  // their addresses need only n, and the kernel is bound by the latency of its loads, not by their volume.
+  float pre[8][V];
+  const int npre = min(n, 8);
+#pragma unroll
+  for (int u = 0; u < 8; ++u)
+    if (u < npre)
+#pragma unroll
+      for (int j = 0; j < V; ++j) pre[u][j] = part_o[(base + u) * D + lane * V + j];
   float mmax = -INFINITY;
   for (int s0 = 0; s0 < n; s0 += 32) {
     const float m = s0 + lane < n ? part_ml[base + s0 + lane].x : -INFINITY;
     mmax = fmaxf(mmax, warp_max(m));
   }
   float den = 0.f;
-  constexpr int V = D / 32;  // floats per lane
   float acc[V];
 #pragma unroll
   for (int j = 0; j < V; ++j) acc[j] = 0.f;
@@ -401,6 +410,16 @@ paged_attn_reduce_kernel(const float* __restrict__ part_o, const float2* __restr
     }
     const int cnt = min(32, n - s0);
     int s = 0;
+    if (s0 == 0) {  // the rows fetched above, in split order like the rest
+#pragma unroll
+      for (int u = 0; u < 8; ++u)
+        if (u < npre) {
+          const float wu = __shfl_sync(0xffffffffu, w, u);
+#pragma unroll
+          for (int j = 0; j < V; ++j) acc[j] += wu * pre[u][j];
+        }
+      s = npre;
+    }
     for (; s + 4 <= cnt; s += 4) {
       float v[4][V];
 #pragma unroll
