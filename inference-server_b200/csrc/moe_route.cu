@@ -105,26 +105,45 @@ constexpr int kRankThreads = 256;
 __global__ void __launch_bounds__(kRankThreads)
 moe_rank_kernel(const int* __restrict__ topk_ids, int n_pairs, int* __restrict__ rank,
                 int* __restrict__ counts) {
-  __shared__ int part[kRankThreads];
+  __shared__ int warp_tot[kRankThreads / 32];
   grid_dep_wait();
   grid_dep_launch();
-  const int e = blockIdx.x, tid = threadIdx.x;
+  const int e = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int chunk = (n_pairs + kRankThreads - 1) / kRankThreads;
   const int lo = min(n_pairs, tid * chunk), hi = min(n_pairs, lo + chunk);
+  // Latency-bound (a few KiB of ids per CTA): a thread's ids are read once, eight at a time into registers
+  // (all loads of a group in flight together), and the prefix over the threads is one shuffle scan plus one
+  // exchange of eight warp totals instead of a scan through shared memory.
+  constexpr int kHold = 8;
+  int held[kHold];
   int c = 0;
-  for (int i = lo; i < hi; ++i) c += topk_ids[i] == e;
-  part[tid] = c;
-  __syncthreads();
-  for (int o = 1; o < kRankThreads; o <<= 1) {
-    const int add = tid >= o ? part[tid - o] : 0;
-    __syncthreads();
-    part[tid] += add;
-    __syncthreads();
+#pragma unroll
+  for (int u = 0; u < kHold; ++u) held[u] = lo + u < hi ? topk_ids[lo + u] : -2;
+#pragma unroll
+  for (int u = 0; u < kHold; ++u) c += held[u] == e;
+  for (int i = lo + kHold; i < hi; ++i) c += topk_ids[i] == e;
+  int inc = c;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const int y = __shfl_up_sync(0xffffffffu, inc, o);
+    if (lane >= o) inc += y;
   }
-  int run = part[tid] - c;  // exclusive prefix
-  for (int i = lo; i < hi; ++i)
+  if (lane == 31) warp_tot[warp] = inc;
+  __syncthreads();
+  int before = 0, total = 0;
+#pragma unroll
+  for (int w = 0; w < kRankThreads / 32; ++w) {
+    const int t = warp_tot[w];
+    if (w < warp) before += t;
+    total += t;
+  }
+  int run = before + inc - c;  // exclusive prefix: pairs of this expert in the threads before this one
+#pragma unroll
+  for (int u = 0; u < kHold; ++u)
+    if (held[u] == e) rank[lo + u] = run++;
+  for (int i = lo + kHold; i < hi; ++i)
     if (topk_ids[i] == e) rank[i] = run++;
-  if (tid == kRankThreads - 1) counts[e] = part[tid];
+  if (tid == 0) counts[e] = total;
 }
 
 constexpr int kScatterThreads = 256;
@@ -333,6 +352,14 @@ __global__ void moe_scatter_quant_kernel(const __nv_bfloat16* __restrict__ x, co
   int* warp_tot = toff + E + 1;
   int* dst = warp_tot + 32;
   const int t = blockIdx.x, tid = threadIdx.x;
+  // Latency-bound: the token's row and (threads < K) its pair's expert and rank are asked for first, so that they
+  // travel while the counts are scanned.
+  const uint4 raw = *reinterpret_cast<const uint4*>(x + static_cast<size_t>(t) * H + tid * 8);
+  int my_e = -1, pair_rank = 0;
+  if (tid < K) {
+    my_e = topk_ids[t * K + tid];
+    pair_rank = rank[t * K + tid];
+  }
   for (int e = tid; e < E; e += blockDim.x) {
     cnt[e] = counts[e];
     ntile[e] = (cnt[e] + tile_rows - 1) / tile_rows;
@@ -355,14 +382,14 @@ __global__ void moe_scatter_quant_kernel(const __nv_bfloat16* __restrict__ x, co
   }
   if (tid < K) {
     const int pair = t * K + tid;
-    const int e = topk_ids[pair];
+    const int e = my_e;
     int d = -1;
     if (e < 0 || e >= E) {
       if (e != -1) set_error(err, kErrDevBadExpert);  // -1 is "no expert": the pair is left out, not an error
       row_of_pair[pair] = -1;
       if (slot_of_pair != nullptr) slot_of_pair[pair] = -1;
     } else {
-      d = off[e] + rank[pair];
+      d = off[e] + pair_rank;
       sorted_pair[d] = pair;
       row_of_pair[pair] = d;
       if (slot_of_pair != nullptr) {
@@ -396,7 +423,6 @@ __global__ void moe_scatter_quant_kernel(const __nv_bfloat16* __restrict__ x, co
   }
   __syncthreads();
 
-  const uint4 raw = *reinterpret_cast<const uint4*>(x + static_cast<size_t>(t) * H + tid * 8);
   const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
   float f[8];
   float amax = 0.f;
