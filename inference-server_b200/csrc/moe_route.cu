@@ -114,7 +114,7 @@ moe_rank_kernel(const int* __restrict__ topk_ids, int n_pairs, int* __restrict__
   // Latency-bound (a few KiB of ids per CTA): a thread's ids are read once, eight at a time into registers
   // (all loads of a group in flight together), and the prefix over the threads is one shuffle scan plus one
   // exchange of eight warp totals instead of a scan through shared memory.
-  constexpr int kHold = 8;
+  constexpr int kHold = 16;
   int held[kHold];
   int c = 0;
 #pragma unroll
@@ -216,48 +216,58 @@ moe_scatter_rows_kernel(const int* __restrict__ ids, const int* __restrict__ ran
   int* cnt = sm;
   int* off = sm + E;
   const int tid = threadIdx.x, nthr = blockDim.x;
-  for (int e = tid; e < E; e += nthr) cnt[e] = counts[e];
+  // Latency-bound: the slot's expert, its rank and the first pieces of its row and scales are asked for before
+  // the counts are summed; where they go is known only afterwards.
+  const int i = blockIdx.x;
+  const int e = ids[i];
+  const int slot_rank = rank[i];
+  const int groups = H / 128;
+  const uint4* s4 = reinterpret_cast<const uint4*>(src_q + static_cast<size_t>(i) * H);
+  const bool live = e >= 0 && e < tile_experts;  // a slot whose row is copied
+  uint4 first_piece = make_uint4(0u, 0u, 0u, 0u);
+  float first_scale = 0.f;
+  if (live && tid < H / 16) first_piece = s4[tid];
+  if (live && tid < groups) first_scale = src_s[static_cast<size_t>(i) * groups + tid];
+  for (int e2 = tid; e2 < E; e2 += nthr) cnt[e2] = counts[e2];
   __syncthreads();
-  for (int e = tid; e <= E; e += nthr) {
+  for (int e2 = tid; e2 <= E; e2 += nthr) {
     int s = 0;
-    for (int j = 0; j < e; ++j) s += cnt[j];
-    off[e] = s;
+    for (int j = 0; j < e2; ++j) s += cnt[j];
+    off[e2] = s;
   }
   __syncthreads();
   if (blockIdx.x == 0) {
-    for (int e = tid; e <= E; e += nthr) expert_offsets[e] = off[e];
-    for (int e = tid; e < tile_experts; e += nthr) {
+    for (int e2 = tid; e2 <= E; e2 += nthr) expert_offsets[e2] = off[e2];
+    for (int e2 = tid; e2 < tile_experts; e2 += nthr) {
       int tp = 0;
-      for (int j = 0; j < e; ++j) tp += (cnt[j] + tile_rows - 1) / tile_rows;
-      const int nt = (cnt[e] + tile_rows - 1) / tile_rows;
+      for (int j = 0; j < e2; ++j) tp += (cnt[j] + tile_rows - 1) / tile_rows;
+      const int nt = (cnt[e2] + tile_rows - 1) / tile_rows;
       for (int j = 0; j < nt; ++j) {
         MoeTile t;
-        t.expert = e;
-        t.row0 = off[e] + j * tile_rows;
-        t.rows = min(tile_rows, cnt[e] - j * tile_rows);
+        t.expert = e2;
+        t.row0 = off[e2] + j * tile_rows;
+        t.rows = min(tile_rows, cnt[e2] - j * tile_rows);
         t.pad = 0;
         tiles[tp + j] = t;
       }
-      if (e == tile_experts - 1) *num_tiles = tp + nt;
+      if (e2 == tile_experts - 1) *num_tiles = tp + nt;
     }
   }
-  const int i = blockIdx.x;
-  const int e = ids[i];
   if (e < 0 || e >= E) {
     if (tid == 0) set_error(err, kErrDevBadExpert);
     return;
   }
-  const int dst = off[e] + rank[i];
+  const int dst = off[e] + slot_rank;
   if (tid == 0) {
     sorted_pair[dst] = i;
     row_of_pair[i] = dst;
   }
   if (e >= tile_experts) return;
-  const uint4* s4 = reinterpret_cast<const uint4*>(src_q + static_cast<size_t>(i) * H);
   uint4* d4 = reinterpret_cast<uint4*>(dst_q + static_cast<size_t>(dst) * H);
-  for (int c = tid; c < H / 16; c += nthr) d4[c] = s4[c];
-  const int groups = H / 128;
-  for (int gidx = tid; gidx < groups; gidx += nthr)
+  if (tid < H / 16) d4[tid] = first_piece;
+  for (int c = tid + nthr; c < H / 16; c += nthr) d4[c] = s4[c];
+  if (tid < groups) dst_s[static_cast<size_t>(dst) * groups + tid] = first_scale;
+  for (int gidx = tid + nthr; gidx < groups; gidx += nthr)
     dst_s[static_cast<size_t>(dst) * groups + gidx] = src_s[static_cast<size_t>(i) * groups + gidx];
 }
 
