@@ -63,3 +63,20 @@ def test_overlapped_and_serial_launches_give_the_same_bits():
     assert overlapped["tokens"] == serial["tokens"]
     assert overlapped["logit_bits"] == serial["logit_bits"]
     assert len(overlapped["tokens"]) == 17 and len(overlapped["logit_bits"]) == 16
+
+
+def test_prompt_attention_parity_also_holds_for_the_mma_sync_kernel_at_head_dim_128():
+    """head_dim 128 takes the tcgen05 kernel by default, so the parity tests of the prompt attention exercise the
+    mma.sync kernel only at head_dim 64; with B200_PREFILL_MMA_SYNC=1 (read once per process) the same tests run
+    the mma.sync kernel at every shape."""
+    import torch
+
+    if not torch.cuda.is_available():
+        pytest.skip("no CUDA device")
+    env = dict(os.environ)
+    env["B200_PREFILL_MMA_SYNC"] = "1"
+    out = subprocess.run([sys.executable, "-m", "pytest", os.path.join(ROOT, "tests", "test_gpu_prefill_attn.py"), "-x", "-q",
+                          "-m", "gpu", "-p", "no:cacheprovider"], env=env, cwd=ROOT, capture_output=True, text=True,
+                         timeout=900)
+    assert out.returncode == 0, out.stdout[-3000:] + out.stderr[-1000:]
+    assert " passed" in out.stdout and "failed" not in out.stdout
